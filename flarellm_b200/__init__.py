@@ -1,0 +1,368 @@
+"""flarellm_b200 — B200 attention engine for Flare, host side.
+
+Everything here is a thin ctypes layer over ``libflare_attn.so`` (the C ABI declared in
+``include/flare_attn.h``).  There is no CPU path: a missing library or a missing CUDA
+device raises.
+
+* ``Engine`` / ``KvCache``  — the rich interface (batch, quantised caches, verify, partials)
+* ``CudaBackend``           — the attention hooks of flare-core's ``ComputeBackend`` trait
+  (flare-core/src/model.rs:246-368), same names and argument meaning, batch 1, host f32.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libflare_attn.so")
+
+OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_OOM, ERR_CUDA, ERR_TIMEOUT, ERR_STATE = range(7)
+KV_F32, KV_Q8_0, KV_KIVI_REF, KV_KIVI_G32 = range(4)
+DT_F32, DT_BF16 = 0, 1
+(PLANE_K, PLANE_V, PLANE_K_Q, PLANE_V_Q, PLANE_K_SCALE, PLANE_V_SCALE, PLANE_K_MIN, PLANE_V_MIN,
+ PLANE_K_RES, PLANE_V_RES) = range(10)
+
+_STATUS_NAMES = {0: "OK", 1: "INVALID_ARG", 2: "UNSUPPORTED", 3: "OOM", 4: "CUDA", 5: "TIMEOUT", 6: "STATE"}
+
+# every symbol include/flare_attn.h declares: (name, restype, argtypes)
+_vp, _i, _i64, _f, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_size_t
+_ip = C.POINTER(C.c_int)
+_i64p = C.POINTER(C.c_int64)
+SYMBOLS = [
+    ("flare_attn_create", _i, [_i, C.POINTER(_vp)]),
+    ("flare_attn_destroy", _i, [_vp]),
+    ("flare_attn_set_stream", _i, [_vp, _vp]),
+    ("flare_attn_sync", _i, [_vp]),
+    ("flare_attn_last_error", C.c_char_p, [_vp]),
+    ("flare_attn_launch_count", C.c_uint64, [_vp]),
+    ("flare_attn_backend_name", C.c_char_p, []),
+    ("flare_kv_alloc", _i, [_vp, _i, _i, _i, _i, _i, _i, C.POINTER(_vp)]),
+    ("flare_kv_free", _i, [_vp]),
+    ("flare_kv_write_f32", _i, [_vp, _i, _i, _i64, _vp, _vp, _i]),
+    ("flare_kv_append_f32", _i, [_vp, _i, _i, _i, _vp, _vp, _i]),
+    ("flare_kv_write_step_f32", _i, [_vp, _i, _vp, _vp, _i]),
+    ("flare_kv_advance", _i, [_vp, _i, _i]),
+    ("flare_kv_get_state", _i, [_vp, _i, _i64p, _i64p]),
+    ("flare_kv_set_state", _i, [_vp, _i, _i64, _i64]),
+    ("flare_kv_truncate", _i, [_vp, _i, _i64]),
+    ("flare_kv_clear", _i, [_vp, _i]),
+    ("flare_kv_plane_bytes", _sz, [_vp, _i]),
+    ("flare_kv_export_plane", _i, [_vp, _i, _i, _i, _vp, _sz, _i]),
+    ("flare_kv_import_plane", _i, [_vp, _i, _i, _i, _vp, _sz, _i]),
+    ("flare_kv_import_q8_0_blocks", _i, [_vp, _i, _i, _i, _i, _vp, _vp, _i]),
+    ("flare_kv_export_q8_0_blocks", _i, [_vp, _i, _i, _i, _i, _vp, _vp, _i]),
+    ("flare_kv_export_dequant", _i, [_vp, _i, _i, _vp, _vp, _i]),
+    ("flare_decode_attn", _i, [_vp, _vp, _i, _i, _vp, _i, _ip, _f, _vp, _i]),
+    ("flare_decode_attn_partial", _i, [_vp, _vp, _i, _i, _vp, _i, _i, _i, _vp, _i]),
+    ("flare_merge_partials", _i, [_vp, _vp, _i, _i, _i, _vp, _i]),
+    ("flare_gqa_attention_host", _i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _vp]),
+    ("flare_prefill_attn", _i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _i, _i]),
+    ("flare_backend_init_gpu_kv_cache", _i, [_vp, _i, _i, _i, _i]),
+    ("flare_backend_init_gpu_kv_cache_dtype", _i, [_vp, _i, _i, _i, _i, _i]),
+    ("flare_backend_gpu_kv_write", _i, [_vp, _i, _i64, _i, _i, _vp, _vp]),
+    ("flare_backend_has_gpu_kv_cache", _i, [_vp]),
+    ("flare_backend_gqa_from_gpu_cache", _i, [_vp, _vp, _i, _i, _i, _i, _i, _f, _vp]),
+    ("flare_backend_kv", _vp, [_vp]),
+]
+
+_lib = None
+
+
+class FlareError(RuntimeError):
+    def __init__(self, status, message):
+        super().__init__(f"flare_attn status {status} ({_STATUS_NAMES.get(status, '?')}): {message}")
+        self.status = status
+
+
+def lib() -> C.CDLL:
+    """Load libflare_attn.so and declare every entry point.  Raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise FileNotFoundError(
+                f"{LIB_PATH} is missing: build it with `python -m flarellm_b200.build` "
+                "(there is no CPU fallback)")
+        L = C.CDLL(LIB_PATH)
+        for name, res, args in SYMBOLS:
+            fn = getattr(L, name)          # AttributeError if the library lacks a declared symbol
+            fn.restype = res
+            fn.argtypes = args
+        _lib = L
+    return _lib
+
+
+def _ptr(a):
+    """numpy array -> host pointer; int -> device pointer."""
+    if a is None:
+        return None
+    if isinstance(a, np.ndarray):
+        assert a.flags["C_CONTIGUOUS"]
+        return a.ctypes.data
+    return int(a)
+
+
+class Engine:
+    """One CUDA device + stream (flare_attn_ctx)."""
+
+    def __init__(self, device: int = 0):
+        self.L = lib()
+        h = _vp()
+        st = self.L.flare_attn_create(device, C.byref(h))
+        if st != OK:
+            raise FlareError(st, "flare_attn_create failed (is a CUDA device present?)")
+        self.h = h
+        self.device = device
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.L.flare_attn_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def check(self, st):
+        if st != OK:
+            raise FlareError(st, self.L.flare_attn_last_error(self.h).decode())
+
+    def set_stream(self, cuda_stream):
+        self.check(self.L.flare_attn_set_stream(self.h, cuda_stream))
+
+    def sync(self):
+        self.check(self.L.flare_attn_sync(self.h))
+
+    def launch_count(self) -> int:
+        return int(self.L.flare_attn_launch_count(self.h))
+
+    def kv_alloc(self, num_layers, batch, max_seq_len, num_kv_heads, head_dim, dtype=KV_F32) -> "KvCache":
+        return KvCache(self, num_layers, batch, max_seq_len, num_kv_heads, head_dim, dtype)
+
+    # ---- attention -------------------------------------------------------------------------
+    def decode(self, kv: "KvCache", layer, num_heads, q, n_q=1, attend_len=None, softcap=0.0, out=None):
+        """q: host ndarray [batch][n_q][num_heads][head_dim] f32, or a device pointer (int) with
+        ``out`` a device pointer as well."""
+        on_device = not isinstance(q, np.ndarray)
+        if not on_device:
+            q = np.ascontiguousarray(q, dtype=np.float32)
+            assert q.size == kv.batch * n_q * num_heads * kv.head_dim
+            if out is None:
+                out = np.empty((kv.batch, n_q, num_heads, kv.head_dim), dtype=np.float32)
+        al = None
+        if attend_len is not None:
+            al_arr = np.ascontiguousarray(attend_len, dtype=np.int32)
+            assert al_arr.size == kv.batch
+            al = al_arr.ctypes.data_as(_ip)
+        self.check(self.L.flare_decode_attn(self.h, kv.h, layer, num_heads, _ptr(q), n_q, al, softcap, _ptr(out),
+                                            int(on_device)))
+        return out
+
+    def decode_partial(self, kv, layer, num_heads, q, slot_begin, slot_end, n_q=1, out=None):
+        on_device = not isinstance(q, np.ndarray)
+        if not on_device:
+            q = np.ascontiguousarray(q, dtype=np.float32)
+            if out is None:
+                out = np.empty((kv.batch, n_q, num_heads, kv.head_dim + 2), dtype=np.float32)
+        self.check(self.L.flare_decode_attn_partial(self.h, kv.h, layer, num_heads, _ptr(q), n_q, slot_begin,
+                                                    slot_end, _ptr(out), int(on_device)))
+        return out
+
+    def merge_partials(self, partials, n_parts, rows, head_dim, out=None):
+        on_device = not isinstance(partials, np.ndarray)
+        if not on_device:
+            partials = np.ascontiguousarray(partials, dtype=np.float32)
+            assert partials.size == n_parts * rows * (head_dim + 2)
+            if out is None:
+                out = np.empty((rows, head_dim), dtype=np.float32)
+        self.check(self.L.flare_merge_partials(self.h, _ptr(partials), n_parts, rows, head_dim, _ptr(out),
+                                               int(on_device)))
+        return out
+
+    def gqa_attention_host(self, q, k_cache, v_cache, num_heads, num_kv_heads, head_dim, seq_len, softcap=0.0):
+        q = np.ascontiguousarray(q, dtype=np.float32)
+        k = np.ascontiguousarray(k_cache, dtype=np.float32)
+        v = np.ascontiguousarray(v_cache, dtype=np.float32)
+        out = np.empty(num_heads * head_dim, dtype=np.float32)
+        self.check(self.L.flare_gqa_attention_host(self.h, _ptr(q), _ptr(k), _ptr(v), num_heads, num_kv_heads,
+                                                   head_dim, seq_len, softcap, _ptr(out)))
+        return out
+
+    def prefill(self, q, k, v, batch, seq_len, num_heads, num_kv_heads, head_dim, window=0, softcap=0.0,
+                in_dtype=DT_F32, out_dtype=DT_F32, out=None):
+        """Host: q/k/v ndarrays (float32, or uint16 holding bf16 bits).  Device: pointers (int)."""
+        on_device = not isinstance(q, np.ndarray)
+        if not on_device:
+            want = np.float32 if in_dtype == DT_F32 else np.uint16
+            q, k, v = (np.ascontiguousarray(a, dtype=want) for a in (q, k, v))
+            if out is None:
+                out = np.empty((batch, seq_len, num_heads, head_dim),
+                               dtype=np.float32 if out_dtype == DT_F32 else np.uint16)
+        self.check(self.L.flare_prefill_attn(self.h, _ptr(q), _ptr(k), _ptr(v), in_dtype, batch, seq_len, num_heads,
+                                             num_kv_heads, head_dim, window, softcap, _ptr(out), out_dtype,
+                                             int(on_device)))
+        return out
+
+
+class KvCache:
+    """Device ring-buffer KV cache for ``batch`` sequences (flare_kv)."""
+
+    def __init__(self, eng: Engine, num_layers, batch, max_seq_len, num_kv_heads, head_dim, dtype):
+        self.eng, self.L = eng, eng.L
+        h = _vp()
+        eng.check(self.L.flare_kv_alloc(eng.h, num_layers, batch, max_seq_len, num_kv_heads, head_dim, dtype,
+                                        C.byref(h)))
+        self.h = h
+        self.num_layers, self.batch, self.max_seq_len = num_layers, batch, max_seq_len
+        self.num_kv_heads, self.head_dim, self.dtype = num_kv_heads, head_dim, dtype
+        self.kv_dim = num_kv_heads * head_dim
+        self._owned = True
+
+    def free(self):
+        if getattr(self, "h", None) and self._owned and getattr(self.eng, "h", None):
+            self.L.flare_kv_free(self.h)
+        self.h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+    def write(self, layer, seq, abs_position, key, value):
+        on_device = not isinstance(key, np.ndarray)
+        if not on_device:
+            key = np.ascontiguousarray(key, dtype=np.float32)
+            value = np.ascontiguousarray(value, dtype=np.float32)
+            assert key.size == value.size == self.kv_dim
+        self.eng.check(self.L.flare_kv_write_f32(self.h, layer, seq, abs_position, _ptr(key), _ptr(value),
+                                                 int(on_device)))
+
+    def append(self, layer, seq, key, value, n_rows=None):
+        on_device = not isinstance(key, np.ndarray)
+        if not on_device:
+            key = np.ascontiguousarray(key, dtype=np.float32)
+            value = np.ascontiguousarray(value, dtype=np.float32)
+            n_rows = key.size // self.kv_dim
+            assert key.size == value.size == n_rows * self.kv_dim
+        self.eng.check(self.L.flare_kv_append_f32(self.h, layer, seq, n_rows, _ptr(key), _ptr(value), int(on_device)))
+
+    def write_step(self, layer, key, value):
+        """Row b of key/value [batch][kv_dim] -> the current ring position of sequence b."""
+        on_device = not isinstance(key, np.ndarray)
+        if not on_device:
+            key = np.ascontiguousarray(key, dtype=np.float32)
+            value = np.ascontiguousarray(value, dtype=np.float32)
+            assert key.size == value.size == self.batch * self.kv_dim
+        self.eng.check(self.L.flare_kv_write_step_f32(self.h, layer, _ptr(key), _ptr(value), int(on_device)))
+
+    def advance(self, seq=-1, n=1):
+        self.eng.check(self.L.flare_kv_advance(self.h, seq, n))
+
+    def state(self, seq=0):
+        p, l = C.c_int64(), C.c_int64()
+        self.eng.check(self.L.flare_kv_get_state(self.h, seq, C.byref(p), C.byref(l)))
+        return int(p.value), int(l.value)
+
+    def set_state(self, seq, position, length):
+        self.eng.check(self.L.flare_kv_set_state(self.h, seq, position, length))
+
+    def len(self, seq=0):
+        return self.state(seq)[1]
+
+    def position(self, seq=0):
+        return self.state(seq)[0]
+
+    def truncate(self, seq, target_len):
+        self.eng.check(self.L.flare_kv_truncate(self.h, seq, target_len))
+
+    def clear(self, seq=-1):
+        self.eng.check(self.L.flare_kv_clear(self.h, seq))
+
+    def plane_bytes(self, plane) -> int:
+        return int(self.L.flare_kv_plane_bytes(self.h, plane))
+
+    def export_plane(self, layer, seq, plane, dtype=np.uint8) -> np.ndarray:
+        n = self.plane_bytes(plane)
+        out = np.empty(n, dtype=np.uint8)
+        self.eng.check(self.L.flare_kv_export_plane(self.h, layer, seq, plane, _ptr(out), n, 0))
+        return out.view(dtype)
+
+    def import_plane(self, layer, seq, plane, data):
+        on_device = not isinstance(data, np.ndarray)
+        if on_device:
+            n = self.plane_bytes(plane)
+        else:
+            data = np.ascontiguousarray(data)
+            n = data.nbytes
+        self.eng.check(self.L.flare_kv_import_plane(self.h, layer, seq, plane, _ptr(data), n, int(on_device)))
+
+    def import_q8_0_blocks(self, layer, seq, first_slot, k_blocks, v_blocks):
+        k_blocks = np.ascontiguousarray(k_blocks, dtype=np.uint8)
+        v_blocks = np.ascontiguousarray(v_blocks, dtype=np.uint8)
+        n_slots = k_blocks.size // (self.kv_dim // 32 * 34)
+        self.eng.check(self.L.flare_kv_import_q8_0_blocks(self.h, layer, seq, first_slot, n_slots, _ptr(k_blocks),
+                                                          _ptr(v_blocks), 0))
+
+    def export_q8_0_blocks(self, layer, seq, first_slot, n_slots):
+        n = n_slots * (self.kv_dim // 32 * 34)
+        kb, vb = np.empty(n, dtype=np.uint8), np.empty(n, dtype=np.uint8)
+        self.eng.check(self.L.flare_kv_export_q8_0_blocks(self.h, layer, seq, first_slot, n_slots, _ptr(kb), _ptr(vb), 0))
+        return kb, vb
+
+    def export_dequant(self, layer, seq):
+        k = np.empty((self.max_seq_len, self.kv_dim), dtype=np.float32)
+        v = np.empty((self.max_seq_len, self.kv_dim), dtype=np.float32)
+        self.eng.check(self.L.flare_kv_export_dequant(self.h, layer, seq, _ptr(k), _ptr(v), 0))
+        return k, v
+
+
+class CudaBackend:
+    """The attention hooks of flare-core's ``ComputeBackend`` (flare-core/src/model.rs:246-368),
+    as a Rust ``impl ComputeBackend for CudaBackend`` would forward them.  The trait's only
+    error channel is a panic; here a non-zero status raises ``FlareError``."""
+
+    def __init__(self, device: int = 0):
+        self.eng = Engine(device)
+        self.L = self.eng.L
+
+    def name(self) -> str:
+        return self.L.flare_attn_backend_name().decode()
+
+    def init_gpu_kv_cache(self, num_layers, max_seq_len, num_kv_heads, head_dim, kv_dtype=KV_F32):
+        self.eng.check(self.L.flare_backend_init_gpu_kv_cache_dtype(self.eng.h, num_layers, max_seq_len, num_kv_heads,
+                                                                    head_dim, kv_dtype))
+
+    def gpu_kv_write(self, layer, position, num_kv_heads, head_dim, key, value):
+        key = np.ascontiguousarray(key, dtype=np.float32)
+        value = np.ascontiguousarray(value, dtype=np.float32)
+        self.eng.check(self.L.flare_backend_gpu_kv_write(self.eng.h, layer, position, num_kv_heads, head_dim,
+                                                         _ptr(key), _ptr(value)))
+
+    def has_gpu_kv_cache(self) -> bool:
+        return bool(self.L.flare_backend_has_gpu_kv_cache(self.eng.h))
+
+    def grouped_query_attention_from_gpu_cache(self, q, layer, num_heads, num_kv_heads, head_dim, seq_len,
+                                               attn_softcap=0.0) -> np.ndarray:
+        q = np.ascontiguousarray(q, dtype=np.float32)
+        out = np.empty(num_heads * head_dim, dtype=np.float32)
+        self.eng.check(self.L.flare_backend_gqa_from_gpu_cache(self.eng.h, _ptr(q), layer, num_heads, num_kv_heads,
+                                                               head_dim, seq_len, attn_softcap, _ptr(out)))
+        return out
+
+    def grouped_query_attention(self, q, k_cache, v_cache, num_heads, num_kv_heads, head_dim, seq_len,
+                                attn_softcap=0.0) -> np.ndarray:
+        return self.eng.gqa_attention_host(q, k_cache, v_cache, num_heads, num_kv_heads, head_dim, seq_len,
+                                           attn_softcap)
+
+    def prefill_attention_gpu(self, q, k, v, seq_len, num_heads, num_kv_heads, head_dim, attn_softcap=0.0):
+        out = self.eng.prefill(q, k, v, 1, seq_len, num_heads, num_kv_heads, head_dim, softcap=attn_softcap)
+        return out.reshape(-1)
+
+    def advance_kv(self, n=1):
+        """KvCache::advance for the context-owned cache (the Rust side calls flare_kv_advance on
+        flare_backend_kv() where Model advances its CPU cache, flare-core/src/model.rs:2547)."""
+        self.eng.check(self.L.flare_kv_advance(self.L.flare_backend_kv(self.eng.h), 0, n))

@@ -1,0 +1,131 @@
+// Internal declarations shared by the .cu files of libflare_attn.so.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+#include <string>
+#include <vector>
+
+#include "../../include/flare_attn.h"
+
+#define FLARE_G32_RESIDUAL 128
+#define FLARE_REF_RESIDUAL 32
+#define FLARE_SMALL_SLOTS 64
+
+struct flare_attn_ctx {
+    int device = 0;
+    cudaStream_t own_stream = nullptr;
+    cudaStream_t stream = nullptr;
+    std::string last_error;
+    uint64_t launches = 0;
+    // scratch owned by the context (grown on demand, never shrunk)
+    void* d_work = nullptr;      size_t work_bytes = 0;     // split-KV partials
+    void* d_stage_in = nullptr;  size_t stage_in_bytes = 0; // device copy of host q / K / V
+    void* d_stage_out = nullptr; size_t stage_out_bytes = 0;
+    void* d_misc = nullptr;      size_t misc_bytes = 0;     // attend_len and other small arrays
+    void* h_pinned = nullptr;    size_t pinned_bytes = 0;
+    uint64_t small_counter = 0;
+    cudaEvent_t small_events[FLARE_SMALL_SLOTS] = {};
+    int sm_count = 148;
+    flare_kv* backend_kv = nullptr;  // cache created by flare_backend_init_gpu_kv_cache
+};
+
+struct flare_kv {
+    flare_attn_ctx* ctx = nullptr;
+    int num_layers = 0, batch = 0, max_seq_len = 0, num_kv_heads = 0, head_dim = 0, kv_dim = 0;
+    int dtype = 0;
+    void* plane[FLARE_PLANE_COUNT] = {};
+    size_t plane_bytes[FLARE_PLANE_COUNT] = {};   // per (layer, sequence)
+    std::vector<int64_t> position, length;       // per sequence
+    inline char* plane_ptr(int p, int layer, int seq) const {
+        return (char*)plane[p] + ((size_t)layer * batch + seq) * plane_bytes[p];
+    }
+};
+
+int flare_set_error(flare_attn_ctx* ctx, int code, const char* fmt, ...);
+
+#define FLARE_CUDA_OK(ctx, expr)                                                           \
+    do {                                                                                   \
+        cudaError_t _e = (expr);                                                           \
+        if (_e != cudaSuccess)                                                             \
+            return flare_set_error((ctx), _e == cudaErrorMemoryAllocation ? FLARE_ERR_OOM : FLARE_ERR_CUDA, \
+                                   "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), __FILE__, __LINE__); \
+    } while (0)
+
+#define FLARE_TRY(expr)                 \
+    do {                                \
+        int _s = (expr);                \
+        if (_s != FLARE_OK) return _s;  \
+    } while (0)
+
+#define FLARE_LAUNCH_CHECK(ctx)                                                            \
+    do {                                                                                   \
+        (ctx)->launches++;                                                                 \
+        cudaError_t _e = cudaGetLastError();                                               \
+        if (_e != cudaSuccess)                                                             \
+            return flare_set_error((ctx), FLARE_ERR_CUDA, "kernel launch failed: %s (%s:%d)", \
+                                   cudaGetErrorString(_e), __FILE__, __LINE__);            \
+    } while (0)
+
+int flare_ensure(flare_attn_ctx* ctx, void** buf, size_t* have, size_t need);
+int flare_ensure_pinned(flare_attn_ctx* ctx, size_t need);
+
+// ---- device views of one (layer) of a cache, handed to kernels by value -------------------
+struct KvLayerView {
+    int dtype, batch, max_seq_len, num_kv_heads, head_dim, kv_dim;
+    const char* plane[FLARE_PLANE_COUNT];     // base of (layer, seq 0)
+    size_t stride[FLARE_PLANE_COUNT];         // bytes between sequences
+};
+KvLayerView flare_layer_view(const flare_kv* kv, int layer);
+
+// ---- kernels-in-other-files entry points (host launchers) ----------------------------------
+struct DecodeArgs {
+    KvLayerView kv;
+    const float* q;        // device [batch][n_q][nh][hd]
+    float* out;            // device: final [batch][n_q][nh][hd] or partial [..][hd+2]
+    const int* attend_len; // device [batch]  (slots seen by the last query)
+    const int2* ring;      // device [batch]  (position, length) — KIVI caches need it
+    int batch, n_q, num_heads;
+    int slot_begin, slot_end;  // restrict to [slot_begin, slot_end) (slot_end < 0: no restriction)
+    int want_partial;          // 1: write [m, l, o] unnormalised
+    int causal_q;              // 1: query i of n_q reads attend_len - (n_q-1-i) slots; 0: all read attend_len
+    int max_attend;            // max over batch of attend_len (host-known upper bound)
+};
+int flare_launch_decode(flare_attn_ctx* ctx, const DecodeArgs& a);
+int flare_launch_decode_generic(flare_attn_ctx* ctx, const DecodeArgs& a);
+int flare_launch_merge(flare_attn_ctx* ctx, const float* partials, size_t part_stride_floats, int n_parts,
+                       int rows, int head_dim, float* out, int want_partial);
+
+struct PrefillArgs {
+    const void *q, *k, *v; void* out;   // device
+    int in_dtype, out_dtype, batch, seq_len, num_heads, num_kv_heads, head_dim, window;
+};
+int flare_launch_prefill(flare_attn_ctx* ctx, const PrefillArgs& a);
+
+int flare_launch_kv_write(flare_kv* kv, int layer, int seq, int64_t first_abs_position, int64_t length_before,
+                          int n_rows, const float* d_key, const float* d_value);
+int flare_launch_kv_write_step(flare_kv* kv, int layer, const int2* d_ring, const float* d_key, const float* d_value);
+int flare_launch_kv_export_dequant(flare_kv* kv, int layer, int seq, float* d_k, float* d_v);
+int flare_launch_q8_blocks(flare_kv* kv, int layer, int seq, int first_slot, int n_slots, void* d_kb, void* d_vb,
+                           int to_blocks);
+
+// ---- device codecs ---------------------------------------------------------------------------
+#ifdef __CUDACC__
+// 2-bit code i of a packed stream (flare-core/src/kv_cache.rs:374-391).
+__device__ __forceinline__ float q2_code(const uint8_t* packed, int i) {
+    return (float)((packed[i >> 2] >> ((i & 3) * 2)) & 3);
+}
+// code * scale + min as a separate multiply and add, never fused.
+__device__ __forceinline__ float q2_dequant(float code, float scale, float mn) {
+    return __fadd_rn(__fmul_rn(code, scale), mn);
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+#endif

@@ -1,0 +1,447 @@
+// Split-KV GQA decode attention over the ring-buffer cache, all cache formats, dequantised
+// in the kernel.  This is the general CUDA-core path: every (kv head, group of <= 4 query
+// heads, query, slot range) is one CTA that streams its K and V rows exactly once and keeps
+// the running (max, sum, output) of flare-core's online softmax
+// (flare-core/src/model.rs:9914-9966) in registers; ranges are combined by log-sum-exp.
+//
+// Work split inside a CTA (128 threads): a group of TPS = head_dim/8 lanes owns one slot at
+// a time, each lane 8 consecutive channels of it, so a row is read with 16/32-byte vector
+// loads; the 32/TPS lane groups of the 4 warps take interleaved slots and hold independent
+// softmax states that are combined once at the end (shuffles, then shared memory).
+#include "common.cuh"
+#include <math_constants.h>
+
+namespace {
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+struct SeqKv {
+    const char* p[FLARE_PLANE_COUNT];
+    int max_seq, kv_dim, position, length, newest;
+};
+
+// ---- row loaders: channels [c0, c0+8) of ring slot `slot`, as the reference dequantises them
+template <int DT, bool IS_V> struct Row;
+
+template <bool IS_V> struct Row<FLARE_KV_F32, IS_V> {
+    static __device__ __forceinline__ void load8(const SeqKv& s, int slot, int c0, float* o) {
+        const float4* r = reinterpret_cast<const float4*>(s.p[IS_V ? FLARE_PLANE_V : FLARE_PLANE_K]) +
+                          ((size_t)slot * s.kv_dim + c0) / 4;
+        float4 a = __ldg(r), b = __ldg(r + 1);
+        o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+    }
+};
+
+template <bool IS_V> struct Row<FLARE_KV_Q8_0, IS_V> {
+    static __device__ __forceinline__ void load8(const SeqKv& s, int slot, int c0, float* o) {
+        const char* qp = s.p[IS_V ? FLARE_PLANE_V_Q : FLARE_PLANE_K_Q] + (size_t)slot * s.kv_dim + c0;
+        int2 raw = __ldg(reinterpret_cast<const int2*>(qp));
+        const __half* sp = reinterpret_cast<const __half*>(s.p[IS_V ? FLARE_PLANE_V_SCALE : FLARE_PLANE_K_SCALE]) +
+                           (size_t)slot * (s.kv_dim / 32) + c0 / 32;
+        float sc = __half2float(__ldg(sp));
+        // (i8 as f32) * scale, one multiply (flare-loader/src/quantize.rs:188-197)
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            o[i] = (float)(int8_t)((raw.x >> (8 * i)) & 0xFF) * sc;
+            o[4 + i] = (float)(int8_t)((raw.y >> (8 * i)) & 0xFF) * sc;
+        }
+    }
+};
+
+// flare-core QuantizedKvCache::dequant_keys / dequant_values (kv_cache.rs:189-250) seen
+// from a ring slot, including what the decode step observes between write and advance.
+template <bool IS_V> struct Row<FLARE_KV_KIVI_REF, IS_V> {
+    static __device__ __forceinline__ void load8(const SeqKv& s, int slot, int c0, float* o) {
+        int R = s.max_seq < FLARE_REF_RESIDUAL ? s.max_seq : FLARE_REF_RESIDUAL;
+        int t;
+        if (s.length < s.max_seq) {
+            if (slot >= s.length) {   // not yet part of the cache: dequant_* leaves zeros there
+#pragma unroll
+                for (int i = 0; i < 8; i++) o[i] = 0.0f;
+                return;
+            }
+            t = slot;
+        } else {
+            t = slot - s.position;
+            if (t < 0) t += s.max_seq;
+        }
+        bool in_res = (s.length <= R) || (t >= s.length - R);
+        if (in_res) {
+            const float* r = reinterpret_cast<const float*>(s.p[IS_V ? FLARE_PLANE_V_RES : FLARE_PLANE_K_RES]) +
+                             (size_t)(slot % R) * s.kv_dim + c0;
+#pragma unroll
+            for (int i = 0; i < 8; i++) o[i] = __ldg(r + i);
+            return;
+        }
+        int ppt = s.kv_dim / 4;
+        const uint8_t* pk = reinterpret_cast<const uint8_t*>(s.p[IS_V ? FLARE_PLANE_V_Q : FLARE_PLANE_K_Q]) +
+                            (size_t)slot * ppt;
+        if (IS_V) {
+            float sc = __ldg(reinterpret_cast<const float*>(s.p[FLARE_PLANE_V_SCALE]) + slot);
+            float mn = __ldg(reinterpret_cast<const float*>(s.p[FLARE_PLANE_V_MIN]) + slot);
+#pragma unroll
+            for (int i = 0; i < 8; i++) o[i] = q2_dequant(q2_code(pk, c0 + i), sc, mn);
+        } else {
+            const float* sc = reinterpret_cast<const float*>(s.p[FLARE_PLANE_K_SCALE]) + c0;
+            const float* mn = reinterpret_cast<const float*>(s.p[FLARE_PLANE_K_MIN]) + c0;
+#pragma unroll
+            for (int i = 0; i < 8; i++) o[i] = q2_dequant(q2_code(pk, c0 + i), __ldg(sc + i), __ldg(mn + i));
+        }
+    }
+};
+
+template <bool IS_V> struct Row<FLARE_KV_KIVI_G32, IS_V> {
+    static __device__ __forceinline__ void load8(const SeqKv& s, int slot, int c0, float* o) {
+        int age = s.newest - slot;
+        if (age < 0) age += s.max_seq;
+        if (age < FLARE_G32_RESIDUAL) {
+            const uint4* r = reinterpret_cast<const uint4*>(
+                s.p[IS_V ? FLARE_PLANE_V_RES : FLARE_PLANE_K_RES] +
+                ((size_t)(slot % FLARE_G32_RESIDUAL) * s.kv_dim + c0) * 2);
+            uint4 w = __ldg(r);
+            const __half2* h = reinterpret_cast<const __half2*>(&w);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                float2 f = __half22float2(h[i]);
+                o[2 * i] = f.x; o[2 * i + 1] = f.y;
+            }
+            return;
+        }
+        if (IS_V) {
+            const uint16_t* cp = reinterpret_cast<const uint16_t*>(s.p[FLARE_PLANE_V_Q] + (size_t)slot * (s.kv_dim / 4) + c0 / 4);
+            uint32_t w = __ldg(cp);
+            const __half2* mp = reinterpret_cast<const __half2*>(s.p[FLARE_PLANE_V_SCALE]) +
+                                (size_t)slot * (s.kv_dim / 32) + c0 / 32;
+            float2 m = __half22float2(__ldg(mp));
+#pragma unroll
+            for (int i = 0; i < 8; i++) o[i] = q2_dequant((float)((w >> (2 * i)) & 3), m.x, m.y);
+        } else {
+            int grp = slot >> 5, tin = slot & 31;
+            const uint8_t* cp = reinterpret_cast<const uint8_t*>(s.p[FLARE_PLANE_K_Q]) +
+                                ((size_t)grp * s.kv_dim + c0) * 8 + (tin >> 2);
+            const __half2* mp = reinterpret_cast<const __half2*>(s.p[FLARE_PLANE_K_SCALE]) + (size_t)grp * s.kv_dim + c0;
+            int sh = (tin & 3) * 2;
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                float2 m = __half22float2(__ldg(mp + i));
+                o[i] = q2_dequant((float)((__ldg(cp + 8 * i) >> sh) & 3), m.x, m.y);
+            }
+        }
+    }
+};
+
+struct DecodeParams {
+    KvLayerView kv;
+    const float* q;
+    float* out;        // final output (n_split == 1 and !want_partial) ...
+    float* work;       // ... else partials [row][n_split][hd+2], m in log2 units
+    const int* attend_len;
+    const int2* ring;
+    int n_q, num_heads, n_chunks, slot_begin, slot_end, want_partial, range_max, causal_q;
+};
+
+__device__ __forceinline__ SeqKv seq_view(const DecodeParams& p, int b, int n_q) {
+    SeqKv s;
+#pragma unroll
+    for (int i = 0; i < FLARE_PLANE_COUNT; i++) s.p[i] = p.kv.plane[i] ? p.kv.plane[i] + (size_t)b * p.kv.stride[i] : nullptr;
+    s.max_seq = p.kv.max_seq_len;
+    s.kv_dim = p.kv.kv_dim;
+    int2 r = p.ring[b];
+    s.position = r.x;
+    s.length = r.y;
+    s.newest = (r.x + n_q - 1) % s.max_seq;
+    return s;
+}
+
+template <int DT, int TPS, int GC>
+__global__ void __launch_bounds__(128) decode_splitkv_kernel(DecodeParams p) {
+    constexpr int HD = TPS * 8;
+    constexpr int SPW = 32 / TPS;           // slots per warp per iteration
+    const int split = blockIdx.x, n_split = gridDim.x;
+    const int kvh = blockIdx.y / p.n_chunks, chunk = blockIdx.y % p.n_chunks;
+    const int b = blockIdx.z / p.n_q, qi = blockIdx.z % p.n_q;
+    const int G = p.num_heads / p.kv.num_kv_heads;
+    const int h0 = kvh * G + chunk * GC;
+    const int heads_here = min(GC, G - chunk * GC);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int sub = lane / TPS, cl = lane % TPS;
+    const int c0 = kvh * HD + cl * 8;
+
+    const SeqKv s = seq_view(p, b, p.n_q);
+    int n = p.attend_len[b] - (p.causal_q ? (p.n_q - 1 - qi) : 0);
+    int lo = 0, hi = n;
+    if (p.slot_end >= 0) { lo = max(lo, p.slot_begin); hi = min(hi, p.slot_end); }
+    const int base = p.slot_end >= 0 ? p.slot_begin : 0;
+    const int per = (p.range_max + n_split - 1) / n_split;
+    const int s0 = max(lo, base + split * per);
+    const int s1 = min(hi, base + (split + 1) * per);
+
+    const float scale_log2 = rsqrtf((float)HD) * kLog2e;
+    float q[GC][8], o[GC][8], m[GC], l[GC];
+    const size_t row0 = ((size_t)b * p.n_q + qi) * p.num_heads;
+#pragma unroll
+    for (int g = 0; g < GC; g++) {
+        m[g] = -CUDART_INF_F;
+        l[g] = 0.0f;
+        const float* qp = p.q + (row0 + h0 + (g < heads_here ? g : 0)) * HD + cl * 8;
+#pragma unroll
+        for (int i = 0; i < 8; i++) { q[g][i] = qp[i] * scale_log2; o[g][i] = 0.0f; }
+    }
+
+    // the loop bound is the same for every lane of a warp, so the shuffles stay convergent;
+    // a lane group whose slot falls past the end computes on zeros and skips the update.
+    for (int tb = s0 + warp * SPW; tb < s1; tb += 4 * SPW) {
+        const int t = tb + sub;
+        const bool valid = t < s1;
+        float k[8], v[8];
+        if (valid) {
+            Row<DT, false>::load8(s, t, c0, k);
+            Row<DT, true>::load8(s, t, c0, v);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; i++) { k[i] = 0.0f; v[i] = 0.0f; }
+        }
+#pragma unroll
+        for (int g = 0; g < GC; g++) {
+            float d = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; i++) d = fmaf(q[g][i], k[i], d);
+#pragma unroll
+            for (int off = 1; off < TPS; off <<= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
+            if (valid) {
+                float mn = fmaxf(m[g], d);
+                float a = fast_exp2(m[g] - mn), w = fast_exp2(d - mn);
+                l[g] = l[g] * a + w;
+#pragma unroll
+                for (int i = 0; i < 8; i++) o[g][i] = o[g][i] * a + w * v[i];
+                m[g] = mn;
+            }
+        }
+    }
+
+    // combine the SPW lane groups of this warp
+#pragma unroll
+    for (int off = TPS; off < 32; off <<= 1) {
+#pragma unroll
+        for (int g = 0; g < GC; g++) {
+            float m2 = __shfl_xor_sync(0xffffffffu, m[g], off);
+            float l2 = __shfl_xor_sync(0xffffffffu, l[g], off);
+            float mn = fmaxf(m[g], m2);
+            float a1 = (m[g] == -CUDART_INF_F) ? 0.0f : fast_exp2(m[g] - mn);
+            float a2 = (m2 == -CUDART_INF_F) ? 0.0f : fast_exp2(m2 - mn);
+            l[g] = l[g] * a1 + l2 * a2;
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                float o2 = __shfl_xor_sync(0xffffffffu, o[g][i], off);
+                o[g][i] = o[g][i] * a1 + o2 * a2;
+            }
+            m[g] = mn;
+        }
+    }
+    __shared__ float sm_o[4][GC][HD];
+    __shared__ float sm_m[4][GC], sm_l[4][GC];
+    if (sub == 0) {
+#pragma unroll
+        for (int g = 0; g < GC; g++) {
+#pragma unroll
+            for (int i = 0; i < 8; i++) sm_o[warp][g][cl * 8 + i] = o[g][i];
+            if (cl == 0) { sm_m[warp][g] = m[g]; sm_l[warp][g] = l[g]; }
+        }
+    }
+    __syncthreads();
+    const bool final_out = (n_split == 1) && !p.want_partial;
+    for (int t = threadIdx.x; t < heads_here * HD; t += 128) {
+        int g = t / HD, d = t % HD;
+        float mm = fmaxf(fmaxf(sm_m[0][g], sm_m[1][g]), fmaxf(sm_m[2][g], sm_m[3][g]));
+        float acc = 0.0f, ll = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 4; w++) {
+            float a = (sm_m[w][g] == -CUDART_INF_F) ? 0.0f : fast_exp2(sm_m[w][g] - mm);
+            acc += sm_o[w][g][d] * a;
+            ll += sm_l[w][g] * a;
+        }
+        size_t row = row0 + h0 + g;
+        if (final_out) {
+            p.out[row * HD + d] = ll > 0.0f ? acc / ll : 0.0f;
+        } else {
+            float* w = p.work + (row * n_split + split) * (HD + 2);
+            w[2 + d] = acc;
+            if (d == 0) { w[0] = mm; w[1] = ll; }
+        }
+    }
+}
+
+// Any head_dim / any group size, f32 cache only: one warp per (sequence, query, head), lanes
+// stride over channels.  Slow; exists so that the trait's shapes (head_dim 1, 2, 3, 4 ...
+// flare-core/src/model.rs:10427-10435) run on the device as well.
+__global__ void decode_f32_anyshape_kernel(DecodeParams p) {
+    const int hd = p.kv.head_dim;
+    const int h = blockIdx.x, b = blockIdx.z / p.n_q, qi = blockIdx.z % p.n_q;
+    const int lane = threadIdx.x;
+    const int kvh = h / (p.num_heads / p.kv.num_kv_heads);
+    int n = p.attend_len[b] - (p.causal_q ? (p.n_q - 1 - qi) : 0);
+    int lo = 0, hi = n;
+    if (p.slot_end >= 0) { lo = max(lo, p.slot_begin); hi = min(hi, p.slot_end); }
+    const float* K = reinterpret_cast<const float*>(p.kv.plane[FLARE_PLANE_K] + (size_t)b * p.kv.stride[FLARE_PLANE_K]);
+    const float* V = reinterpret_cast<const float*>(p.kv.plane[FLARE_PLANE_V] + (size_t)b * p.kv.stride[FLARE_PLANE_V]);
+    const size_t row = ((size_t)b * p.n_q + qi) * p.num_heads + h;
+    const float* q = p.q + row * hd;
+    const float scale_log2 = rsqrtf((float)hd) * kLog2e;
+    constexpr int MAXD = 8;   // head_dim <= 256
+    float o[MAXD], qq[MAXD];
+#pragma unroll
+    for (int i = 0; i < MAXD; i++) { o[i] = 0.0f; int d = lane + 32 * i; qq[i] = d < hd ? q[d] * scale_log2 : 0.0f; }
+    float m = -CUDART_INF_F, l = 0.0f;
+    for (int t = lo; t < hi; t++) {
+        const float* kr = K + (size_t)t * p.kv.kv_dim + kvh * hd;
+        const float* vr = V + (size_t)t * p.kv.kv_dim + kvh * hd;
+        float d = 0.0f;
+#pragma unroll
+        for (int i = 0; i < MAXD; i++) { int c = lane + 32 * i; if (c < hd) d = fmaf(qq[i], kr[c], d); }
+#pragma unroll
+        for (int off = 16; off; off >>= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
+        float mn = fmaxf(m, d);
+        float a = fast_exp2(m - mn), w = fast_exp2(d - mn);
+        l = l * a + w;
+#pragma unroll
+        for (int i = 0; i < MAXD; i++) { int c = lane + 32 * i; if (c < hd) o[i] = o[i] * a + w * vr[c]; }
+        m = mn;
+    }
+#pragma unroll
+    for (int i = 0; i < MAXD; i++) {
+        int c = lane + 32 * i;
+        if (c >= hd) continue;
+        if (p.want_partial) p.out[row * (hd + 2) + 2 + c] = o[i];
+        else p.out[row * hd + c] = l > 0.0f ? o[i] / l : 0.0f;
+    }
+    if (p.want_partial && lane == 0) { p.out[row * (hd + 2)] = m * kLn2; p.out[row * (hd + 2) + 1] = l; }
+}
+
+// Log-sum-exp merge of n_parts partials per row.  in_log2: the stored max is in log2 units
+// (the split kernel's workspace); otherwise natural units (partials exchanged between GPUs).
+__global__ void merge_partials_kernel(const float* __restrict__ parts, size_t part_stride, size_t row_stride,
+                                      int n_parts, int hd, float* __restrict__ out, int in_log2,
+                                      int want_partial) {
+    const int row = blockIdx.x;
+    const float* base = parts + (size_t)row * row_stride;
+    const float unit = in_log2 ? 1.0f : kLog2e;
+    float mm = -CUDART_INF_F;
+    for (int r = 0; r < n_parts; r++) {
+        const float* pr = base + r * part_stride;
+        if (pr[1] > 0.0f) mm = fmaxf(mm, pr[0] * unit);
+    }
+    float ll = 0.0f;
+    for (int r = 0; r < n_parts; r++) {
+        const float* pr = base + r * part_stride;
+        if (pr[1] > 0.0f) ll += pr[1] * fast_exp2(pr[0] * unit - mm);
+    }
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+        float acc = 0.0f;
+        for (int r = 0; r < n_parts; r++) {
+            const float* pr = base + r * part_stride;
+            if (pr[1] > 0.0f) acc += pr[2 + d] * fast_exp2(pr[0] * unit - mm);
+        }
+        if (want_partial) out[(size_t)row * (hd + 2) + 2 + d] = acc;
+        else out[(size_t)row * hd + d] = ll > 0.0f ? acc / ll : 0.0f;
+    }
+    if (want_partial && threadIdx.x == 0) {
+        out[(size_t)row * (hd + 2)] = mm * kLn2;
+        out[(size_t)row * (hd + 2) + 1] = ll;
+    }
+}
+
+template <int DT, int TPS>
+void launch_gc(int gc, dim3 grid, cudaStream_t st, const DecodeParams& p) {
+    switch (gc) {
+        case 1: decode_splitkv_kernel<DT, TPS, 1><<<grid, 128, 0, st>>>(p); break;
+        case 2: decode_splitkv_kernel<DT, TPS, 2><<<grid, 128, 0, st>>>(p); break;
+        case 3: decode_splitkv_kernel<DT, TPS, 3><<<grid, 128, 0, st>>>(p); break;
+        default: decode_splitkv_kernel<DT, TPS, 4><<<grid, 128, 0, st>>>(p); break;
+    }
+}
+template <int DT>
+bool launch_tps(int hd, int gc, dim3 grid, cudaStream_t st, const DecodeParams& p) {
+    switch (hd) {
+        case 64: launch_gc<DT, 8>(gc, grid, st, p); return true;
+        case 128: launch_gc<DT, 16>(gc, grid, st, p); return true;
+        default: return false;
+    }
+}
+bool launch_f32_small(int hd, int gc, dim3 grid, cudaStream_t st, const DecodeParams& p) {
+    switch (hd) {
+        case 32: launch_gc<FLARE_KV_F32, 4>(gc, grid, st, p); return true;
+        case 256: launch_gc<FLARE_KV_F32, 32>(gc, grid, st, p); return true;
+        default: return false;
+    }
+}
+
+}  // namespace
+
+int flare_launch_merge(flare_attn_ctx* ctx, const float* partials, size_t part_stride_floats, int n_parts,
+                       int rows, int head_dim, float* out, int want_partial) {
+    if (rows <= 0) return FLARE_OK;
+    int threads = head_dim < 128 ? ((head_dim + 31) / 32) * 32 : 128;
+    merge_partials_kernel<<<rows, threads, 0, ctx->stream>>>(partials, part_stride_floats, (size_t)(head_dim + 2),
+                                                             n_parts, head_dim, out, 0, want_partial);
+    FLARE_LAUNCH_CHECK(ctx);
+    return FLARE_OK;
+}
+
+int flare_launch_decode_generic(flare_attn_ctx* ctx, const DecodeArgs& a) {
+    const int hd = a.kv.head_dim, nkv = a.kv.num_kv_heads;
+    const int G = a.num_heads / nkv;
+    const int rows = a.batch * a.n_q * a.num_heads;
+    if (rows == 0) return FLARE_OK;
+    DecodeParams p;
+    p.kv = a.kv; p.q = a.q; p.out = a.out; p.work = nullptr;
+    p.attend_len = a.attend_len; p.ring = a.ring;
+    p.n_q = a.n_q; p.num_heads = a.num_heads;
+    p.slot_begin = a.slot_begin; p.slot_end = a.slot_end; p.want_partial = a.want_partial; p.causal_q = a.causal_q;
+    p.range_max = a.slot_end >= 0 ? (a.slot_end - a.slot_begin) : a.max_attend;
+    if (p.range_max < 0) p.range_max = 0;
+
+    const bool fast_hd = (hd == 64 || hd == 128) || (a.kv.dtype == FLARE_KV_F32 && (hd == 32 || hd == 256));
+    if (!fast_hd) {
+        if (a.kv.dtype != FLARE_KV_F32 || hd > 256)
+            return flare_set_error(ctx, FLARE_ERR_UNSUPPORTED, "head_dim %d is not supported for this cache format", hd);
+        p.n_chunks = 1;
+        dim3 grid(a.num_heads, 1, a.batch * a.n_q);
+        decode_f32_anyshape_kernel<<<grid, 32, 0, ctx->stream>>>(p);
+        FLARE_LAUNCH_CHECK(ctx);
+        return FLARE_OK;
+    }
+    const int gc = G >= 4 ? 4 : G;
+    p.n_chunks = (G + gc - 1) / gc;
+    // enough CTAs to fill the machine several times over, but at least 256 slots per CTA
+    const int units = a.batch * a.n_q * nkv * p.n_chunks;
+    int want = (ctx->sm_count * 8 + units - 1) / units;
+    int max_split = (p.range_max + 255) / 256;
+    int n_split = want < max_split ? want : max_split;
+    if (n_split < 1) n_split = 1;
+    if (n_split > 256) n_split = 256;
+    if (n_split > 1 || a.want_partial) {
+        size_t need = (size_t)rows * n_split * (hd + 2) * sizeof(float);
+        FLARE_TRY(flare_ensure(ctx, &ctx->d_work, &ctx->work_bytes, need));
+        p.work = (float*)ctx->d_work;
+    }
+    dim3 grid(n_split, nkv * p.n_chunks, a.batch * a.n_q);
+    bool ok = false;
+    switch (a.kv.dtype) {
+        case FLARE_KV_F32:
+            ok = launch_tps<FLARE_KV_F32>(hd, gc, grid, ctx->stream, p) || launch_f32_small(hd, gc, grid, ctx->stream, p);
+            break;
+        case FLARE_KV_Q8_0: ok = launch_tps<FLARE_KV_Q8_0>(hd, gc, grid, ctx->stream, p); break;
+        case FLARE_KV_KIVI_REF: ok = launch_tps<FLARE_KV_KIVI_REF>(hd, gc, grid, ctx->stream, p); break;
+        case FLARE_KV_KIVI_G32: ok = launch_tps<FLARE_KV_KIVI_G32>(hd, gc, grid, ctx->stream, p); break;
+    }
+    if (!ok) return flare_set_error(ctx, FLARE_ERR_UNSUPPORTED, "no decode kernel for dtype %d head_dim %d", a.kv.dtype, hd);
+    FLARE_LAUNCH_CHECK(ctx);
+    if (n_split > 1 || a.want_partial) {
+        int threads = hd < 128 ? hd : 128;
+        merge_partials_kernel<<<rows, threads, 0, ctx->stream>>>(p.work, (size_t)(hd + 2), (size_t)n_split * (hd + 2),
+                                                                 n_split, hd, a.out, 1, a.want_partial);
+        FLARE_LAUNCH_CHECK(ctx);
+    }
+    return FLARE_OK;
+}

@@ -1,0 +1,247 @@
+/*
+ * flare_attn.h — C ABI of the B200 attention engine for Flare.
+ *
+ * This is the boundary a Rust crate `flare-cuda` (beside flare-gpu) binds with
+ * `extern "C"`; it replaces the attention / KV-cache hooks of flare-core's
+ * `ComputeBackend` trait (flare-core/src/model.rs:176-618) and the attention / KV
+ * shaders of flare-gpu.  Paths in comments are relative to the reference project.
+ *
+ * Conventions
+ *  - every function returns a flare_status (0 = OK); nothing aborts or throws;
+ *    flare_attn_last_error() gives the text of the last failure on a context.
+ *  - one context = one CUDA device + one stream.  Calls on one context must be
+ *    serialised by the caller (the Rust side keeps it behind a Mutex, as
+ *    flare-gpu/src/backend.rs:183-188 does for its own state).
+ *  - a pointer argument is host memory unless the function has an `on_device`
+ *    flag and it is non-zero; host buffers are fully consumed / produced before
+ *    the call returns, device buffers are used asynchronously on the context's
+ *    stream and must stay alive until flare_attn_sync().
+ *  - there is no CPU fallback: without a CUDA device every call fails with
+ *    FLARE_ERR_CUDA.
+ *
+ * Layouts (row-major, last index fastest)
+ *  - q   [batch][n_q][num_heads][head_dim]            f32
+ *  - out [batch][n_q][num_heads][head_dim]            f32
+ *  - a K or V row is [num_kv_heads][head_dim] = kv_dim values, exactly the row of
+ *    flare-core's KvCache tensor [max_seq_len, num_kv_heads, head_dim]
+ *    (flare-core/src/kv_cache.rs:431-446); a ring slot is position % max_seq_len.
+ *  - query head h reads kv head h / (num_heads / num_kv_heads)
+ *    (flare-core/src/model.rs:9877-9882).
+ */
+#ifndef FLARE_ATTN_H
+#define FLARE_ATTN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define FLARE_API
+#else
+#define FLARE_API __attribute__((visibility("default")))
+#endif
+
+typedef struct flare_attn_ctx flare_attn_ctx;
+typedef struct flare_kv flare_kv;
+
+typedef enum {
+    FLARE_OK = 0,
+    FLARE_ERR_INVALID_ARG = 1,
+    FLARE_ERR_UNSUPPORTED = 2,   /* softcap != 0 on the GPU path, head_dim outside the kernels' range ... */
+    FLARE_ERR_OOM = 3,
+    FLARE_ERR_CUDA = 4,
+    FLARE_ERR_TIMEOUT = 5,
+    FLARE_ERR_STATE = 6          /* e.g. attention before any KV cache exists */
+} flare_status;
+
+/* How a cache stores its rows. */
+typedef enum {
+    FLARE_KV_F32 = 0,       /* flare-core KvCache: f32 rows (kv_cache.rs:431-546) */
+    FLARE_KV_Q8_0 = 1,      /* Q8_0 codec (flare-loader/src/quantize.rs:188-197): 32 int8 + one f16 scale */
+    FLARE_KV_KIVI_REF = 2,  /* flare-core QuantizedKvCache, bit for bit (kv_cache.rs:35-420) */
+    FLARE_KV_KIVI_G32 = 3   /* 2-bit, groups of 32, f16 scale+zero, 128-token f16 residual ring */
+} flare_kv_dtype;
+
+typedef enum { FLARE_DT_F32 = 0, FLARE_DT_BF16 = 1 } flare_dtype;
+
+/* Raw planes of a cache, for flare_kv_export_plane / flare_kv_import_plane.
+ * Sizes are per (layer, sequence); kv_dim = num_kv_heads * head_dim.
+ *   F32       K, V                 f32  [max_seq][kv_dim]
+ *   Q8_0      K_Q, V_Q             i8   [max_seq][kv_dim]
+ *             K_SCALE, V_SCALE     f16  [max_seq][kv_dim/32]
+ *   KIVI_REF  K_Q, V_Q             u8   [max_seq][kv_dim/4]     (kv_cache.rs:27-29)
+ *             K_SCALE, K_MIN       f32  [kv_dim]                 running per-channel stats
+ *             V_SCALE, V_MIN       f32  [max_seq]                per-token
+ *             K_RES, V_RES         f32  [32][kv_dim]             residual window
+ *   KIVI_G32  K_Q                  u8   [max_seq/32][kv_dim][8]  byte j holds slots 4j..4j+3 of the group
+ *             K_SCALE              f16x2 [max_seq/32][kv_dim]    (scale, zero)
+ *             V_Q                  u8   [max_seq][kv_dim/4]
+ *             V_SCALE              f16x2 [max_seq][kv_dim/32]    (scale, zero)
+ *             K_RES, V_RES         f16  [128][kv_dim]            residual ring, slot % 128
+ */
+typedef enum {
+    FLARE_PLANE_K = 0, FLARE_PLANE_V = 1,
+    FLARE_PLANE_K_Q = 2, FLARE_PLANE_V_Q = 3,
+    FLARE_PLANE_K_SCALE = 4, FLARE_PLANE_V_SCALE = 5,
+    FLARE_PLANE_K_MIN = 6, FLARE_PLANE_V_MIN = 7,
+    FLARE_PLANE_K_RES = 8, FLARE_PLANE_V_RES = 9,
+    FLARE_PLANE_COUNT = 10
+} flare_kv_plane;
+
+/* ---------------------------------------------------------------- context */
+
+/* Replaces WebGpuBackend::new (flare-gpu/src/backend.rs:219-228): binds CUDA device
+ * `device` and creates the stream all work of this context runs on. */
+FLARE_API int flare_attn_create(int device, flare_attn_ctx** out_ctx);
+FLARE_API int flare_attn_destroy(flare_attn_ctx* ctx);
+/* Run on a caller-owned cudaStream_t instead (NULL restores the context's own). */
+FLARE_API int flare_attn_set_stream(flare_attn_ctx* ctx, void* cuda_stream);
+/* Replaces the blocking readback device.poll(Maintain::Wait) (flare-gpu/src/backend.rs:417). */
+FLARE_API int flare_attn_sync(flare_attn_ctx* ctx);
+FLARE_API const char* flare_attn_last_error(const flare_attn_ctx* ctx);
+/* Kernels launched by this context so far (replaces nothing; for measurement). */
+FLARE_API uint64_t flare_attn_launch_count(const flare_attn_ctx* ctx);
+/* ComputeBackend::name (flare-core/src/model.rs:615-617): "cuda". */
+FLARE_API const char* flare_attn_backend_name(void);
+
+/* ---------------------------------------------------------------- KV cache */
+
+/* Replaces KvCache::new / QuantizedKvCache::new / GpuKvCache::new
+ * (flare-core/src/kv_cache.rs:448-473, 62-114; flare-gpu/src/kv_cache.rs:16-98) with a
+ * batch dimension: `batch` independent sequences, each with its own ring state.
+ * Q8_0 and KIVI_G32 need head_dim % 32 == 0; KIVI_G32 needs max_seq_len % 128 == 0;
+ * KIVI_REF needs kv_dim % 4 == 0. */
+FLARE_API int flare_kv_alloc(flare_attn_ctx* ctx, int num_layers, int batch, int max_seq_len,
+                             int num_kv_heads, int head_dim, int kv_dtype, flare_kv** out_kv);
+FLARE_API int flare_kv_free(flare_kv* kv);
+
+/* Replaces KvCache::write + ComputeBackend::gpu_kv_write (flare-core/src/kv_cache.rs:475-481,
+ * model.rs:287-296; GpuKvCache::write flare-gpu/src/kv_cache.rs:116-160): store the post-RoPE
+ * row of one token of sequence `seq` at ring slot abs_position % max_seq_len of `layer`.
+ * Quantised caches quantise on the device (QuantizedKvCache::write, kv_cache.rs:121-162).
+ * The ring state is NOT advanced (flare_kv_advance does that once per token, after all
+ * layers, as model.rs:2547 does). */
+FLARE_API int flare_kv_write_f32(flare_kv* kv, int layer, int seq, int64_t abs_position,
+                                 const float* key, const float* value, int on_device);
+
+/* n_rows consecutive tokens, as if written and advanced one by one starting from the
+ * current state of `seq` (replaces the bulk write after prefill, model.rs:2956-2979).
+ * key/value are [n_rows][kv_dim].  Does not advance; call flare_kv_advance(kv, seq, n_rows)
+ * after every layer has been written. */
+FLARE_API int flare_kv_append_f32(flare_kv* kv, int layer, int seq, int n_rows,
+                                  const float* key, const float* value, int on_device);
+
+/* One decode step of the whole batch: row b of key/value ([batch][kv_dim]) is the new token
+ * of sequence b and goes to that sequence's current ring position (the batched form of the
+ * gpu_kv_write call at model.rs:2199-2206).  Does not advance. */
+FLARE_API int flare_kv_write_step_f32(flare_kv* kv, int layer, const float* key, const float* value,
+                                      int on_device);
+
+/* KvCache::advance (kv_cache.rs:484-489) applied n times; seq < 0 = every sequence. */
+FLARE_API int flare_kv_advance(flare_kv* kv, int seq, int n);
+/* KvCache::len / position (kv_cache.rs:502-513). */
+FLARE_API int flare_kv_get_state(const flare_kv* kv, int seq, int64_t* position, int64_t* length);
+/* Restore a state previously read with flare_kv_get_state (checkpoint / resume). */
+FLARE_API int flare_kv_set_state(flare_kv* kv, int seq, int64_t position, int64_t length);
+/* KvCache::truncate_to (kv_cache.rs:521-531): ignored once the ring has wrapped. */
+FLARE_API int flare_kv_truncate(flare_kv* kv, int seq, int64_t target_len);
+/* KvCache::clear (kv_cache.rs:534-545): zero-fill and reset; seq < 0 = every sequence. */
+FLARE_API int flare_kv_clear(flare_kv* kv, int seq);
+
+/* Byte size of one plane for one (layer, sequence); 0 if the cache has no such plane. */
+FLARE_API size_t flare_kv_plane_bytes(const flare_kv* kv, int plane);
+FLARE_API int flare_kv_export_plane(flare_kv* kv, int layer, int seq, int plane, void* dst,
+                                    size_t bytes, int on_device);
+FLARE_API int flare_kv_import_plane(flare_kv* kv, int layer, int seq, int plane, const void* src,
+                                    size_t bytes, int on_device);
+/* Q8_0 rows as the GGUF block stream [n_slots][kv_dim/32] x 34 bytes (f16 LE scale, 32 i8),
+ * the format of flare-loader/src/quantize.rs:188-197. */
+FLARE_API int flare_kv_import_q8_0_blocks(flare_kv* kv, int layer, int seq, int first_slot, int n_slots,
+                                          const void* k_blocks, const void* v_blocks, int on_device);
+FLARE_API int flare_kv_export_q8_0_blocks(flare_kv* kv, int layer, int seq, int first_slot, int n_slots,
+                                          void* k_blocks, void* v_blocks, int on_device);
+
+/* The f32 view attention reads: [max_seq_len][kv_dim] indexed by ring slot, computed with
+ * the literal reference formulae so that it is bit-identical to the CPU:
+ *   Q8_0      (i8 as f32) * f16_to_f32(scale)             (quantize.rs:188-197)
+ *   KIVI_REF  QuantizedKvCache::dequant_keys/_values        (kv_cache.rs:189-250, 374-391)
+ *   KIVI_G32  code * scale + zero, residual ring for the newest 128 tokens
+ * Either output may be NULL. */
+FLARE_API int flare_kv_export_dequant(flare_kv* kv, int layer, int seq, float* k_out, float* v_out,
+                                      int on_device);
+
+/* ---------------------------------------------------------------- attention */
+
+/* Replaces ComputeBackend::grouped_query_attention_from_gpu_cache (model.rs:311-322;
+ * flare-gpu/src/backend.rs:4885-4979) and the CPU routine it stands for
+ * (cpu_grouped_query_attention_into, model.rs:9849-9905), for `batch` sequences and
+ * n_q causally ordered queries per sequence (n_q = 1: plain decode; n_q = 1 + drafts:
+ * speculative verify, flare-core/src/generate.rs:258-303 done in one call).
+ *   attend_len[b]  slots 0..attend_len[b]-1 of sequence b are read by the LAST query;
+ *                  query i reads attend_len[b] - (n_q-1-i) slots.  NULL = ring state:
+ *                  min(length + 1, max_seq_len)  (model.rs:2209; clamped once the ring is full).
+ *   softcap        must be 0 (the wgpu backend asserts the same, backend.rs:4907-4910).
+ * K/V are streamed once per kv head for all query heads that share it. */
+FLARE_API int flare_decode_attn(flare_attn_ctx* ctx, flare_kv* kv, int layer, int num_heads,
+                                const float* q, int n_q, const int* attend_len, float softcap,
+                                float* out, int on_device);
+
+/* Split-KV building blocks for one sequence spread over several GPUs (no counterpart in
+ * the reference, which is single-device).  Attends slots [slot_begin, slot_end) only and
+ * returns, per (sequence, query, head), [m, l, o[head_dim]] with o unnormalised:
+ * partial is [batch][n_q][num_heads][head_dim + 2]. */
+FLARE_API int flare_decode_attn_partial(flare_attn_ctx* ctx, flare_kv* kv, int layer, int num_heads,
+                                        const float* q, int n_q, int slot_begin, int slot_end,
+                                        float* partial, int on_device);
+/* Log-sum-exp merge of n_parts partials, each [rows][head_dim + 2], into out [rows][head_dim]. */
+FLARE_API int flare_merge_partials(flare_attn_ctx* ctx, const float* partials, int n_parts, int rows,
+                                   int head_dim, float* out, int on_device);
+
+/* Replaces ComputeBackend::grouped_query_attention (model.rs:246-267;
+ * flare-gpu/src/backend.rs:4701-4811): K/V given as host f32 [seq_len][kv_dim]. */
+FLARE_API int flare_gqa_attention_host(flare_attn_ctx* ctx, const float* q, const float* k_cache,
+                                       const float* v_cache, int num_heads, int num_kv_heads,
+                                       int head_dim, int seq_len, float softcap, float* out);
+
+/* Replaces ComputeBackend::prefill_attention_gpu (model.rs:336-368;
+ * flare-gpu/src/backend.rs:4981-5022, 2461-2533): causal self-attention of `batch`
+ * prompts of seq_len tokens; row t attends rows max(0, t-window+1)..=t (window 0 = all).
+ * q [batch][seq_len][num_heads][head_dim]; k, v [batch][seq_len][num_kv_heads][head_dim];
+ * in_dtype / out_dtype are flare_dtype.  f32 inputs are rounded to bf16 for the tensor cores,
+ * accumulation is f32. */
+FLARE_API int flare_prefill_attn(flare_attn_ctx* ctx, const void* q, const void* k, const void* v,
+                                 int in_dtype, int batch, int seq_len, int num_heads, int num_kv_heads,
+                                 int head_dim, int window, float softcap, void* out, int out_dtype,
+                                 int on_device);
+
+/* ---------------------------------------------------------------- trait-shaped shims
+ * The exact ComputeBackend attention hooks, batch 1, host f32 in and out. */
+
+/* ComputeBackend::init_gpu_kv_cache (model.rs:274-281): f32 cache owned by the context. */
+FLARE_API int flare_backend_init_gpu_kv_cache(flare_attn_ctx* ctx, int num_layers, int max_seq_len,
+                                              int num_kv_heads, int head_dim);
+/* Same, choosing the storage (no counterpart: the trait has no quantised-cache notion). */
+FLARE_API int flare_backend_init_gpu_kv_cache_dtype(flare_attn_ctx* ctx, int num_layers, int max_seq_len,
+                                                    int num_kv_heads, int head_dim, int kv_dtype);
+/* ComputeBackend::gpu_kv_write (model.rs:287-296). */
+FLARE_API int flare_backend_gpu_kv_write(flare_attn_ctx* ctx, int layer, int64_t position,
+                                         int num_kv_heads, int head_dim, const float* key,
+                                         const float* value);
+/* ComputeBackend::has_gpu_kv_cache (model.rs:299-301): 1 or 0. */
+FLARE_API int flare_backend_has_gpu_kv_cache(const flare_attn_ctx* ctx);
+/* ComputeBackend::grouped_query_attention_from_gpu_cache (model.rs:311-322): attends ring
+ * slots 0..seq_len-1 (seq_len is clamped to max_seq_len). */
+FLARE_API int flare_backend_gqa_from_gpu_cache(flare_attn_ctx* ctx, const float* q, int layer,
+                                               int num_heads, int num_kv_heads, int head_dim,
+                                               int seq_len, float softcap, float* out);
+/* The context-owned cache, e.g. to advance or truncate it (Model::truncate_kv_cache,
+ * model.rs:4835-4840); NULL before init. */
+FLARE_API flare_kv* flare_backend_kv(flare_attn_ctx* ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLARE_ATTN_H */
