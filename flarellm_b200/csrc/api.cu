@@ -413,8 +413,9 @@ static int upload_small(flare_attn_ctx* ctx, const flare_kv* kv, int n_q, const 
     size_t off = (size_t)slot * slot_bytes;
     if (!ctx->small_events[slot]) FLARE_CUDA_OK(ctx, cudaEventCreateWithFlags(&ctx->small_events[slot], cudaEventDisableTiming));
     else FLARE_CUDA_OK(ctx, cudaEventSynchronize(ctx->small_events[slot]));   // the copy that last used this slot is done
-    int* h_att = (int*)((char*)ctx->h_pinned + off);
-    int2* h_ring = (int2*)(h_att + B);
+    // the 8-byte ring records come first so that both arrays are naturally aligned
+    int2* h_ring = (int2*)((char*)ctx->h_pinned + off);
+    int* h_att = (int*)(h_ring + B);
     int mx = 0;
     for (int b = 0; b < B; b++) {
         int64_t a;
@@ -427,10 +428,10 @@ static int upload_small(flare_attn_ctx* ctx, const flare_kv* kv, int n_q, const 
         h_ring[b] = make_int2((int)kv->position[b], (int)kv->length[b]);
     }
     char* d = (char*)ctx->d_misc + off;
-    FLARE_CUDA_OK(ctx, cudaMemcpyAsync(d, h_att, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    FLARE_CUDA_OK(ctx, cudaMemcpyAsync(d, h_ring, bytes, cudaMemcpyHostToDevice, ctx->stream));
     FLARE_CUDA_OK(ctx, cudaEventRecord(ctx->small_events[slot], ctx->stream));
-    *d_attend = (const int*)d;
-    *d_ring = (const int2*)(d + (size_t)B * sizeof(int));
+    *d_ring = (const int2*)d;
+    *d_attend = (const int*)(d + (size_t)B * sizeof(int2));
     *max_attend = mx;
     return FLARE_OK;
 }
