@@ -55,6 +55,8 @@ SYMBOLS = [
     ("flare_kv_export_q8_0_blocks", _i, [_vp, _i, _i, _i, _i, _vp, _vp, _i]),
     ("flare_kv_export_dequant", _i, [_vp, _i, _i, _vp, _vp, _i]),
     ("flare_decode_attn", _i, [_vp, _vp, _i, _i, _vp, _i, _ip, _f, _vp, _i]),
+    ("flare_decode_attn_noalloc", _i, [_vp, _vp, _i, _i, _vp, _i, _ip, _vp]),
+    ("flare_decode_attn_noalloc_scratch_bytes", _sz, []),
     ("flare_decode_attn_partial", _i, [_vp, _vp, _i, _i, _vp, _i, _i, _i, _vp, _i]),
     ("flare_merge_partials", _i, [_vp, _vp, _i, _i, _i, _vp, _i]),
     ("flare_gqa_attention_host", _i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _vp]),
@@ -160,6 +162,16 @@ class Engine:
         self.check(self.L.flare_decode_attn(self.h, kv.h, layer, num_heads, _ptr(q), n_q, al, softcap, _ptr(out),
                                             int(on_device)))
         return out
+
+    def decode_noalloc(self, kv: "KvCache", layer, num_heads, q_dev: int, out_dev: int, n_q=1, attend_len=None):
+        """flare_decode_attn_noalloc: device pointers in and out, workspace inside the library,
+        no device allocation during the call."""
+        al = None
+        if attend_len is not None:
+            al_arr = np.ascontiguousarray(attend_len, dtype=np.int32)
+            assert al_arr.size == kv.batch
+            al = al_arr.ctypes.data_as(_ip)
+        self.check(self.L.flare_decode_attn_noalloc(self.h, kv.h, layer, num_heads, int(q_dev), n_q, al, int(out_dev)))
 
     def decode_partial(self, kv, layer, num_heads, q, slot_begin, slot_end, n_q=1, out=None):
         on_device = not isinstance(q, np.ndarray)

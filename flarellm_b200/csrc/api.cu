@@ -478,6 +478,19 @@ int flare_decode_attn(flare_attn_ctx* ctx, flare_kv* kv, int layer, int num_head
     return decode_common(ctx, kv, layer, num_heads, q, n_q, attend_len, softcap, 0, -1, 0, 1, out, on_device);
 }
 
+int flare_decode_attn_noalloc(flare_attn_ctx* ctx, flare_kv* kv, int layer, int num_heads, const float* q_dev, int n_q,
+                              const int* attend_len, float* out_dev) {
+    CHECK_CTX(ctx);
+    if (!kv || kv->ctx != ctx) return flare_set_error(ctx, FLARE_ERR_STATE, "no KV cache bound to this context");
+    if (layer < 0 || layer >= kv->num_layers) return flare_set_error(ctx, FLARE_ERR_INVALID_ARG, "layer %d out of range", layer);
+    if (!q_dev || !out_dev || n_q < 1 || num_heads < 1 || num_heads % kv->num_kv_heads)
+        return flare_set_error(ctx, FLARE_ERR_INVALID_ARG, "decode: bad q/out/n_q or num_heads %d not a multiple of %d kv heads",
+                               num_heads, kv->num_kv_heads);
+    BIND(ctx);
+    return flare_decode_noalloc(ctx, kv, layer, num_heads, q_dev, n_q, attend_len, out_dev);
+}
+size_t flare_decode_attn_noalloc_scratch_bytes(void) { return flare_noalloc_scratch_bytes(); }
+
 int flare_decode_attn_partial(flare_attn_ctx* ctx, flare_kv* kv, int layer, int num_heads, const float* q, int n_q,
                               int slot_begin, int slot_end, float* partial, int on_device) {
     CHECK_CTX(ctx);

@@ -97,6 +97,9 @@ struct DecodeArgs {
 };
 int flare_launch_decode(flare_attn_ctx* ctx, const DecodeArgs& a);
 int flare_launch_decode_generic(flare_attn_ctx* ctx, const DecodeArgs& a);
+int flare_decode_noalloc(flare_attn_ctx* ctx, const flare_kv* kv, int layer, int num_heads, const float* q_dev,
+                         int n_q, const int* attend_len, float* out_dev);
+size_t flare_noalloc_scratch_bytes();
 int flare_launch_merge(flare_attn_ctx* ctx, const float* partials, size_t part_stride_floats, int n_parts,
                        int rows, int head_dim, float* out, int want_partial);
 

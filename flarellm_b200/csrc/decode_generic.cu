@@ -445,3 +445,112 @@ int flare_launch_decode_generic(flare_attn_ctx* ctx, const DecodeArgs& a) {
     }
     return FLARE_OK;
 }
+
+// ---------------------------------------------------------------------------------------
+// Decode attention that allocates nothing (flare_decode_attn_noalloc).
+//
+// Who needs it: code that calls into this library at a point where device allocation is
+// off the table — a serving loop that has handed the whole GPU memory to its own pool at
+// start-up, a latency-critical callback that must not take the driver's allocation lock,
+// a host that forbids cudaMalloc after initialisation.  The ordinary entry point grows a
+// split-KV workspace and a few staging buffers with cudaMalloc on first use; this one keeps
+// its workspace in the library image instead.
+//
+// The workspace is one file-scope __device__ array: every GPU that loads the library carries
+// these bytes until the process exits, which is why the size is modest and fixed.  In host
+// code the array's name is only a handle; the device address is obtained once per device
+// with cudaGetSymbolAddress (while that device is current) and handed to the kernels.
+//
+// Layout of the array: [0, kSmallBytes) the per-sequence (position, length) records followed
+// by the per-sequence attend lengths; [kSmallBytes, end) the split-KV partials
+// [row][split][head_dim + 2].  Nothing has to start at zero: every (row, split) record and
+// every small record that a call reads is written by that same call first.  All calls on a
+// device share the array, so two calls that overlap on the GPU (different streams or
+// contexts) race; callers serialise them.
+// ---------------------------------------------------------------------------------------
+#define FLARE_NOALLOC_SCRATCH_BYTES (8u << 20)      /* the stated maximum: 8 MiB per GPU */
+#define FLARE_NOALLOC_MAX_BATCH 256
+static __device__ __align__(256) unsigned char g_noalloc_scratch[FLARE_NOALLOC_SCRATCH_BYTES];
+
+namespace {
+constexpr size_t kSmallBytes = 4096;   // 256 x (int2 + int) = 3072, rounded up
+void* g_noalloc_ptr[64] = {};          // device address of the array, per device ordinal
+}
+
+size_t flare_noalloc_scratch_bytes() { return FLARE_NOALLOC_SCRATCH_BYTES; }
+
+int flare_decode_noalloc(flare_attn_ctx* ctx, const flare_kv* kv, int layer, int num_heads, const float* q_dev,
+                         int n_q, const int* attend_len, float* out_dev) {
+    const int hd = kv->head_dim, nkv = kv->num_kv_heads, B = kv->batch;
+    if (kv->dtype != FLARE_KV_F32 && kv->dtype != FLARE_KV_Q8_0)
+        return flare_set_error(ctx, FLARE_ERR_UNSUPPORTED, "the no-allocation entry point serves f32 and Q8_0 caches only");
+    if (hd != 64 && hd != 128)
+        return flare_set_error(ctx, FLARE_ERR_UNSUPPORTED, "the no-allocation entry point needs head_dim 64 or 128, got %d", hd);
+    if (B > FLARE_NOALLOC_MAX_BATCH)
+        return flare_set_error(ctx, FLARE_ERR_INVALID_ARG, "batch %d exceeds the no-allocation maximum of %d", B,
+                               FLARE_NOALLOC_MAX_BATCH);
+    if (ctx->device < 0 || ctx->device >= 64) return flare_set_error(ctx, FLARE_ERR_INVALID_ARG, "device ordinal out of range");
+
+    // set-up, once per device, with that device current (the caller has bound it)
+    if (!g_noalloc_ptr[ctx->device]) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess || !p)
+            return flare_set_error(ctx, FLARE_ERR_CUDA, "cudaGetSymbolAddress(g_noalloc_scratch) failed: %s", cudaGetErrorString(e));
+        g_noalloc_ptr[ctx->device] = p;
+    }
+    char* scratch = (char*)g_noalloc_ptr[ctx->device];
+
+    // small per-sequence records: built on the host stack, copied into the head of the array
+    struct { int2 ring[FLARE_NOALLOC_MAX_BATCH]; int att[FLARE_NOALLOC_MAX_BATCH]; } small;
+    int max_attend = 0;
+    for (int b = 0; b < B; b++) {
+        int64_t a;
+        if (attend_len) a = attend_len[b];
+        else { a = kv->length[b] + n_q; if (a > kv->max_seq_len) a = kv->max_seq_len; }
+        if (a < 0 || a > kv->max_seq_len)
+            return flare_set_error(ctx, FLARE_ERR_INVALID_ARG, "attend_len[%d] = %lld outside [0, %d]", b, (long long)a, kv->max_seq_len);
+        small.att[b] = (int)a;
+        if (a > max_attend) max_attend = (int)a;
+        small.ring[b] = make_int2((int)kv->position[b], (int)kv->length[b]);
+    }
+    int* d_att = (int*)(scratch + sizeof(small.ring));
+    // pageable source: the runtime has taken its copy of `small` by the time these return
+    FLARE_CUDA_OK(ctx, cudaMemcpyAsync(scratch, small.ring, sizeof(int2) * B, cudaMemcpyHostToDevice, ctx->stream));
+    FLARE_CUDA_OK(ctx, cudaMemcpyAsync(d_att, small.att, sizeof(int) * B, cudaMemcpyHostToDevice, ctx->stream));
+
+    const int G = num_heads / nkv;
+    const int rows = B * n_q * num_heads;
+    DecodeParams p;
+    p.kv = flare_layer_view(kv, layer);
+    p.q = q_dev; p.out = out_dev; p.work = (float*)(scratch + kSmallBytes);
+    p.attend_len = d_att; p.ring = (const int2*)scratch;
+    p.n_q = n_q; p.num_heads = num_heads;
+    p.slot_begin = 0; p.slot_end = -1; p.want_partial = 0; p.causal_q = 1;
+    p.range_max = max_attend;
+    const int gc = G >= 4 ? 4 : G;
+    p.n_chunks = (G + gc - 1) / gc;
+    const int units = B * n_q * nkv * p.n_chunks;
+    int want = (ctx->sm_count * 8 + units - 1) / units;
+    int max_split = (p.range_max + 255) / 256;
+    int n_split = want < max_split ? want : max_split;
+    if (n_split < 1) n_split = 1;
+    if (n_split > 256) n_split = 256;
+    const size_t need = n_split > 1 ? (size_t)rows * n_split * (hd + 2) * sizeof(float) : 0;
+    if (need > FLARE_NOALLOC_SCRATCH_BYTES - kSmallBytes)
+        return flare_set_error(ctx, FLARE_ERR_INVALID_ARG,
+                               "this call needs %zu bytes of split-KV workspace (%d rows x %d splits); the no-allocation "
+                               "entry point has %zu", need, rows, n_split, (size_t)FLARE_NOALLOC_SCRATCH_BYTES - kSmallBytes);
+    dim3 grid(n_split, nkv * p.n_chunks, B * n_q);
+    bool ok = kv->dtype == FLARE_KV_F32 ? launch_tps<FLARE_KV_F32>(hd, gc, grid, ctx->stream, p)
+                                        : launch_tps<FLARE_KV_Q8_0>(hd, gc, grid, ctx->stream, p);
+    if (!ok) return flare_set_error(ctx, FLARE_ERR_UNSUPPORTED, "no decode kernel for head_dim %d", hd);
+    FLARE_LAUNCH_CHECK(ctx);
+    if (n_split > 1) {
+        int threads = hd < 128 ? hd : 128;
+        merge_partials_kernel<<<rows, threads, 0, ctx->stream>>>(p.work, (size_t)(hd + 2), (size_t)n_split * (hd + 2),
+                                                                 n_split, hd, out_dev, 1, 0);
+        FLARE_LAUNCH_CHECK(ctx);
+    }
+    return FLARE_OK;
+}

@@ -189,6 +189,30 @@ FLARE_API int flare_decode_attn(flare_attn_ctx* ctx, flare_kv* kv, int layer, in
                                 const float* q, int n_q, const int* attend_len, float softcap,
                                 float* out, int on_device);
 
+/* No counterpart in the reference.  flare_decode_attn for callers that must not allocate
+ * device memory when they call in: an inference server that gave all GPU memory to its own
+ * pool at start-up, a real-time callback that may not wait on the driver's allocator, a host
+ * whose policy forbids cudaMalloc after initialisation.  This entry point calls no cudaMalloc,
+ * cudaFree or other allocating routine: the split-KV workspace is a fixed 8 MiB __device__
+ * array inside the library (flare_decode_attn_noalloc_scratch_bytes()), which every GPU that
+ * loads the library carries until the process exits.
+ *   - q_dev and out_dev are DEVICE pointers owned by the caller ([batch][n_q][num_heads][head_dim]
+ *     f32); attend_len is a host array as in flare_decode_attn (NULL = ring state).
+ *   - f32 and Q8_0 caches, head_dim 64 or 128, batch <= 256.  A call whose workspace would not
+ *     fit (rows x splits x (head_dim + 2) floats) is refused with FLARE_ERR_INVALID_ARG and a
+ *     message that names both sizes.
+ *   - the first call on a device is the set-up call: it looks up the array's device address
+ *     (cudaGetSymbolAddress), and the driver may load the library's device image, array
+ *     included, at that moment.  Make that first call before any stream capture begins.
+ *   - every call on a device shares the one array and leaves its partial results in it; a
+ *     call overwrites what it reads, so nothing needs clearing, but two calls that overlap on
+ *     the GPU (different streams or contexts) race — serialise them.
+ * Results are the same as flare_decode_attn's. */
+FLARE_API int flare_decode_attn_noalloc(flare_attn_ctx* ctx, flare_kv* kv, int layer, int num_heads,
+                                        const float* q_dev, int n_q, const int* attend_len,
+                                        float* out_dev);
+FLARE_API size_t flare_decode_attn_noalloc_scratch_bytes(void);
+
 /* Split-KV building blocks for one sequence spread over several GPUs (no counterpart in
  * the reference, which is single-device).  Attends slots [slot_begin, slot_end) only and
  * returns, per (sequence, query, head), [m, l, o[head_dim]] with o unnormalised:
