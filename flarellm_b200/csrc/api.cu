@@ -2,6 +2,7 @@
 // buffers, and dispatch to the kernels.  Declarations and reference citations are in
 // include/flare_attn.h.
 #include "common.cuh"
+#include "tma.cuh"
 #include <stdarg.h>
 #include <new>
 
@@ -49,7 +50,22 @@ KvLayerView flare_layer_view(const flare_kv* kv, int layer) {
     return v;
 }
 
-int flare_launch_decode(flare_attn_ctx* ctx, const DecodeArgs& a) { return flare_launch_decode_generic(ctx, a); }
+int flare_launch_decode(flare_attn_ctx* ctx, const DecodeArgs& a) {
+    if (flare_decode_q8_supported(a)) return flare_launch_decode_q8(ctx, a);
+    return flare_launch_decode_generic(ctx, a);
+}
+
+// A kernel whose bounded wait gave up leaves a status in ctx->d_err; read and clear it.
+int flare_check_device_error(flare_attn_ctx* ctx) {
+    int h = 0;
+    FLARE_CUDA_OK(ctx, cudaMemcpyAsync(&h, ctx->d_err, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+    FLARE_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
+    if (h != 0) {
+        FLARE_CUDA_OK(ctx, cudaMemsetAsync(ctx->d_err, 0, sizeof(int), ctx->stream));
+        return flare_set_error(ctx, h, "a kernel gave up waiting for its own memory copies (status %d)", h);
+    }
+    return FLARE_OK;
+}
 
 #define CHECK_CTX(ctx) do { if (!(ctx)) return FLARE_ERR_INVALID_ARG; } while (0)
 #define BIND(ctx) FLARE_CUDA_OK(ctx, cudaSetDevice((ctx)->device))
@@ -71,6 +87,11 @@ int flare_attn_create(int device, flare_attn_ctx** out_ctx) {
         return FLARE_ERR_CUDA;
     }
     ctx->stream = ctx->own_stream;
+    if (cudaMalloc(&ctx->d_err, sizeof(int)) != cudaSuccess || cudaMemset(ctx->d_err, 0, sizeof(int)) != cudaSuccess) {
+        cudaStreamDestroy(ctx->own_stream);
+        delete ctx;
+        return FLARE_ERR_CUDA;
+    }
     cudaDeviceGetAttribute(&ctx->sm_count, cudaDevAttrMultiProcessorCount, device);
     *out_ctx = ctx;
     return FLARE_OK;
@@ -81,6 +102,7 @@ int flare_attn_destroy(flare_attn_ctx* ctx) {
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     if (ctx->backend_kv) flare_kv_free(ctx->backend_kv);
+    cudaFree(ctx->d_err);
     cudaFree(ctx->d_work); cudaFree(ctx->d_stage_in); cudaFree(ctx->d_stage_out); cudaFree(ctx->d_misc);
     if (ctx->h_pinned) cudaFreeHost(ctx->h_pinned);
     for (int i = 0; i < FLARE_SMALL_SLOTS; i++) if (ctx->small_events[i]) cudaEventDestroy(ctx->small_events[i]);
@@ -101,7 +123,7 @@ int flare_attn_sync(flare_attn_ctx* ctx) {
     CHECK_CTX(ctx);
     BIND(ctx);
     FLARE_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
-    return FLARE_OK;
+    return flare_check_device_error(ctx);
 }
 
 const char* flare_attn_last_error(const flare_attn_ctx* ctx) { return ctx ? ctx->last_error.c_str() : "null context"; }
@@ -169,6 +191,20 @@ int flare_kv_alloc(flare_attn_ctx* ctx, int num_layers, int batch, int max_seq_l
             flare_kv_free(kv);
             return code;
         }
+    }
+    if (kv_dtype == FLARE_KV_Q8_0 && (head_dim == 64 || head_dim == 128) && num_kv_heads <= 8) {
+        const uint64_t dims[4] = {(uint64_t)head_dim, (uint64_t)num_kv_heads, (uint64_t)max_seq_len, (uint64_t)num_layers * batch};
+        const uint64_t strides[3] = {(uint64_t)head_dim, (uint64_t)kvd, (uint64_t)max_seq_len * kvd};
+        const uint32_t box[4] = {(uint32_t)head_dim, 1, 32, 1};
+        CUtensorMapSwizzle swz = head_dim == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B;
+        int r1 = flare_make_tensor_map(&kv->kq_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, kv->plane[FLARE_PLANE_K_Q], dims, strides, box, swz);
+        int r2 = flare_make_tensor_map(&kv->vq_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, kv->plane[FLARE_PLANE_V_Q], dims, strides, box, swz);
+        if (r1 != 0 || r2 != 0) {
+            flare_set_error(ctx, FLARE_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d, %d)", r1, r2);
+            flare_kv_free(kv);
+            return FLARE_ERR_CUDA;
+        }
+        kv->has_maps = true;
     }
     *out_kv = kv;
     return FLARE_OK;
@@ -452,6 +488,9 @@ static int decode_common(flare_attn_ctx* ctx, flare_kv* kv, int layer, int num_h
     BIND(ctx);
     DecodeArgs a;
     a.kv = flare_layer_view(kv, layer);
+    a.layer = layer;
+    a.kmap = kv->has_maps ? &kv->kq_map : nullptr;
+    a.vmap = kv->has_maps ? &kv->vq_map : nullptr;
     a.batch = kv->batch; a.n_q = n_q; a.num_heads = num_heads;
     a.slot_begin = slot_begin; a.slot_end = slot_end; a.want_partial = want_partial; a.causal_q = causal_q;
     FLARE_TRY(upload_small(ctx, kv, n_q, attend_len, &a.attend_len, &a.ring, &a.max_attend));
@@ -468,7 +507,7 @@ static int decode_common(flare_attn_ctx* ctx, flare_kv* kv, int layer, int num_h
     FLARE_TRY(flare_launch_decode(ctx, a));
     if (!on_device) {
         FLARE_CUDA_OK(ctx, cudaMemcpyAsync(out, a.out, o_bytes, cudaMemcpyDeviceToHost, ctx->stream));
-        FLARE_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
+        FLARE_TRY(flare_check_device_error(ctx));    // synchronises the stream
     }
     return FLARE_OK;
 }

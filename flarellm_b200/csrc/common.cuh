@@ -1,6 +1,7 @@
 // Internal declarations shared by the .cu files of libflare_attn.so.
 #pragma once
 
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <cuda_fp16.h>
 #include <cuda_bf16.h>
@@ -30,6 +31,7 @@ struct flare_attn_ctx {
     void* h_pinned = nullptr;    size_t pinned_bytes = 0;
     uint64_t small_counter = 0;
     cudaEvent_t small_events[FLARE_SMALL_SLOTS] = {};
+    int* d_err = nullptr;            // device word a kernel sets when a bounded wait gives up
     int sm_count = 148;
     flare_kv* backend_kv = nullptr;  // cache created by flare_backend_init_gpu_kv_cache
 };
@@ -41,6 +43,9 @@ struct flare_kv {
     void* plane[FLARE_PLANE_COUNT] = {};
     size_t plane_bytes[FLARE_PLANE_COUNT] = {};   // per (layer, sequence)
     std::vector<int64_t> position, length;       // per sequence
+    // TMA maps of the Q8_0 payload planes: (head_dim bytes, kv head, slot, layer*batch + seq), box 32 slots of one head
+    CUtensorMap kq_map, vq_map;
+    bool has_maps = false;
     inline char* plane_ptr(int p, int layer, int seq) const {
         return (char*)plane[p] + ((size_t)layer * batch + seq) * plane_bytes[p];
     }
@@ -94,9 +99,14 @@ struct DecodeArgs {
     int want_partial;          // 1: write [m, l, o] unnormalised
     int causal_q;              // 1: query i of n_q reads attend_len - (n_q-1-i) slots; 0: all read attend_len
     int max_attend;            // max over batch of attend_len (host-known upper bound)
+    int layer;
+    const CUtensorMap *kmap, *vmap;   // Q8_0 payload maps (null when the cache has none)
 };
 int flare_launch_decode(flare_attn_ctx* ctx, const DecodeArgs& a);
 int flare_launch_decode_generic(flare_attn_ctx* ctx, const DecodeArgs& a);
+bool flare_decode_q8_supported(const DecodeArgs& a);
+int flare_launch_decode_q8(flare_attn_ctx* ctx, const DecodeArgs& a);
+int flare_check_device_error(flare_attn_ctx* ctx);
 int flare_decode_noalloc(flare_attn_ctx* ctx, const flare_kv* kv, int layer, int num_heads, const float* q_dev,
                          int n_q, const int* attend_len, float* out_dev);
 size_t flare_noalloc_scratch_bytes();

@@ -388,6 +388,15 @@ int flare_launch_merge(flare_attn_ctx* ctx, const float* partials, size_t part_s
     return FLARE_OK;
 }
 
+int flare_launch_merge_work(flare_attn_ctx* ctx, const float* work, int n_split, int rows, int hd, float* out,
+                            int want_partial) {
+    int threads = hd < 128 ? hd : 128;
+    merge_partials_kernel<<<rows, threads, 0, ctx->stream>>>(work, (size_t)(hd + 2), (size_t)n_split * (hd + 2), n_split,
+                                                             hd, out, 1, want_partial);
+    FLARE_LAUNCH_CHECK(ctx);
+    return FLARE_OK;
+}
+
 int flare_launch_decode_generic(flare_attn_ctx* ctx, const DecodeArgs& a) {
     const int hd = a.kv.head_dim, nkv = a.kv.num_kv_heads;
     const int G = a.num_heads / nkv;

@@ -1,0 +1,401 @@
+// Q8_0 split-KV decode attention, the bandwidth-bound fast path (head_dim 64 / 128, up to 4
+// query heads per KV head, one query per sequence).
+//
+// One CTA = one (sequence, slot range); one warp per KV head.  Every warp runs its own
+// TMA pipeline: 32-slot tiles of its head's int8 K and V payload ([32][head_dim] bytes, hardware
+// 64B/128B swizzle) land in its private shared-memory ring through cp.async.bulk.tensor, each
+// stage guarded by an mbarrier; nothing is shared between warps, so there is no CTA-wide
+// barrier in the loop.  K/V are read from HBM exactly once for the 4 query heads sharing them.
+//
+// Dequantise-then-FMA on CUDA cores costs ~10 instructions per KV byte and cannot keep up with
+// HBM, so both contractions run on tensor cores with the Q8_0 scales hoisted out of the sums:
+//   scores  S[head, slot] = qs_head * sum_blk ks[slot, blk] * (Qint[head, blk, :] . Kint[slot, blk, :])
+//           as an exact int8 MMA (m16n8k32): Qint is q * log2e/sqrt(d) in 15-bit fixed point per head,
+//           carried as two int8 limbs (rows g and g+8 of the A operand).
+//   output  O[head, d] = sum_slot (p * vs[slot, blk(d)]) * Vint[slot, d]
+//           as an f16 MMA (m16n8k16, f32 accumulate): the weight p*vs is split into f16 hi + lo
+//           parts (two A rows), Vint bytes become exact f16 values 1024 + (v + 128) with one
+//           xor and one byte-permute per pair, and the constant 1152 * sum(p*vs) is subtracted at
+//           the end.  V is transposed for the MMA by ldmatrix.trans on the swizzled tile.
+// Softmax is the single-pass online recurrence of flare-core/src/model.rs:9914-9966, applied to
+// 32 slots at a time; ranges are merged by log-sum-exp (merge_partials_kernel).
+#include "common.cuh"
+#include "tma.cuh"
+#include <math_constants.h>
+
+namespace {
+
+constexpr int T = 32;            // slots per tile
+constexpr int STAGES = 3;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kQFix = 16256.0f;     // 127 * 128: |Qint| <= 16256 = 128 * limb0 + limb1
+
+struct Q8Params {
+    const float* q;
+    float* out;
+    float* work;
+    const int* attend_len;
+    const __half* k_scale;      // layer base, sequence 0
+    const __half* v_scale;
+    size_t scale_seq_stride;    // halves between sequences
+    int layer_seq0;             // layer * batch: TMA coordinate of sequence 0
+    int num_heads, nkv, G, max_seq, n_split, slot_begin, slot_end, want_partial, range_max;
+    int* err;
+};
+
+template <int HD> __device__ __forceinline__ uint32_t swz(int row, int chunk) {
+    uint32_t off = (uint32_t)(row * HD + chunk * 16);
+    constexpr uint32_t MASK = (HD == 64) ? 3u : 7u;
+    return off ^ (((off >> 7) & MASK) << 4);
+}
+
+__device__ __forceinline__ void mma_s8(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_f16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ CUtensorMap kmap,
+                                                        const __grid_constant__ CUtensorMap vmap, Q8Params p) {
+    constexpr int NB = HD / 32;        // Q8_0 blocks per head row
+    constexpr int MT = NB / 2;         // M-tiles of the PV product (two 32-channel blocks each)
+    constexpr int TILE = T * HD;       // bytes of one K (or V) tile
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    __shared__ uint64_t bars[8][STAGES];
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, tig = lane & 3;
+    const int split = blockIdx.x, b = blockIdx.y;
+    const int kvh = warp;
+    // 1024-aligned base: each warp owns STAGES x (K tile, V tile)
+    unsigned char* wbase = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023)) +
+                           (size_t)warp * STAGES * 2 * TILE;
+    uint64_t* bar = bars[warp];
+
+    // slot range of this (sequence, split), in whole tiles
+    int lo = 0, hi = p.attend_len[b];
+    if (p.slot_end >= 0) { lo = max(lo, p.slot_begin); hi = min(hi, p.slot_end); }
+    int t_first = lo / T, t_last = hi > lo ? (hi + T - 1) / T : t_first;
+    const int n_tiles_seq = t_last - t_first;
+    const int t_begin = t_first + (int)(((long long)split * n_tiles_seq) / p.n_split);
+    const int t_end = t_first + (int)(((long long)(split + 1) * n_tiles_seq) / p.n_split);
+    const int n_tiles = t_end - t_begin;
+
+    if (lane == 0) {
+        for (int s = 0; s < STAGES; s++) ptx::mbar_init(&bar[s], 1);
+        ptx::fence_barrier_init();
+        ptx::fence_proxy_async();
+    }
+    __syncwarp();
+
+    auto issue = [&](int i) {   // lane 0 only: tile i of this warp -> stage i % STAGES
+        const int s = i % STAGES;
+        unsigned char* kt = wbase + (size_t)s * 2 * TILE;
+        ptx::mbar_expect_tx(&bar[s], 2 * TILE);
+        ptx::tma_load_4d(kt, &kmap, &bar[s], 0, kvh, (t_begin + i) * T, p.layer_seq0 + b);
+        ptx::tma_load_4d(kt + TILE, &vmap, &bar[s], 0, kvh, (t_begin + i) * T, p.layer_seq0 + b);
+    };
+    if (lane == 0)
+        for (int i = 0; i < STAGES && i < n_tiles; i++) issue(i);
+
+    // ---- q as two int8 limbs per head, laid out as the A operand of m16n8k32 --------------
+    const int hq = g & 3;                          // query head of this lane within the group
+    const bool head_ok = hq < p.G;
+    const size_t row = (size_t)b * p.num_heads + kvh * p.G + (head_ok ? hq : 0);
+    uint32_t qa[NB][4];
+    float qs;                                       // score = qs * sum_blk ks * (int dot)
+    {
+        const float sc = rsqrtf((float)HD) * kLog2e;
+        float qv[NB][8];
+        float amax = 0.0f;
+#pragma unroll
+        for (int blk = 0; blk < NB; blk++) {
+            const float4* qp = reinterpret_cast<const float4*>(p.q + row * HD + blk * 32 + tig * 8);
+            float4 x = __ldg(qp), y = __ldg(qp + 1);
+            qv[blk][0] = x.x * sc; qv[blk][1] = x.y * sc; qv[blk][2] = x.z * sc; qv[blk][3] = x.w * sc;
+            qv[blk][4] = y.x * sc; qv[blk][5] = y.y * sc; qv[blk][6] = y.z * sc; qv[blk][7] = y.w * sc;
+#pragma unroll
+            for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(qv[blk][i]));
+        }
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        const float inv = amax > 0.0f ? kQFix / amax : 0.0f;
+        qs = amax / kQFix;
+        const bool limb_rows = (g < 4) && head_ok;   // rows g (limb 0) and g+8 (limb 1) carry head g
+#pragma unroll
+        for (int blk = 0; blk < NB; blk++) {
+            uint32_t l0[2] = {0, 0}, l1[2] = {0, 0};
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                int Q = __float2int_rn(qv[blk][i] * inv);
+                int lo_limb = ((Q + 64) & 127) - 64;          // [-64, 63]
+                int hi_limb = (Q - lo_limb) >> 7;              // exact: Q = 128 * hi + lo
+                l0[i >> 2] |= (uint32_t)(hi_limb & 0xFF) << (8 * (i & 3));
+                l1[i >> 2] |= (uint32_t)(lo_limb & 0xFF) << (8 * (i & 3));
+            }
+            qa[blk][0] = limb_rows ? l0[0] : 0u;   // row g,   k 0..15 half
+            qa[blk][1] = limb_rows ? l1[0] : 0u;   // row g+8
+            qa[blk][2] = limb_rows ? l0[1] : 0u;   // row g,   k 16..31 half
+            qa[blk][3] = limb_rows ? l1[1] : 0u;
+        }
+    }
+
+    // ---- running state ---------------------------------------------------------------------
+    float acc[MT][4][2][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+        for (int c = 0; c < 4; c++)
+#pragma unroll
+            for (int e = 0; e < 2; e++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) acc[mt][c][e][i] = 0.0f;
+    float m_run = -CUDART_INF_F, l_run = 0.0f, lb[MT];
+#pragma unroll
+    for (int mt = 0; mt < MT; mt++) lb[mt] = 0.0f;
+
+    const int bpr = p.nkv * NB;     // scale entries per slot row
+    const __half* ksp = p.k_scale + (size_t)b * p.scale_seq_stride + kvh * NB;
+    const __half* vsp = p.v_scale + (size_t)b * p.scale_seq_stride + kvh * NB;
+    const int lane_blk = g >> 2;    // which block of an M-tile this lane's rows belong to
+
+    bool failed = false;
+    for (int i = 0; i < n_tiles; i++) {
+        const int s = i % STAGES;
+        const int slot0 = (t_begin + i) * T;
+        // scales of this tile (small, L1/L2 resident; issued before the wait to overlap it)
+        float ks[4][2][NB], vs[MT][4][2];
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                int slot = min(slot0 + 8 * j + 2 * tig + e, p.max_seq - 1);
+                const __half* kr = ksp + (size_t)slot * bpr;
+                const __half* vr = vsp + (size_t)slot * bpr;
+#pragma unroll
+                for (int blk = 0; blk < NB; blk += 2) {
+                    float2 f = __half22float2(__ldg(reinterpret_cast<const __half2*>(kr + blk)));
+                    ks[j][e][blk] = f.x; ks[j][e][blk + 1] = f.y;
+                }
+#pragma unroll
+                for (int mt = 0; mt < MT; mt++) vs[mt][j][e] = __half2float(__ldg(vr + 2 * mt + lane_blk));
+            }
+        if (!ptx::mbar_wait(&bar[s], (uint32_t)((i / STAGES) & 1))) { failed = true; break; }
+        const unsigned char* kt = wbase + (size_t)s * 2 * TILE;
+        const uint32_t vt = ptx::smem_u32(kt + TILE);
+
+        // ---- scores: int8 MMA per 8-slot column tile and 32-channel block ------------------
+        float sc[4][2];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            float s0 = 0.0f, s1 = 0.0f;
+#pragma unroll
+            for (int blk = 0; blk < NB; blk++) {
+                // B fragment: 8 contiguous bytes of slot 8j+g, channels blk*32 + 8*tig .. +7
+                const uint2 kb = *reinterpret_cast<const uint2*>(kt + swz<HD>(8 * j + g, blk * 2 + (tig >> 1)) + (tig & 1) * 8);
+                int d[4] = {0, 0, 0, 0};
+                mma_s8(d, qa[blk], kb.x, kb.y);
+                // rows g / g+8 = limb 0 / limb 1 of head g (lanes with g < 4); columns = slots 2tig, 2tig+1
+                s0 = fmaf(ks[j][0][blk], (float)(d[0] * 128 + d[2]), s0);
+                s1 = fmaf(ks[j][1][blk], (float)(d[1] * 128 + d[3]), s1);
+            }
+            const int slot = slot0 + 8 * j + 2 * tig;
+            sc[j][0] = (slot >= lo && slot < hi) ? s0 * qs : -CUDART_INF_F;
+            sc[j][1] = (slot + 1 >= lo && slot + 1 < hi) ? s1 * qs : -CUDART_INF_F;
+        }
+        // rows 4..7 of the PV operand serve the same heads for the second channel block:
+        // lanes g >= 4 take the scores of lane g - 4
+        float tmax = -CUDART_INF_F;
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                sc[j][e] = __shfl_sync(0xffffffffu, sc[j][e], lane & 15);
+                tmax = fmaxf(tmax, sc[j][e]);
+            }
+        tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
+        tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+        const float m_new = fmaxf(m_run, tmax);
+        const bool any_valid = m_new > -CUDART_INF_F;
+        const float alpha = any_valid ? fast_exp2(m_run - m_new) : 1.0f;   // m_run = -inf -> 0
+        float pw[4][2], psum = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                pw[j][e] = any_valid ? fast_exp2(sc[j][e] - m_new) : 0.0f;
+                psum += pw[j][e];
+            }
+        l_run = l_run * alpha + psum;
+        m_run = m_new;
+        if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+#pragma unroll
+            for (int mt = 0; mt < MT; mt++) {
+                lb[mt] *= alpha;
+#pragma unroll
+                for (int c = 0; c < 4; c++)
+#pragma unroll
+                    for (int e = 0; e < 2; e++)
+#pragma unroll
+                        for (int k = 0; k < 4; k++) acc[mt][c][e][k] *= alpha;
+            }
+        }
+
+        // ---- output: f16 MMA, weights p * vs split into hi + lo -----------------------------
+#pragma unroll
+        for (int mt = 0; mt < MT; mt++) {
+            uint32_t pa[2][4];   // A fragments of the two 16-slot k-steps
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                float w0 = pw[j][0] * vs[mt][j][0], w1 = pw[j][1] * vs[mt][j][1];
+                lb[mt] += w0 + w1;
+                __half2 h = __floats2half2_rn(w0, w1);
+                float2 hf = __half22float2(h);
+                uint32_t hi_bits = *reinterpret_cast<uint32_t*>(&h);
+                uint32_t lo_bits = pack_half2(w0 - hf.x, w1 - hf.y);
+                pa[j >> 1][(j & 1) * 2] = hi_bits;        // a0 / a2: row g   (hi part)
+                pa[j >> 1][(j & 1) * 2 + 1] = lo_bits;    // a1 / a3: row g+8 (lo part)
+            }
+#pragma unroll
+            for (int kstep = 0; kstep < 2; kstep++) {
+#pragma unroll
+                for (int cp = 0; cp < 2; cp++) {          // chunk pairs of this M-tile's 64 channels
+                    const int mi = lane >> 3, r = lane & 7;
+                    const int vrow = 16 * kstep + (mi & 1) * 8 + r;
+                    const int chunk = 4 * mt + 2 * cp + (mi >> 1);
+                    uint32_t rr[4];
+                    ldmatrix_x4_trans(rr, vt + swz<HD>(vrow, chunk));
+#pragma unroll
+                    for (int k = 0; k < 4; k++) rr[k] ^= 0x80808080u;     // int8 -> uint8 (v + 128)
+                    // bytes (slot a, ch 0), (slot a, ch 1), (slot a+1, ch 0), (slot a+1, ch 1) ->
+                    // half2 (1024 + u[a][ch], 1024 + u[a+1][ch]) for ch = even / odd
+#pragma unroll
+                    for (int cc = 0; cc < 2; cc++) {
+                        uint32_t b0e = __byte_perm(rr[2 * cc], 0x64646464u, 0x4240);
+                        uint32_t b1e = __byte_perm(rr[2 * cc + 1], 0x64646464u, 0x4240);
+                        uint32_t b0o = __byte_perm(rr[2 * cc], 0x64646464u, 0x4341);
+                        uint32_t b1o = __byte_perm(rr[2 * cc + 1], 0x64646464u, 0x4341);
+                        mma_f16(acc[mt][2 * cp + cc][0], pa[kstep], b0e, b1e);
+                        mma_f16(acc[mt][2 * cp + cc][1], pa[kstep], b0o, b1o);
+                    }
+                }
+            }
+        }
+
+        // ---- refill this stage -------------------------------------------------------------
+        __syncwarp();
+        if (lane == 0 && i + STAGES < n_tiles) {
+            ptx::fence_proxy_async();
+            issue(i + STAGES);
+        }
+    }
+    if (failed) {
+        if (lane == 0) atomicExch(p.err, FLARE_ERR_TIMEOUT);
+        return;
+    }
+
+    // ---- finish: sums over the 4 lanes that share a row, remove the 1152 bias, write --------
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+#pragma unroll
+    for (int mt = 0; mt < MT; mt++) {
+        lb[mt] += __shfl_xor_sync(0xffffffffu, lb[mt], 1);
+        lb[mt] += __shfl_xor_sync(0xffffffffu, lb[mt], 2);
+    }
+    if (!head_ok) return;
+    const bool final_out = (p.n_split == 1) && !p.want_partial;
+    const float inv_l = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+    float* wrec = p.work + (row * p.n_split + split) * (HD + 2);
+#pragma unroll
+    for (int mt = 0; mt < MT; mt++) {
+        const float bias = 1152.0f * lb[mt];
+#pragma unroll
+        for (int lc = 0; lc < 2; lc++) {
+            const int c = 2 * lane_blk + lc;                  // chunk within the M-tile whose rows are ours
+            const int d0 = 64 * mt + 16 * c + 4 * tig;
+            float o0 = acc[mt][c][0][0] + acc[mt][c][0][2] - bias;   // channel d0
+            float o1 = acc[mt][c][1][0] + acc[mt][c][1][2] - bias;   // d0 + 1
+            float o2 = acc[mt][c][0][1] + acc[mt][c][0][3] - bias;   // d0 + 2
+            float o3 = acc[mt][c][1][1] + acc[mt][c][1][3] - bias;   // d0 + 3
+            if (final_out) {
+                *reinterpret_cast<float4*>(p.out + row * HD + d0) = make_float4(o0 * inv_l, o1 * inv_l, o2 * inv_l, o3 * inv_l);
+            } else {
+                *reinterpret_cast<float2*>(wrec + 2 + d0) = make_float2(o0, o1);
+                *reinterpret_cast<float2*>(wrec + 2 + d0 + 2) = make_float2(o2, o3);
+            }
+        }
+    }
+    if (!final_out && g < 4 && tig == 0) { wrec[0] = m_run; wrec[1] = l_run; }
+}
+
+}  // namespace
+
+// merge kernel shared with the general path
+extern int flare_launch_merge_work(flare_attn_ctx* ctx, const float* work, int n_split, int rows, int hd, float* out,
+                                   int want_partial);
+
+bool flare_decode_q8_supported(const DecodeArgs& a) {
+    const int hd = a.kv.head_dim, nkv = a.kv.num_kv_heads;
+    return a.kv.dtype == FLARE_KV_Q8_0 && (hd == 64 || hd == 128) && a.n_q == 1 && nkv <= 8 &&
+           a.num_heads / nkv <= 4 && a.kmap != nullptr;
+}
+
+int flare_launch_decode_q8(flare_attn_ctx* ctx, const DecodeArgs& a) {
+    const int hd = a.kv.head_dim, nkv = a.kv.num_kv_heads;
+    const int rows = a.batch * a.num_heads;
+    if (rows == 0) return FLARE_OK;
+    Q8Params p;
+    p.q = a.q; p.out = a.out; p.attend_len = a.attend_len;
+    p.k_scale = reinterpret_cast<const __half*>(a.kv.plane[FLARE_PLANE_K_SCALE]);
+    p.v_scale = reinterpret_cast<const __half*>(a.kv.plane[FLARE_PLANE_V_SCALE]);
+    p.scale_seq_stride = a.kv.stride[FLARE_PLANE_K_SCALE] / 2;
+    p.layer_seq0 = a.layer * a.batch;
+    p.num_heads = a.num_heads; p.nkv = nkv; p.G = a.num_heads / nkv; p.max_seq = a.kv.max_seq_len;
+    p.slot_begin = a.slot_begin; p.slot_end = a.slot_end; p.want_partial = a.want_partial;
+    p.range_max = a.slot_end >= 0 ? (a.slot_end - a.slot_begin) : a.max_attend;
+    if (p.range_max < 0) p.range_max = 0;
+    p.err = ctx->d_err;
+
+    const size_t smem = (size_t)nkv * STAGES * 2 * T * hd + 1024;
+    const int ctas_per_sm = smem <= 110 * 1024 ? 2 : 1;
+    // one wave: as many splits as fit without a second, partly filled wave
+    int n_split = (ctx->sm_count * ctas_per_sm) / a.batch;
+    const int max_split = (p.range_max + 4 * T - 1) / (4 * T);    // at least 4 tiles per CTA
+    if (n_split > max_split) n_split = max_split;
+    if (n_split < 1) n_split = 1;
+    if (n_split > 256) n_split = 256;
+    p.n_split = n_split;
+    size_t need = (size_t)rows * n_split * (hd + 2) * sizeof(float);
+    FLARE_TRY(flare_ensure(ctx, &ctx->d_work, &ctx->work_bytes, need));
+    p.work = (float*)ctx->d_work;
+
+    dim3 grid(n_split, a.batch);
+    // opt in to the large dynamic shared memory once per device
+    static bool attr_done[64][2] = {};
+    bool& done = attr_done[ctx->device & 63][hd == 128];
+    if (!done) {
+        const int max_smem = 8 * STAGES * 2 * T * hd + 1024;
+        if (hd == 64) FLARE_CUDA_OK(ctx, cudaFuncSetAttribute(decode_q8_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
+        else FLARE_CUDA_OK(ctx, cudaFuncSetAttribute(decode_q8_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
+        done = true;
+    }
+    if (hd == 64) decode_q8_kernel<64><<<grid, 32 * nkv, smem, ctx->stream>>>(*a.kmap, *a.vmap, p);
+    else decode_q8_kernel<128><<<grid, 32 * nkv, smem, ctx->stream>>>(*a.kmap, *a.vmap, p);
+    FLARE_LAUNCH_CHECK(ctx);
+    if (n_split > 1 || a.want_partial) FLARE_TRY(flare_launch_merge_work(ctx, p.work, n_split, rows, hd, a.out, a.want_partial));
+    return FLARE_OK;
+}
