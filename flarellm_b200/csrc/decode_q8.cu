@@ -63,9 +63,17 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t add
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
+// register-only conversions (no address is taken, so nothing is forced into local memory)
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
-    __half2 h = __floats2half2_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&h);
+    uint32_t u;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(u) : "f"(hi), "f"(lo));
+    return u;
+}
+__device__ __forceinline__ float2 unpack_half2(uint32_t u) {
+    float2 f;
+    asm("{\n\t.reg .f16 lo, hi;\n\tmov.b32 {lo, hi}, %2;\n\tcvt.f32.f16 %0, lo;\n\tcvt.f32.f16 %1, hi;\n\t}"
+        : "=f"(f.x), "=f"(f.y) : "r"(u));
+    return f;
 }
 
 template <int HD>
@@ -135,7 +143,9 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
         amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
         const float inv = amax > 0.0f ? kQFix / amax : 0.0f;
         qs = amax / kQFix;
-        const bool limb_rows = (g < 4) && head_ok;   // rows g (limb 0) and g+8 (limb 1) carry head g
+        // rows g and g+4 both carry limb 0 of head g & 3 (rows g+8, g+12: limb 1), so the lanes that
+        // own the second channel block of the PV operand get the same scores without a shuffle
+        const bool limb_rows = head_ok;
 #pragma unroll
         for (int blk = 0; blk < NB; blk++) {
             uint32_t l0[2] = {0, 0}, l1[2] = {0, 0};
@@ -173,76 +183,84 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
     const __half* vsp = p.v_scale + (size_t)b * p.scale_seq_stride + kvh * NB;
     const int lane_blk = g >> 2;    // which block of an M-tile this lane's rows belong to
 
+    // lane-constant shared-memory offsets.  The swizzle XORs the 16-byte chunk index with row bits
+    // that are the same for every 8-slot step (rows advance by 8), so each address is
+    // base(lane) + constant.
+    uint32_t koff[NB];              // K bytes of slot g, channels blk*32 + 8*tig .. +7
+#pragma unroll
+    for (int blk = 0; blk < NB; blk++) koff[blk] = swz<HD>(g, blk * 2 + (tig >> 1)) + (tig & 1) * 8;
+    uint32_t voff[MT][2];           // ldmatrix row address: V slot (mi&1)*8 + r, chunk 4mt + 2cp + (mi>>1)
+#pragma unroll
+    for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+        for (int cp = 0; cp < 2; cp++) voff[mt][cp] = swz<HD>(((lane >> 3) & 1) * 8 + (lane & 7), 4 * mt + 2 * cp + (lane >> 4));
+
+    // Scales: lane l fetches the K and V scales of slot l of the next tile (coalesced, one tile ahead);
+    // the lanes that need them pick them up with shuffles.
+    uint32_t ksr[NB / 2], vsr[NB / 2];
+    auto fetch_scales = [&](int i) {
+        int slot = min((t_begin + i) * T + lane, p.max_seq - 1);
+#pragma unroll
+        for (int h = 0; h < NB / 2; h++) {
+            ksr[h] = __ldg(reinterpret_cast<const uint32_t*>(ksp + (size_t)slot * bpr) + h);
+            vsr[h] = __ldg(reinterpret_cast<const uint32_t*>(vsp + (size_t)slot * bpr) + h);
+        }
+    };
+    if (n_tiles > 0) fetch_scales(0);
+
     bool failed = false;
     for (int i = 0; i < n_tiles; i++) {
         const int s = i % STAGES;
         const int slot0 = (t_begin + i) * T;
-        // scales of this tile (small, L1/L2 resident; issued before the wait to overlap it)
-        float ks[4][2][NB], vs[MT][4][2];
+        uint32_t ksc[NB / 2], vsc[NB / 2];
 #pragma unroll
-        for (int j = 0; j < 4; j++)
-#pragma unroll
-            for (int e = 0; e < 2; e++) {
-                int slot = min(slot0 + 8 * j + 2 * tig + e, p.max_seq - 1);
-                const __half* kr = ksp + (size_t)slot * bpr;
-                const __half* vr = vsp + (size_t)slot * bpr;
-#pragma unroll
-                for (int blk = 0; blk < NB; blk += 2) {
-                    float2 f = __half22float2(__ldg(reinterpret_cast<const __half2*>(kr + blk)));
-                    ks[j][e][blk] = f.x; ks[j][e][blk + 1] = f.y;
-                }
-#pragma unroll
-                for (int mt = 0; mt < MT; mt++) vs[mt][j][e] = __half2float(__ldg(vr + 2 * mt + lane_blk));
-            }
+        for (int h = 0; h < NB / 2; h++) { ksc[h] = ksr[h]; vsc[h] = vsr[h]; }
+        if (i + 1 < n_tiles) fetch_scales(i + 1);
         if (!ptx::mbar_wait(&bar[s], (uint32_t)((i / STAGES) & 1))) { failed = true; break; }
         const unsigned char* kt = wbase + (size_t)s * 2 * TILE;
         const uint32_t vt = ptx::smem_u32(kt + TILE);
 
         // ---- scores: int8 MMA per 8-slot column tile and 32-channel block ------------------
-        float sc[4][2];
+        float sc[4][2], vs[MT][4][2];
+        float tmax = -CUDART_INF_F;
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             float s0 = 0.0f, s1 = 0.0f;
+            const int src = 8 * j + 2 * tig;           // lanes holding the scales of this lane's two slots
 #pragma unroll
-            for (int blk = 0; blk < NB; blk++) {
-                // B fragment: 8 contiguous bytes of slot 8j+g, channels blk*32 + 8*tig .. +7
-                const uint2 kb = *reinterpret_cast<const uint2*>(kt + swz<HD>(8 * j + g, blk * 2 + (tig >> 1)) + (tig & 1) * 8);
-                int d[4] = {0, 0, 0, 0};
-                mma_s8(d, qa[blk], kb.x, kb.y);
-                // rows g / g+8 = limb 0 / limb 1 of head g (lanes with g < 4); columns = slots 2tig, 2tig+1
-                s0 = fmaf(ks[j][0][blk], (float)(d[0] * 128 + d[2]), s0);
-                s1 = fmaf(ks[j][1][blk], (float)(d[1] * 128 + d[3]), s1);
+            for (int h = 0; h < NB / 2; h++) {
+                const uint32_t k0 = __shfl_sync(0xffffffffu, ksc[h], src), k1 = __shfl_sync(0xffffffffu, ksc[h], src + 1);
+                const uint32_t v0 = __shfl_sync(0xffffffffu, vsc[h], src), v1 = __shfl_sync(0xffffffffu, vsc[h], src + 1);
+                const float2 kf0 = unpack_half2(k0), kf1 = unpack_half2(k1);
+                const float2 vf0 = unpack_half2(v0), vf1 = unpack_half2(v1);
+                vs[h][j][0] = lane_blk ? vf0.y : vf0.x;     // M-tile h = blocks 2h, 2h+1
+                vs[h][j][1] = lane_blk ? vf1.y : vf1.x;
+#pragma unroll
+                for (int bb = 0; bb < 2; bb++) {
+                    const int blk = 2 * h + bb;
+                    // B fragment: 8 contiguous bytes of slot 8j+g, channels blk*32 + 8*tig .. +7
+                    const uint2 kb = *reinterpret_cast<const uint2*>(kt + koff[blk] + j * 8 * HD);
+                    int d[4] = {0, 0, 0, 0};
+                    mma_s8(d, qa[blk], kb.x, kb.y);
+                    // rows g / g+8 = limb 0 / limb 1 of head g & 3; columns = slots 2tig, 2tig+1
+                    s0 = fmaf(bb ? kf0.y : kf0.x, (float)(d[0] * 128 + d[2]), s0);
+                    s1 = fmaf(bb ? kf1.y : kf1.x, (float)(d[1] * 128 + d[3]), s1);
+                }
             }
             const int slot = slot0 + 8 * j + 2 * tig;
             sc[j][0] = (slot >= lo && slot < hi) ? s0 * qs : -CUDART_INF_F;
             sc[j][1] = (slot + 1 >= lo && slot + 1 < hi) ? s1 * qs : -CUDART_INF_F;
+            tmax = fmaxf(tmax, fmaxf(sc[j][0], sc[j][1]));
         }
-        // rows 4..7 of the PV operand serve the same heads for the second channel block:
-        // lanes g >= 4 take the scores of lane g - 4
-        float tmax = -CUDART_INF_F;
-#pragma unroll
-        for (int j = 0; j < 4; j++)
-#pragma unroll
-            for (int e = 0; e < 2; e++) {
-                sc[j][e] = __shfl_sync(0xffffffffu, sc[j][e], lane & 15);
-                tmax = fmaxf(tmax, sc[j][e]);
-            }
         tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
         tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
-        const float m_new = fmaxf(m_run, tmax);
-        const bool any_valid = m_new > -CUDART_INF_F;
-        const float alpha = any_valid ? fast_exp2(m_run - m_new) : 1.0f;   // m_run = -inf -> 0
-        float pw[4][2], psum = 0.0f;
-#pragma unroll
-        for (int j = 0; j < 4; j++)
-#pragma unroll
-            for (int e = 0; e < 2; e++) {
-                pw[j][e] = any_valid ? fast_exp2(sc[j][e] - m_new) : 0.0f;
-                psum += pw[j][e];
-            }
-        l_run = l_run * alpha + psum;
-        m_run = m_new;
-        if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+        // Lazy rescaling: the reference maximum m_run only moves when the tile maximum exceeds it by
+        // more than 2^8, so exponentials stay below 256 and the accumulators are rarely rescaled.
+        const bool bump = tmax > m_run + 8.0f;          // also true for the first valid tile (m_run = -inf)
+        if (__any_sync(0xffffffffu, bump)) {
+            const float alpha = bump ? fast_exp2(m_run - tmax) : 1.0f;     // m_run = -inf -> 0
+            if (bump) m_run = tmax;
+            l_run *= alpha;
 #pragma unroll
             for (int mt = 0; mt < MT; mt++) {
                 lb[mt] *= alpha;
@@ -254,6 +272,15 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
                         for (int k = 0; k < 4; k++) acc[mt][c][e][k] *= alpha;
             }
         }
+        float pw[4][2];
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                // m_run = -inf only while every slot so far was masked: exp2(-inf - -inf) would be NaN
+                pw[j][e] = m_run > -CUDART_INF_F ? fast_exp2(sc[j][e] - m_run) : 0.0f;
+                l_run += pw[j][e];
+            }
 
         // ---- output: f16 MMA, weights p * vs split into hi + lo -----------------------------
 #pragma unroll
@@ -263,10 +290,9 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
             for (int j = 0; j < 4; j++) {
                 float w0 = pw[j][0] * vs[mt][j][0], w1 = pw[j][1] * vs[mt][j][1];
                 lb[mt] += w0 + w1;
-                __half2 h = __floats2half2_rn(w0, w1);
-                float2 hf = __half22float2(h);
-                uint32_t hi_bits = *reinterpret_cast<uint32_t*>(&h);
-                uint32_t lo_bits = pack_half2(w0 - hf.x, w1 - hf.y);
+                const uint32_t hi_bits = pack_half2(w0, w1);
+                const float2 hf = unpack_half2(hi_bits);
+                const uint32_t lo_bits = pack_half2(w0 - hf.x, w1 - hf.y);
                 pa[j >> 1][(j & 1) * 2] = hi_bits;        // a0 / a2: row g   (hi part)
                 pa[j >> 1][(j & 1) * 2 + 1] = lo_bits;    // a1 / a3: row g+8 (lo part)
             }
@@ -274,11 +300,8 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
             for (int kstep = 0; kstep < 2; kstep++) {
 #pragma unroll
                 for (int cp = 0; cp < 2; cp++) {          // chunk pairs of this M-tile's 64 channels
-                    const int mi = lane >> 3, r = lane & 7;
-                    const int vrow = 16 * kstep + (mi & 1) * 8 + r;
-                    const int chunk = 4 * mt + 2 * cp + (mi >> 1);
                     uint32_t rr[4];
-                    ldmatrix_x4_trans(rr, vt + swz<HD>(vrow, chunk));
+                    ldmatrix_x4_trans(rr, vt + voff[mt][cp] + kstep * 16 * HD);
 #pragma unroll
                     for (int k = 0; k < 4; k++) rr[k] ^= 0x80808080u;     // int8 -> uint8 (v + 128)
                     // bytes (slot a, ch 0), (slot a, ch 1), (slot a+1, ch 0), (slot a+1, ch 1) ->
@@ -325,12 +348,13 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
         const float bias = 1152.0f * lb[mt];
 #pragma unroll
         for (int lc = 0; lc < 2; lc++) {
-            const int c = 2 * lane_blk + lc;                  // chunk within the M-tile whose rows are ours
-            const int d0 = 64 * mt + 16 * c + 4 * tig;
-            float o0 = acc[mt][c][0][0] + acc[mt][c][0][2] - bias;   // channel d0
-            float o1 = acc[mt][c][1][0] + acc[mt][c][1][2] - bias;   // d0 + 1
-            float o2 = acc[mt][c][0][1] + acc[mt][c][0][3] - bias;   // d0 + 2
-            float o3 = acc[mt][c][1][1] + acc[mt][c][1][3] - bias;   // d0 + 3
+            // chunk 2*lane_blk + lc of the M-tile holds this lane's rows; select without a
+            // lane-dependent array index (that would push the accumulators into local memory)
+            const int d0 = 64 * mt + 16 * (2 * lane_blk + lc) + 4 * tig;
+            float o0 = (lane_blk ? acc[mt][2 + lc][0][0] + acc[mt][2 + lc][0][2] : acc[mt][lc][0][0] + acc[mt][lc][0][2]) - bias;   // channel d0
+            float o1 = (lane_blk ? acc[mt][2 + lc][1][0] + acc[mt][2 + lc][1][2] : acc[mt][lc][1][0] + acc[mt][lc][1][2]) - bias;   // d0 + 1
+            float o2 = (lane_blk ? acc[mt][2 + lc][0][1] + acc[mt][2 + lc][0][3] : acc[mt][lc][0][1] + acc[mt][lc][0][3]) - bias;   // d0 + 2
+            float o3 = (lane_blk ? acc[mt][2 + lc][1][1] + acc[mt][2 + lc][1][3] : acc[mt][lc][1][1] + acc[mt][lc][1][3]) - bias;   // d0 + 3
             if (final_out) {
                 *reinterpret_cast<float4*>(p.out + row * HD + d0) = make_float4(o0 * inv_l, o1 * inv_l, o2 * inv_l, o3 * inv_l);
             } else {
