@@ -193,12 +193,23 @@ int flare_kv_alloc(flare_attn_ctx* ctx, int num_layers, int batch, int max_seq_l
         }
     }
     if (kv_dtype == FLARE_KV_Q8_0 && (head_dim == 64 || head_dim == 128) && num_kv_heads <= 8) {
-        const uint64_t dims[4] = {(uint64_t)head_dim, (uint64_t)num_kv_heads, (uint64_t)max_seq_len, (uint64_t)num_layers * batch};
-        const uint64_t strides[3] = {(uint64_t)head_dim, (uint64_t)kvd, (uint64_t)max_seq_len * kvd};
-        const uint32_t box[4] = {(uint32_t)head_dim, 1, 32, 1};
         CUtensorMapSwizzle swz = head_dim == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B;
-        int r1 = flare_make_tensor_map(&kv->kq_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, kv->plane[FLARE_PLANE_K_Q], dims, strides, box, swz);
-        int r2 = flare_make_tensor_map(&kv->vq_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, kv->plane[FLARE_PLANE_V_Q], dims, strides, box, swz);
+        // preferred: (head_dim bytes, slot, kv head, layer*batch + seq) with a box of 32 slots x all heads,
+        // which lands in shared memory as [head][slot][head_dim] from one contiguous stretch of the plane
+        const uint64_t dims_w[4] = {(uint64_t)head_dim, (uint64_t)max_seq_len, (uint64_t)num_kv_heads, (uint64_t)num_layers * batch};
+        const uint64_t strides_w[3] = {(uint64_t)kvd, (uint64_t)head_dim, (uint64_t)max_seq_len * kvd};
+        const uint32_t box_w[4] = {(uint32_t)head_dim, 32, (uint32_t)num_kv_heads, 1};
+        int r1 = flare_make_tensor_map(&kv->kq_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, kv->plane[FLARE_PLANE_K_Q], dims_w, strides_w, box_w, swz);
+        int r2 = flare_make_tensor_map(&kv->vq_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, kv->plane[FLARE_PLANE_V_Q], dims_w, strides_w, box_w, swz);
+        kv->maps_whole_rows = (r1 == 0 && r2 == 0);
+        if (!kv->maps_whole_rows) {
+            // fallback: natural dimension order, one box per head
+            const uint64_t dims[4] = {(uint64_t)head_dim, (uint64_t)num_kv_heads, (uint64_t)max_seq_len, (uint64_t)num_layers * batch};
+            const uint64_t strides[3] = {(uint64_t)head_dim, (uint64_t)kvd, (uint64_t)max_seq_len * kvd};
+            const uint32_t box[4] = {(uint32_t)head_dim, 1, 32, 1};
+            r1 = flare_make_tensor_map(&kv->kq_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, kv->plane[FLARE_PLANE_K_Q], dims, strides, box, swz);
+            r2 = flare_make_tensor_map(&kv->vq_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, kv->plane[FLARE_PLANE_V_Q], dims, strides, box, swz);
+        }
         if (r1 != 0 || r2 != 0) {
             flare_set_error(ctx, FLARE_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d, %d)", r1, r2);
             flare_kv_free(kv);
@@ -491,6 +502,7 @@ static int decode_common(flare_attn_ctx* ctx, flare_kv* kv, int layer, int num_h
     a.layer = layer;
     a.kmap = kv->has_maps ? &kv->kq_map : nullptr;
     a.vmap = kv->has_maps ? &kv->vq_map : nullptr;
+    a.whole_rows = kv->maps_whole_rows ? 1 : 0;
     a.batch = kv->batch; a.n_q = n_q; a.num_heads = num_heads;
     a.slot_begin = slot_begin; a.slot_end = slot_end; a.want_partial = want_partial; a.causal_q = causal_q;
     FLARE_TRY(upload_small(ctx, kv, n_q, attend_len, &a.attend_len, &a.ring, &a.max_attend));

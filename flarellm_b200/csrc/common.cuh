@@ -46,6 +46,7 @@ struct flare_kv {
     // TMA maps of the Q8_0 payload planes: (head_dim bytes, kv head, slot, layer*batch + seq), box 32 slots of one head
     CUtensorMap kq_map, vq_map;
     bool has_maps = false;
+    bool maps_whole_rows = false;
     inline char* plane_ptr(int p, int layer, int seq) const {
         return (char*)plane[p] + ((size_t)layer * batch + seq) * plane_bytes[p];
     }
@@ -101,6 +102,7 @@ struct DecodeArgs {
     int max_attend;            // max over batch of attend_len (host-known upper bound)
     int layer;
     const CUtensorMap *kmap, *vmap;   // Q8_0 payload maps (null when the cache has none)
+    int whole_rows;                   // maps deliver [head][32 slots][head_dim] in one copy
 };
 int flare_launch_decode(flare_attn_ctx* ctx, const DecodeArgs& a);
 int flare_launch_decode_generic(flare_attn_ctx* ctx, const DecodeArgs& a);

@@ -1,11 +1,13 @@
 // Q8_0 split-KV decode attention, the bandwidth-bound fast path (head_dim 64 / 128, up to 4
 // query heads per KV head, one query per sequence).
 //
-// One CTA = one (sequence, slot range); one warp per KV head.  Every warp runs its own
-// TMA pipeline: 32-slot tiles of its head's int8 K and V payload ([32][head_dim] bytes, hardware
-// 64B/128B swizzle) land in its private shared-memory ring through cp.async.bulk.tensor, each
-// stage guarded by an mbarrier; nothing is shared between warps, so there is no CTA-wide
-// barrier in the loop.  K/V are read from HBM exactly once for the 4 query heads sharing them.
+// One CTA = one (sequence, slot range), one warp per KV head.  Whole 32-slot tiles — every
+// head's int8 K and V payload and the f16 scales, i.e. contiguous 16 KB + 1 KB pieces of each
+// plane, which keeps DRAM pages open — stream into a ring of shared-memory stages through
+// cp.async.bulk.tensor (hardware 64B/128B swizzle, landing as [head][slot][head_dim]) and
+// cp.async.bulk, each stage guarded by an mbarrier.  There is no producer warp and no wait for
+// a free stage: the last warp to finish with a stage (a shared-memory ticket) refills it.
+// K/V are read from HBM exactly once for the 4 query heads sharing them.
 //
 // Dequantise-then-FMA on CUDA cores costs ~10 instructions per KV byte and cannot keep up with
 // HBM, so both contractions run on tensor cores with the Q8_0 scales hoisted out of the sums:
@@ -13,10 +15,10 @@
 //           as an exact int8 MMA (m16n8k32): Qint is q * log2e/sqrt(d) in 15-bit fixed point per head,
 //           carried as two int8 limbs (rows g and g+8 of the A operand).
 //   output  O[head, d] = sum_slot (p * vs[slot, blk(d)]) * Vint[slot, d]
-//           as an f16 MMA (m16n8k16, f32 accumulate): the weight p*vs is split into f16 hi + lo
-//           parts (two A rows), Vint bytes become exact f16 values 1024 + (v + 128) with one
-//           xor and one byte-permute per pair, and the constant 1152 * sum(p*vs) is subtracted at
-//           the end.  V is transposed for the MMA by ldmatrix.trans on the swizzled tile.
+//           as an f16 MMA (m16n8k16, f32 accumulate): the weight p*vs is rounded to f16, Vint bytes
+//           become exact f16 values 1024 + (v + 128) with one xor and one byte-permute per pair,
+//           and the constant 1152 * sum(weights) is subtracted at the end.  V is transposed for
+//           the MMA by ldmatrix.trans on the swizzled tile.
 // Softmax is the single-pass online recurrence of flare-core/src/model.rs:9914-9966, applied to
 // 32 slots at a time; ranges are merged by log-sum-exp (merge_partials_kernel).
 #include "common.cuh"
@@ -40,6 +42,7 @@ struct Q8Params {
     size_t scale_seq_stride;    // halves between sequences
     int layer_seq0;             // layer * batch: TMA coordinate of sequence 0
     int num_heads, nkv, G, max_seq, n_split, slot_begin, slot_end, want_partial, range_max;
+    int whole_rows;             // 1: the maps deliver all heads of a tile in one copy; 0: one copy per head
     int* err;
 };
 
@@ -82,17 +85,22 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
     constexpr int NB = HD / 32;        // Q8_0 blocks per head row
     constexpr int MT = NB / 2;         // M-tiles of the PV product (two 32-channel blocks each)
     constexpr int TILE = T * HD;       // bytes of one K (or V) tile
+    constexpr int SCALE_ROW = 8 * NB * 2;   // bytes of one slot's scale row when nkv == 8 (runtime: p.nkv * NB * 2)
     extern __shared__ __align__(1024) unsigned char smem_raw[];
-    __shared__ uint64_t bars[8][STAGES];
+    __shared__ uint64_t full_bar[STAGES];
+    __shared__ int done_cnt[STAGES];        // warps that have finished with the stage's current tile
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, tig = lane & 3;
     const int split = blockIdx.x, b = blockIdx.y;
+    const int nkv = p.nkv;
     const int kvh = warp;
-    // 1024-aligned base: each warp owns STAGES x (K tile, V tile)
-    unsigned char* wbase = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023)) +
-                           (size_t)warp * STAGES * 2 * TILE;
-    uint64_t* bar = bars[warp];
+    // stage layout: K payload [nkv][T][HD], V payload [nkv][T][HD], K scales [T][nkv*NB] f16, V scales
+    const int payload = nkv * TILE;
+    const int scale_tile = T * nkv * NB * 2;
+    const int stage_bytes = 2 * payload + 2 * scale_tile;     // a multiple of 1024 (checked on the host)
+    unsigned char* sbase = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    (void)SCALE_ROW;
 
     // slot range of this (sequence, split), in whole tiles
     int lo = 0, hi = p.attend_len[b];
@@ -103,22 +111,35 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
     const int t_end = t_first + (int)(((long long)(split + 1) * n_tiles_seq) / p.n_split);
     const int n_tiles = t_end - t_begin;
 
-    if (lane == 0) {
-        for (int s = 0; s < STAGES; s++) ptx::mbar_init(&bar[s], 1);
+    const int bpr = nkv * NB;       // scale entries per slot row
+    const unsigned char* ksg = reinterpret_cast<const unsigned char*>(p.k_scale + (size_t)b * p.scale_seq_stride);
+    const unsigned char* vsg = reinterpret_cast<const unsigned char*>(p.v_scale + (size_t)b * p.scale_seq_stride);
+    auto issue = [&](int i) {       // one thread: tile i of this CTA -> stage i % STAGES
+        const int s = i % STAGES;
+        unsigned char* st = sbase + (size_t)s * stage_bytes;
+        const int slot0 = (t_begin + i) * T;
+        const int rows = min(T, p.max_seq - slot0);            // scale rows that exist in the plane
+        const uint32_t sbytes = (uint32_t)rows * bpr * 2;
+        ptx::mbar_expect_tx(&full_bar[s], 2 * payload + 2 * sbytes);
+        if (p.whole_rows) {
+            ptx::tma_load_4d(st, &kmap, &full_bar[s], 0, slot0, 0, p.layer_seq0 + b);
+            ptx::tma_load_4d(st + payload, &vmap, &full_bar[s], 0, slot0, 0, p.layer_seq0 + b);
+        } else {
+            for (int h = 0; h < nkv; h++) {
+                ptx::tma_load_4d(st + h * TILE, &kmap, &full_bar[s], 0, h, slot0, p.layer_seq0 + b);
+                ptx::tma_load_4d(st + payload + h * TILE, &vmap, &full_bar[s], 0, h, slot0, p.layer_seq0 + b);
+            }
+        }
+        ptx::bulk_load(st + 2 * payload, ksg + (size_t)slot0 * bpr * 2, sbytes, &full_bar[s]);
+        ptx::bulk_load(st + 2 * payload + scale_tile, vsg + (size_t)slot0 * bpr * 2, sbytes, &full_bar[s]);
+    };
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) { ptx::mbar_init(&full_bar[s], 1); done_cnt[s] = 0; }
         ptx::fence_barrier_init();
         ptx::fence_proxy_async();
-    }
-    __syncwarp();
-
-    auto issue = [&](int i) {   // lane 0 only: tile i of this warp -> stage i % STAGES
-        const int s = i % STAGES;
-        unsigned char* kt = wbase + (size_t)s * 2 * TILE;
-        ptx::mbar_expect_tx(&bar[s], 2 * TILE);
-        ptx::tma_load_4d(kt, &kmap, &bar[s], 0, kvh, (t_begin + i) * T, p.layer_seq0 + b);
-        ptx::tma_load_4d(kt + TILE, &vmap, &bar[s], 0, kvh, (t_begin + i) * T, p.layer_seq0 + b);
-    };
-    if (lane == 0)
         for (int i = 0; i < STAGES && i < n_tiles; i++) issue(i);
+    }
+    __syncthreads();
 
     // ---- q as two int8 limbs per head, laid out as the A operand of m16n8k32 --------------
     const int hq = g & 3;                          // query head of this lane within the group
@@ -178,9 +199,6 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
 #pragma unroll
     for (int mt = 0; mt < MT; mt++) lb[mt] = 0.0f;
 
-    const int bpr = p.nkv * NB;     // scale entries per slot row
-    const __half* ksp = p.k_scale + (size_t)b * p.scale_seq_stride + kvh * NB;
-    const __half* vsp = p.v_scale + (size_t)b * p.scale_seq_stride + kvh * NB;
     const int lane_blk = g >> 2;    // which block of an M-tile this lane's rows belong to
 
     // lane-constant shared-memory offsets.  The swizzle XORs the 16-byte chunk index with row bits
@@ -188,53 +206,39 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
     // base(lane) + constant.
     uint32_t koff[NB];              // K bytes of slot g, channels blk*32 + 8*tig .. +7
 #pragma unroll
-    for (int blk = 0; blk < NB; blk++) koff[blk] = swz<HD>(g, blk * 2 + (tig >> 1)) + (tig & 1) * 8;
+    for (int blk = 0; blk < NB; blk++) koff[blk] = kvh * TILE + swz<HD>(g, blk * 2 + (tig >> 1)) + (tig & 1) * 8;
     uint32_t voff[MT][2];           // ldmatrix row address: V slot (mi&1)*8 + r, chunk 4mt + 2cp + (mi>>1)
 #pragma unroll
     for (int mt = 0; mt < MT; mt++)
 #pragma unroll
-        for (int cp = 0; cp < 2; cp++) voff[mt][cp] = swz<HD>(((lane >> 3) & 1) * 8 + (lane & 7), 4 * mt + 2 * cp + (lane >> 4));
-
-    // Scales: lane l fetches the K and V scales of slot l of the next tile (coalesced, one tile ahead);
-    // the lanes that need them pick them up with shuffles.
-    uint32_t ksr[NB / 2], vsr[NB / 2];
-    auto fetch_scales = [&](int i) {
-        int slot = min((t_begin + i) * T + lane, p.max_seq - 1);
-#pragma unroll
-        for (int h = 0; h < NB / 2; h++) {
-            ksr[h] = __ldg(reinterpret_cast<const uint32_t*>(ksp + (size_t)slot * bpr) + h);
-            vsr[h] = __ldg(reinterpret_cast<const uint32_t*>(vsp + (size_t)slot * bpr) + h);
-        }
-    };
-    if (n_tiles > 0) fetch_scales(0);
+        for (int cp = 0; cp < 2; cp++)
+            voff[mt][cp] = payload + kvh * TILE + swz<HD>(((lane >> 3) & 1) * 8 + (lane & 7), 4 * mt + 2 * cp + (lane >> 4));
+    // scales of slot 2*tig (+1) of each 8-slot step, this head: [slot][nkv*NB] f16
+    const uint32_t ksoff = 2 * payload + (2 * tig * bpr + kvh * NB) * 2;
+    const uint32_t vsoff = ksoff + scale_tile + lane_blk * 2;
 
     bool failed = false;
     for (int i = 0; i < n_tiles; i++) {
         const int s = i % STAGES;
         const int slot0 = (t_begin + i) * T;
-        uint32_t ksc[NB / 2], vsc[NB / 2];
-#pragma unroll
-        for (int h = 0; h < NB / 2; h++) { ksc[h] = ksr[h]; vsc[h] = vsr[h]; }
-        if (i + 1 < n_tiles) fetch_scales(i + 1);
-        if (!ptx::mbar_wait(&bar[s], (uint32_t)((i / STAGES) & 1))) { failed = true; break; }
-        const unsigned char* kt = wbase + (size_t)s * 2 * TILE;
-        const uint32_t vt = ptx::smem_u32(kt + TILE);
+        if (!ptx::mbar_wait(&full_bar[s], (uint32_t)((i / STAGES) & 1))) { failed = true; break; }
+        const unsigned char* kt = sbase + (size_t)s * stage_bytes;
+        const uint32_t vt = ptx::smem_u32(kt);
 
         // ---- scores: int8 MMA per 8-slot column tile and 32-channel block ------------------
-        float sc[4][2], vs[MT][4][2];
+        float sc[4][2], vs[MT][4][2];    // sc: integer-domain scores (score = qs * sc, qs >= 0)
         float tmax = -CUDART_INF_F;
+        const bool edge_tile = (slot0 < lo) || (slot0 + T > hi);      // warp-uniform
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             float s0 = 0.0f, s1 = 0.0f;
-            const int src = 8 * j + 2 * tig;           // lanes holding the scales of this lane's two slots
 #pragma unroll
             for (int h = 0; h < NB / 2; h++) {
-                const uint32_t k0 = __shfl_sync(0xffffffffu, ksc[h], src), k1 = __shfl_sync(0xffffffffu, ksc[h], src + 1);
-                const uint32_t v0 = __shfl_sync(0xffffffffu, vsc[h], src), v1 = __shfl_sync(0xffffffffu, vsc[h], src + 1);
-                const float2 kf0 = unpack_half2(k0), kf1 = unpack_half2(k1);
-                const float2 vf0 = unpack_half2(v0), vf1 = unpack_half2(v1);
-                vs[h][j][0] = lane_blk ? vf0.y : vf0.x;     // M-tile h = blocks 2h, 2h+1
-                vs[h][j][1] = lane_blk ? vf1.y : vf1.x;
+                // (blk 2h, blk 2h+1) scales of slots 8j + 2tig and 8j + 2tig + 1
+                const float2 kf0 = unpack_half2(*reinterpret_cast<const uint32_t*>(kt + ksoff + (8 * j * bpr + 2 * h) * 2));
+                const float2 kf1 = unpack_half2(*reinterpret_cast<const uint32_t*>(kt + ksoff + ((8 * j + 1) * bpr + 2 * h) * 2));
+                vs[h][j][0] = __half2float(*reinterpret_cast<const __half*>(kt + vsoff + (8 * j * bpr + 2 * h) * 2));
+                vs[h][j][1] = __half2float(*reinterpret_cast<const __half*>(kt + vsoff + ((8 * j + 1) * bpr + 2 * h) * 2));
 #pragma unroll
                 for (int bb = 0; bb < 2; bb++) {
                     const int blk = 2 * h + bb;
@@ -247,18 +251,22 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
                     s1 = fmaf(bb ? kf1.y : kf1.x, (float)(d[1] * 128 + d[3]), s1);
                 }
             }
-            const int slot = slot0 + 8 * j + 2 * tig;
-            sc[j][0] = (slot >= lo && slot < hi) ? s0 * qs : -CUDART_INF_F;
-            sc[j][1] = (slot + 1 >= lo && slot + 1 < hi) ? s1 * qs : -CUDART_INF_F;
-            tmax = fmaxf(tmax, fmaxf(sc[j][0], sc[j][1]));
+            if (edge_tile) {       // only the first and last tile of a range hold slots outside it
+                const int slot = slot0 + 8 * j + 2 * tig;
+                if (slot < lo || slot >= hi) s0 = -CUDART_INF_F;
+                if (slot + 1 < lo || slot + 1 >= hi) s1 = -CUDART_INF_F;
+            }
+            sc[j][0] = s0; sc[j][1] = s1;
+            tmax = fmaxf(tmax, fmaxf(s0, s1));
         }
+        tmax *= qs;
         tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
         tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
         // Lazy rescaling: the reference maximum m_run only moves when the tile maximum exceeds it by
         // more than 2^8, so exponentials stay below 256 and the accumulators are rarely rescaled.
         const bool bump = tmax > m_run + 8.0f;          // also true for the first valid tile (m_run = -inf)
         if (__any_sync(0xffffffffu, bump)) {
-            const float alpha = bump ? fast_exp2(m_run - tmax) : 1.0f;     // m_run = -inf -> 0
+            const float alpha = bump ? fast_exp2(m_run - tmax) : 1.0f;     // m_run = -inf -> 0 (nothing accumulated yet)
             if (bump) m_run = tmax;
             l_run *= alpha;
 #pragma unroll
@@ -272,13 +280,15 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
                         for (int k = 0; k < 4; k++) acc[mt][c][e][k] *= alpha;
             }
         }
+        // every tile of a non-empty range holds at least one slot of it, so m_run is finite from the
+        // first tile on and a masked slot gives exp2(-inf) = 0
         float pw[4][2];
+        const float neg_m = -m_run;
 #pragma unroll
         for (int j = 0; j < 4; j++)
 #pragma unroll
             for (int e = 0; e < 2; e++) {
-                // m_run = -inf only while every slot so far was masked: exp2(-inf - -inf) would be NaN
-                pw[j][e] = m_run > -CUDART_INF_F ? fast_exp2(sc[j][e] - m_run) : 0.0f;
+                pw[j][e] = fast_exp2(fmaf(sc[j][e], qs, neg_m));
                 l_run += pw[j][e];
             }
 
@@ -288,13 +298,13 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
             uint32_t pa[2][4];   // A fragments of the two 16-slot k-steps
 #pragma unroll
             for (int j = 0; j < 4; j++) {
-                float w0 = pw[j][0] * vs[mt][j][0], w1 = pw[j][1] * vs[mt][j][1];
-                lb[mt] += w0 + w1;
-                const uint32_t hi_bits = pack_half2(w0, w1);
-                const float2 hf = unpack_half2(hi_bits);
-                const uint32_t lo_bits = pack_half2(w0 - hf.x, w1 - hf.y);
-                pa[j >> 1][(j & 1) * 2] = hi_bits;        // a0 / a2: row g   (hi part)
-                pa[j >> 1][(j & 1) * 2 + 1] = lo_bits;    // a1 / a3: row g+8 (lo part)
+                // weights rounded to f16 (relative error 2^-12, well inside the output tolerance); the
+                // bias term uses the rounded weights so that it cancels exactly
+                const uint32_t wb = pack_half2(pw[j][0] * vs[mt][j][0], pw[j][1] * vs[mt][j][1]);
+                const float2 wf = unpack_half2(wb);
+                lb[mt] += wf.x + wf.y;
+                pa[j >> 1][(j & 1) * 2] = wb;             // a0 / a2: row g
+                pa[j >> 1][(j & 1) * 2 + 1] = 0u;         // a1 / a3: row g+8 unused
             }
 #pragma unroll
             for (int kstep = 0; kstep < 2; kstep++) {
@@ -319,11 +329,14 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
             }
         }
 
-        // ---- refill this stage -------------------------------------------------------------
+        // ---- the last warp to finish with this stage refills it -------------------------------
         __syncwarp();
         if (lane == 0 && i + STAGES < n_tiles) {
-            ptx::fence_proxy_async();
-            issue(i + STAGES);
+            if (atomicAdd(&done_cnt[s], 1) == nkv - 1) {
+                done_cnt[s] = 0;
+                ptx::fence_proxy_async();
+                issue(i + STAGES);
+            }
         }
     }
     if (failed) {
@@ -351,10 +364,10 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
             // chunk 2*lane_blk + lc of the M-tile holds this lane's rows; select without a
             // lane-dependent array index (that would push the accumulators into local memory)
             const int d0 = 64 * mt + 16 * (2 * lane_blk + lc) + 4 * tig;
-            float o0 = (lane_blk ? acc[mt][2 + lc][0][0] + acc[mt][2 + lc][0][2] : acc[mt][lc][0][0] + acc[mt][lc][0][2]) - bias;   // channel d0
-            float o1 = (lane_blk ? acc[mt][2 + lc][1][0] + acc[mt][2 + lc][1][2] : acc[mt][lc][1][0] + acc[mt][lc][1][2]) - bias;   // d0 + 1
-            float o2 = (lane_blk ? acc[mt][2 + lc][0][1] + acc[mt][2 + lc][0][3] : acc[mt][lc][0][1] + acc[mt][lc][0][3]) - bias;   // d0 + 2
-            float o3 = (lane_blk ? acc[mt][2 + lc][1][1] + acc[mt][2 + lc][1][3] : acc[mt][lc][1][1] + acc[mt][lc][1][3]) - bias;   // d0 + 3
+            float o0 = (lane_blk ? acc[mt][2 + lc][0][0] : acc[mt][lc][0][0]) - bias;   // channel d0
+            float o1 = (lane_blk ? acc[mt][2 + lc][1][0] : acc[mt][lc][1][0]) - bias;   // d0 + 1
+            float o2 = (lane_blk ? acc[mt][2 + lc][0][1] : acc[mt][lc][0][1]) - bias;   // d0 + 2
+            float o3 = (lane_blk ? acc[mt][2 + lc][1][1] : acc[mt][lc][1][1]) - bias;   // d0 + 3
             if (final_out) {
                 *reinterpret_cast<float4*>(p.out + row * HD + d0) = make_float4(o0 * inv_l, o1 * inv_l, o2 * inv_l, o3 * inv_l);
             } else {
@@ -374,8 +387,10 @@ extern int flare_launch_merge_work(flare_attn_ctx* ctx, const float* work, int n
 
 bool flare_decode_q8_supported(const DecodeArgs& a) {
     const int hd = a.kv.head_dim, nkv = a.kv.num_kv_heads;
+    // every stage must start on a 1024-byte boundary (swizzle) and the scale tile on 16 bytes
+    const size_t stage = (size_t)nkv * 2 * T * hd + 2 * (size_t)T * nkv * (hd / 32) * 2;
     return a.kv.dtype == FLARE_KV_Q8_0 && (hd == 64 || hd == 128) && a.n_q == 1 && nkv <= 8 &&
-           a.num_heads / nkv <= 4 && a.kmap != nullptr;
+           a.num_heads / nkv <= 4 && a.kmap != nullptr && stage % 1024 == 0;
 }
 
 int flare_launch_decode_q8(flare_attn_ctx* ctx, const DecodeArgs& a) {
@@ -394,7 +409,9 @@ int flare_launch_decode_q8(flare_attn_ctx* ctx, const DecodeArgs& a) {
     if (p.range_max < 0) p.range_max = 0;
     p.err = ctx->d_err;
 
-    const size_t smem = (size_t)nkv * STAGES * 2 * T * hd + 1024;
+    p.whole_rows = a.whole_rows;
+    const size_t stage = (size_t)nkv * 2 * T * hd + 2 * (size_t)T * nkv * (hd / 32) * 2;
+    const size_t smem = STAGES * stage + 1024;
     const int ctas_per_sm = smem <= 110 * 1024 ? 2 : 1;
     // one wave: as many splits as fit without a second, partly filled wave
     int n_split = (ctx->sm_count * ctas_per_sm) / a.batch;
@@ -412,7 +429,7 @@ int flare_launch_decode_q8(flare_attn_ctx* ctx, const DecodeArgs& a) {
     static bool attr_done[64][2] = {};
     bool& done = attr_done[ctx->device & 63][hd == 128];
     if (!done) {
-        const int max_smem = 8 * STAGES * 2 * T * hd + 1024;
+        const int max_smem = STAGES * (8 * 2 * T * hd + 2 * T * 8 * (hd / 32) * 2) + 1024;
         if (hd == 64) FLARE_CUDA_OK(ctx, cudaFuncSetAttribute(decode_q8_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
         else FLARE_CUDA_OK(ctx, cudaFuncSetAttribute(decode_q8_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
         done = true;
