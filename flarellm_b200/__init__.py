@@ -133,7 +133,14 @@ class Engine:
             raise FlareError(st, self.L.flare_attn_last_error(self.h).decode())
 
     def set_stream(self, cuda_stream):
-        self.check(self.L.flare_attn_set_stream(self.h, cuda_stream))
+        """Run on a caller-owned stream.  A handle of 0 is CUDA's legacy default stream (what
+        ``torch.cuda.current_stream().cuda_stream`` is unless a side stream is current); the C ABI
+        reserves NULL for "back to the context's own stream", so 0 is passed as cudaStreamLegacy."""
+        CUDA_STREAM_LEGACY = 1
+        self.check(self.L.flare_attn_set_stream(self.h, cuda_stream if cuda_stream else CUDA_STREAM_LEGACY))
+
+    def use_own_stream(self):
+        self.check(self.L.flare_attn_set_stream(self.h, None))
 
     def sync(self):
         self.check(self.L.flare_attn_sync(self.h))

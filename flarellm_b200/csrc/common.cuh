@@ -30,7 +30,13 @@ struct flare_attn_ctx {
     void* d_misc = nullptr;      size_t misc_bytes = 0;     // attend_len and other small arrays
     void* h_pinned = nullptr;    size_t pinned_bytes = 0;
     uint64_t small_counter = 0;
+    std::vector<int> small_last;       // host copy of the last uploaded (ring, attend) arrays
+    const void* small_last_dev = nullptr;
     cudaEvent_t small_events[FLARE_SMALL_SLOTS] = {};
+    int work_phase = 0;              // which half of d_work the last split-KV launch used
+    // true while the last kernel put on the stream is one that never writes a cache or q, so that the
+    // next decode kernel may overlap its prologue with it (programmatic dependent launch)
+    bool last_launch_overlappable = false;
     int* d_err = nullptr;            // device word a kernel sets when a bounded wait gives up
     int sm_count = 148;
     flare_kv* backend_kv = nullptr;  // cache created by flare_backend_init_gpu_kv_cache
@@ -71,6 +77,7 @@ int flare_set_error(flare_attn_ctx* ctx, int code, const char* fmt, ...);
 #define FLARE_LAUNCH_CHECK(ctx)                                                            \
     do {                                                                                   \
         (ctx)->launches++;                                                                 \
+        (ctx)->last_launch_overlappable = false;                                                                 \
         cudaError_t _e = cudaGetLastError();                                               \
         if (_e != cudaSuccess)                                                             \
             return flare_set_error((ctx), FLARE_ERR_CUDA, "kernel launch failed: %s (%s:%d)", \

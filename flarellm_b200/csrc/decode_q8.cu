@@ -29,6 +29,7 @@ namespace {
 
 constexpr int T = 32;            // slots per tile
 constexpr int STAGES = 3;
+constexpr int L2_AHEAD = 0;      // tiles requested into L2 ahead of the shared-memory copy (0: off; measured slower)
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kQFix = 16256.0f;     // 127 * 128: |Qint| <= 16256 = 128 * limb0 + limb1
 
@@ -77,6 +78,44 @@ __device__ __forceinline__ float2 unpack_half2(uint32_t u) {
     asm("{\n\t.reg .f16 lo, hi;\n\tmov.b32 {lo, hi}, %2;\n\tcvt.f32.f16 %0, lo;\n\tcvt.f32.f16 %1, hi;\n\t}"
         : "=f"(f.x), "=f"(f.y) : "r"(u));
     return f;
+}
+
+// Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute
+// may start while its predecessor in the stream is still running; pdl_wait() blocks until the
+// predecessor has completed and its writes are visible, pdl_trigger() lets the successor start.
+// Both are no-ops for an ordinary launch.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Log-sum-exp merge of the split partials of this path ([row][split][HD + 2], reference max in
+// log2 units); one CTA per (sequence, head) row.
+__global__ void merge_q8_kernel(const float* __restrict__ work, int n_split, int hd, float* __restrict__ out,
+                                int want_partial) {
+    pdl_trigger();          // the next layer's kernel may begin its prologue
+    pdl_wait();             // the decode kernel has written every partial
+    const int row = blockIdx.x;
+    const float* base = work + (size_t)row * n_split * (hd + 2);
+    float mm = -CUDART_INF_F;
+    for (int r = 0; r < n_split; r++)
+        if (base[r * (hd + 2) + 1] > 0.0f) mm = fmaxf(mm, base[r * (hd + 2)]);
+    float ll = 0.0f;
+    for (int r = 0; r < n_split; r++) {
+        const float* pr = base + r * (hd + 2);
+        if (pr[1] > 0.0f) ll += pr[1] * fast_exp2(pr[0] - mm);
+    }
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+        float acc = 0.0f;
+        for (int r = 0; r < n_split; r++) {
+            const float* pr = base + r * (hd + 2);
+            if (pr[1] > 0.0f) acc += pr[2 + d] * fast_exp2(pr[0] - mm);
+        }
+        if (want_partial) out[(size_t)row * (hd + 2) + 2 + d] = acc;
+        else out[(size_t)row * hd + d] = ll > 0.0f ? acc / ll : 0.0f;
+    }
+    if (want_partial && threadIdx.x == 0) {
+        out[(size_t)row * (hd + 2)] = mm * 0.6931471805599453f;
+        out[(size_t)row * (hd + 2) + 1] = ll;
+    }
 }
 
 template <int HD>
@@ -133,13 +172,32 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
         ptx::bulk_load(st + 2 * payload, ksg + (size_t)slot0 * bpr * 2, sbytes, &full_bar[s]);
         ptx::bulk_load(st + 2 * payload + scale_tile, vsg + (size_t)slot0 * bpr * 2, sbytes, &full_bar[s]);
     };
+    // Shared memory can hold only ~2 tiles in flight per CTA, too few bytes to cover DRAM latency at
+    // full bandwidth; tiles further ahead are therefore pulled into L2 first.
+    auto prefetch = [&](int i) {
+        const int slot0 = (t_begin + i) * T;
+        if (p.whole_rows) {
+            ptx::tma_prefetch_l2_4d(&kmap, 0, slot0, 0, p.layer_seq0 + b);
+            ptx::tma_prefetch_l2_4d(&vmap, 0, slot0, 0, p.layer_seq0 + b);
+        } else {
+            for (int h = 0; h < nkv; h++) {
+                ptx::tma_prefetch_l2_4d(&kmap, 0, h, slot0, p.layer_seq0 + b);
+                ptx::tma_prefetch_l2_4d(&vmap, 0, h, slot0, p.layer_seq0 + b);
+            }
+        }
+    };
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) { ptx::mbar_init(&full_bar[s], 1); done_cnt[s] = 0; }
         ptx::fence_barrier_init();
         ptx::fence_proxy_async();
         for (int i = 0; i < STAGES && i < n_tiles; i++) issue(i);
+        for (int i = STAGES; i < STAGES + L2_AHEAD && i < n_tiles; i++) prefetch(i);
     }
     __syncthreads();
+
+    // The K/V tiles requested above do not depend on the previous kernel in the stream (the previous
+    // layer's attention); q does.
+    pdl_wait();
 
     // ---- q as two int8 limbs per head, laid out as the A operand of m16n8k32 --------------
     const int hq = g & 3;                          // query head of this lane within the group
@@ -336,9 +394,11 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
                 done_cnt[s] = 0;
                 ptx::fence_proxy_async();
                 issue(i + STAGES);
+                if (i + STAGES + L2_AHEAD < n_tiles) prefetch(i + STAGES + L2_AHEAD);
             }
         }
     }
+    pdl_trigger();          // the merge kernel may be scheduled; it waits for this grid to finish
     if (failed) {
         if (lane == 0) atomicExch(p.err, FLARE_ERR_TIMEOUT);
         return;
@@ -381,10 +441,6 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
 
 }  // namespace
 
-// merge kernel shared with the general path
-extern int flare_launch_merge_work(flare_attn_ctx* ctx, const float* work, int n_split, int rows, int hd, float* out,
-                                   int want_partial);
-
 bool flare_decode_q8_supported(const DecodeArgs& a) {
     const int hd = a.kv.head_dim, nkv = a.kv.num_kv_heads;
     // every stage must start on a 1024-byte boundary (swizzle) and the scale tile on 16 bytes
@@ -420,11 +476,13 @@ int flare_launch_decode_q8(flare_attn_ctx* ctx, const DecodeArgs& a) {
     if (n_split < 1) n_split = 1;
     if (n_split > 256) n_split = 256;
     p.n_split = n_split;
-    size_t need = (size_t)rows * n_split * (hd + 2) * sizeof(float);
-    FLARE_TRY(flare_ensure(ctx, &ctx->d_work, &ctx->work_bytes, need));
-    p.work = (float*)ctx->d_work;
+    // two workspaces used alternately: the merge of one call may still be reading while the next
+    // call's decode kernel (started early, see below) writes
+    size_t need = ((size_t)rows * n_split * (hd + 2) * sizeof(float) + 255) / 256 * 256;
+    FLARE_TRY(flare_ensure(ctx, &ctx->d_work, &ctx->work_bytes, 2 * need));
+    ctx->work_phase ^= 1;
+    p.work = (float*)((char*)ctx->d_work + (size_t)ctx->work_phase * need);
 
-    dim3 grid(n_split, a.batch);
     // opt in to the large dynamic shared memory once per device
     static bool attr_done[64][2] = {};
     bool& done = attr_done[ctx->device & 63][hd == 128];
@@ -434,9 +492,33 @@ int flare_launch_decode_q8(flare_attn_ctx* ctx, const DecodeArgs& a) {
         else FLARE_CUDA_OK(ctx, cudaFuncSetAttribute(decode_q8_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
         done = true;
     }
-    if (hd == 64) decode_q8_kernel<64><<<grid, 32 * nkv, smem, ctx->stream>>>(*a.kmap, *a.vmap, p);
-    else decode_q8_kernel<128><<<grid, 32 * nkv, smem, ctx->stream>>>(*a.kmap, *a.vmap, p);
+    // Programmatic dependent launch: when the previous kernel on this stream is one of this path's
+    // own kernels (it never writes the cache), this kernel may start early and request its first
+    // K/V tiles while the predecessor drains; it waits (pdl_wait) before touching q.
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n_split, a.batch);
+    cfg.blockDim = dim3(32 * nkv);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = ctx->last_launch_overlappable ? 1 : 0;
+    if (hd == 64) FLARE_CUDA_OK(ctx, cudaLaunchKernelEx(&cfg, decode_q8_kernel<64>, *a.kmap, *a.vmap, p));
+    else FLARE_CUDA_OK(ctx, cudaLaunchKernelEx(&cfg, decode_q8_kernel<128>, *a.kmap, *a.vmap, p));
     FLARE_LAUNCH_CHECK(ctx);
-    if (n_split > 1 || a.want_partial) FLARE_TRY(flare_launch_merge_work(ctx, p.work, n_split, rows, hd, a.out, a.want_partial));
+    ctx->last_launch_overlappable = true;
+    if (n_split > 1 || a.want_partial) {
+        cudaLaunchConfig_t mcfg = {};
+        mcfg.gridDim = dim3(rows);
+        mcfg.blockDim = dim3(hd < 128 ? hd : 128);
+        mcfg.stream = ctx->stream;
+        mcfg.attrs = attr;
+        mcfg.numAttrs = 1;
+        FLARE_CUDA_OK(ctx, cudaLaunchKernelEx(&mcfg, merge_q8_kernel, (const float*)p.work, n_split, hd, a.out, a.want_partial));
+        FLARE_LAUNCH_CHECK(ctx);
+        ctx->last_launch_overlappable = true;
+    }
     return FLARE_OK;
 }

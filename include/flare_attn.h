@@ -97,7 +97,8 @@ typedef enum {
  * `device` and creates the stream all work of this context runs on. */
 FLARE_API int flare_attn_create(int device, flare_attn_ctx** out_ctx);
 FLARE_API int flare_attn_destroy(flare_attn_ctx* ctx);
-/* Run on a caller-owned cudaStream_t instead (NULL restores the context's own). */
+/* Run on a caller-owned cudaStream_t instead.  NULL restores the context's own stream; to run
+ * on CUDA's legacy default stream pass cudaStreamLegacy, not 0. */
 FLARE_API int flare_attn_set_stream(flare_attn_ctx* ctx, void* cuda_stream);
 /* Replaces the blocking readback device.poll(Maintain::Wait) (flare-gpu/src/backend.rs:417). */
 FLARE_API int flare_attn_sync(flare_attn_ctx* ctx);
