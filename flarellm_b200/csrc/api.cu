@@ -103,6 +103,7 @@ int flare_attn_destroy(flare_attn_ctx* ctx) {
     cudaStreamSynchronize(ctx->stream);
     if (ctx->backend_kv) flare_kv_free(ctx->backend_kv);
     cudaFree(ctx->d_err);
+    cudaFree(ctx->d_misc2); cudaFree(ctx->d_conv);
     cudaFree(ctx->d_work); cudaFree(ctx->d_stage_in); cudaFree(ctx->d_stage_out); cudaFree(ctx->d_misc);
     if (ctx->h_pinned) cudaFreeHost(ctx->h_pinned);
     for (int i = 0; i < FLARE_SMALL_SLOTS; i++) if (ctx->small_events[i]) cudaEventDestroy(ctx->small_events[i]);
@@ -513,6 +514,7 @@ static int decode_common(flare_attn_ctx* ctx, flare_kv* kv, int layer, int num_h
     DecodeArgs a;
     a.kv = flare_layer_view(kv, layer);
     a.layer = layer;
+    a.window = 0;
     a.kmap = kv->has_maps ? &kv->kq_map : nullptr;
     a.vmap = kv->has_maps ? &kv->vq_map : nullptr;
     a.whole_rows = kv->maps_whole_rows ? 1 : 0;

@@ -28,6 +28,8 @@ struct flare_attn_ctx {
     void* d_stage_in = nullptr;  size_t stage_in_bytes = 0; // device copy of host q / K / V
     void* d_stage_out = nullptr; size_t stage_out_bytes = 0;
     void* d_misc = nullptr;      size_t misc_bytes = 0;     // attend_len and other small arrays
+    void* d_misc2 = nullptr;     size_t misc2_bytes = 0;    // small arrays of the prefill path
+    void* d_conv = nullptr;      size_t conv_bytes = 0;     // dtype-converted prefill operands
     void* h_pinned = nullptr;    size_t pinned_bytes = 0;
     uint64_t small_counter = 0;
     std::vector<int> small_last;       // host copy of the last uploaded (ring, attend) arrays
@@ -107,6 +109,7 @@ struct DecodeArgs {
     int want_partial;          // 1: write [m, l, o] unnormalised
     int causal_q;              // 1: query i of n_q reads attend_len - (n_q-1-i) slots; 0: all read attend_len
     int max_attend;            // max over batch of attend_len (host-known upper bound)
+    int window;                // > 0: every query reads at most its newest `window` slots (sliding-window prefill)
     int layer;
     const CUtensorMap *kmap, *vmap;   // Q8_0 payload maps (null when the cache has none)
     int whole_rows;                   // maps deliver [head][32 slots][head_dim] in one copy

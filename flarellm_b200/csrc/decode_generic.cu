@@ -138,7 +138,7 @@ struct DecodeParams {
     float* work;       // ... else partials [row][n_split][hd+2], m in log2 units
     const int* attend_len;
     const int2* ring;
-    int n_q, num_heads, n_chunks, slot_begin, slot_end, want_partial, range_max, causal_q;
+    int n_q, num_heads, n_chunks, slot_begin, slot_end, want_partial, range_max, causal_q, window;
 };
 
 __device__ __forceinline__ SeqKv seq_view(const DecodeParams& p, int b, int n_q) {
@@ -171,6 +171,7 @@ __global__ void __launch_bounds__(128) decode_splitkv_kernel(DecodeParams p) {
     const SeqKv s = seq_view(p, b, p.n_q);
     int n = p.attend_len[b] - (p.causal_q ? (p.n_q - 1 - qi) : 0);
     int lo = 0, hi = n;
+    if (p.window > 0) lo = max(lo, n - p.window);
     if (p.slot_end >= 0) { lo = max(lo, p.slot_begin); hi = min(hi, p.slot_end); }
     const int base = p.slot_end >= 0 ? p.slot_begin : 0;
     const int per = (p.range_max + n_split - 1) / n_split;
@@ -282,6 +283,7 @@ __global__ void decode_f32_anyshape_kernel(DecodeParams p) {
     const int kvh = h / (p.num_heads / p.kv.num_kv_heads);
     int n = p.attend_len[b] - (p.causal_q ? (p.n_q - 1 - qi) : 0);
     int lo = 0, hi = n;
+    if (p.window > 0) lo = max(lo, n - p.window);
     if (p.slot_end >= 0) { lo = max(lo, p.slot_begin); hi = min(hi, p.slot_end); }
     const float* K = reinterpret_cast<const float*>(p.kv.plane[FLARE_PLANE_K] + (size_t)b * p.kv.stride[FLARE_PLANE_K]);
     const float* V = reinterpret_cast<const float*>(p.kv.plane[FLARE_PLANE_V] + (size_t)b * p.kv.stride[FLARE_PLANE_V]);
@@ -407,6 +409,7 @@ int flare_launch_decode_generic(flare_attn_ctx* ctx, const DecodeArgs& a) {
     p.attend_len = a.attend_len; p.ring = a.ring;
     p.n_q = a.n_q; p.num_heads = a.num_heads;
     p.slot_begin = a.slot_begin; p.slot_end = a.slot_end; p.want_partial = a.want_partial; p.causal_q = a.causal_q;
+    p.window = a.window;
     p.range_max = a.slot_end >= 0 ? (a.slot_end - a.slot_begin) : a.max_attend;
     if (p.range_max < 0) p.range_max = 0;
 
@@ -535,7 +538,7 @@ int flare_decode_noalloc(flare_attn_ctx* ctx, const flare_kv* kv, int layer, int
     p.q = q_dev; p.out = out_dev; p.work = (float*)(scratch + kSmallBytes);
     p.attend_len = d_att; p.ring = (const int2*)scratch;
     p.n_q = n_q; p.num_heads = num_heads;
-    p.slot_begin = 0; p.slot_end = -1; p.want_partial = 0; p.causal_q = 1;
+    p.slot_begin = 0; p.slot_end = -1; p.want_partial = 0; p.causal_q = 1; p.window = 0;
     p.range_max = max_attend;
     const int gc = G >= 4 ? 4 : G;
     p.n_chunks = (G + gc - 1) / gc;
