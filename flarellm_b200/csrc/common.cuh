@@ -130,6 +130,8 @@ struct PrefillArgs {
     int in_dtype, out_dtype, batch, seq_len, num_heads, num_kv_heads, head_dim, window;
 };
 int flare_launch_prefill(flare_attn_ctx* ctx, const PrefillArgs& a);
+int flare_launch_prefill_pp(flare_attn_ctx* ctx, const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm,
+                            const PrefillArgs& a);
 
 int flare_launch_kv_write(flare_kv* kv, int layer, int seq, int64_t first_abs_position, int64_t length_before,
                           int n_rows, const float* d_key, const float* d_value);
