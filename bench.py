@@ -150,8 +150,231 @@ def run_reference(args):
         "wall_s": wall}))
 
 
+# --------------------------------------------------------------------------------------------
+# the other configurations of BASELINE.json (selected with --case; the default line is `decode`)
+# --------------------------------------------------------------------------------------------
+def _setup(args):
+    import torch
+    import flarellm_b200 as fb
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    eng = fb.Engine(local)
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    eng.set_stream(stream.cuda_stream)
+    return torch, fb, dist, eng, stream, rank, world, local
+
+
+def _timed(torch, dist, stream, fn, steps, warmup):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier(); torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(steps):
+        fn()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier(); torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    if dist is not None:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms / steps
+
+
+def case_prefill(args):
+    """BASELINE.json configs[3]: Llama-3-8B-shaped causal prefill, bf16, S 4096, batch 4 per GPU
+    (--window 4096: the sliding-window variant at S 8192).  Tensor-bound: flops over causal pairs."""
+    torch, fb, dist, eng, stream, rank, world, local = _setup(args)
+    B, nh, nkv, hd = 4, 32, 8, 128
+    W = args.window
+    S = 8192 if W else 4096
+    gen = torch.Generator(device="cuda").manual_seed(3 + rank)
+    q = (torch.randn(B, S, nh, hd, device="cuda", generator=gen) * 0.5).bfloat16()
+    k = (torch.randn(B, S, nkv, hd, device="cuda", generator=gen) * 0.5).bfloat16()
+    v = (torch.randn(B, S, nkv, hd, device="cuda", generator=gen) * 0.5).bfloat16()
+    o = torch.empty(B, S, nh, hd, device="cuda", dtype=torch.bfloat16)
+    fn = lambda: eng.prefill(q.data_ptr(), k.data_ptr(), v.data_ptr(), B, S, nh, nkv, hd, window=W,
+                             in_dtype=fb.DT_BF16, out_dtype=fb.DT_BF16, out=o.data_ptr())
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    ms = _timed(torch, dist, stream, fn, args.steps, max(3, args.warmup))
+    clocks = sampler.stop() if sampler else None
+    pairs = sum(min(t + 1, W) for t in range(S)) if W else S * (S + 1) // 2
+    flops = 4 * B * nh * hd * pairs
+    if rank == 0:
+        peaks, kind = measured_peaks()
+        tf = flops / (ms * 1e-3) / 1e12
+        check = None
+        if not args.no_cpu:
+            import oracle
+            f32 = lambda t: t[0].float().cpu().numpy().reshape(S, -1)
+            want = oracle.prefill(f32(q), f32(k), f32(v), S, nh, nkv, hd, window=W, row_start=5, row_step=251,
+                                  threads=oracle.max_threads())
+            rows = ~np.isnan(want[:, 0])
+            err = np.abs(f32(o)[rows] - want[rows])
+            check = {"rows_checked": int(rows.sum()), "max_abs_err": float(err.max()),
+                     "within_tolerance": bool(np.all(err <= 2e-3 + (1e-3 + 2.0 ** -8) * np.abs(want[rows])))}
+        print(json.dumps({
+            "metric": "prefill_attn_tflops", "value": world * tf, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"llama-3-8b-shaped causal prefill attention: 32q/8kv heads, head_dim 128, S {S}, batch {B}/GPU"
+                                   + (f", sliding window {W}" if W else ""), "flops": "4*B*heads*head_dim*attended (q,k) pairs"},
+            "tokens_per_s": world * B * S / (ms * 1e-3),
+            "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                         "frac": tf / peaks["bf16_tflops"], "traffic": None, "peak_source": kind},
+            "clocks": clocks, "parity_check": check}))
+    eng.close()
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def case_longctx(args):
+    """BASELINE.json configs[4]: one sequence, 131072 cached positions, Q8_0, Llama-3-8B shape, the slot
+    range split evenly over the ranks; per-rank (m, l, o) records all-gathered (NCCL) and merged."""
+    torch, fb, dist, eng, stream, rank, world, local = _setup(args)
+    from flarellm_b200.splitkv import SplitKvDecoder, shard_slots
+    nh, nkv, hd, total = 32, 8, 128, 131072
+    lo, hi = shard_slots(total, world, rank)
+    n_local = hi - lo
+    kv = eng.kv_alloc(1, 1, max(n_local, 32), nkv, hd, fb.KV_Q8_0)
+    gen = torch.Generator(device="cuda").manual_seed(4)          # every rank draws the whole sequence's stream
+    chunk = 8192
+    for c0 in range(0, total, chunk):
+        k = torch.randn(chunk, nkv * hd, device="cuda", generator=gen)
+        v = torch.randn(chunk, nkv * hd, device="cuda", generator=gen)
+        a, b_ = max(c0, lo), min(c0 + chunk, hi)
+        if b_ > a:
+            kv.append(0, 0, k[a - c0:b_ - c0].contiguous().data_ptr(), v[a - c0:b_ - c0].contiguous().data_ptr(), n_rows=b_ - a)
+            kv.advance(0, b_ - a)
+    q = torch.randn(1, 1, nh, hd, device="cuda", generator=gen) / (hd ** 0.5) * 4
+    dec = SplitKvDecoder(eng, kv, nh, n_local)
+    out = None
+
+    def fn():
+        nonlocal out
+        out = dec.decode(0, q)
+
+    def fn_kernel_only():
+        dec.partial_fn(0, q)
+    ms = _timed(torch, dist, stream, fn, args.steps, max(3, args.warmup))
+    ms_k = _timed(torch, dist, stream, fn_kernel_only, args.steps, 3)
+    row_bytes = nkv * hd + nkv * hd // 32 * 2
+    layer_bytes = total * 2 * row_bytes
+    if rank == 0:
+        peaks, kind = measured_peaks()
+        ach = layer_bytes / world / (ms_k * 1e-3) / 1e9
+        print(json.dumps({
+            "metric": "longctx_decode_attn_tokens_per_s", "value": 1.0 / (ms * 1e-3), "unit": "tok/s (one layer)", "n_gpus": world,
+            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "llama-3-8b-shaped single-sequence decode attention, Q8_0, 131072 slots, 1 layer",
+                       "parallelism": f"slot range split over {world} GPU(s); all-gather of {nh * (hd + 2) * 4} B per rank + merge"},
+            "kernel_only_ms": ms_k, "hbm_gbs_total": layer_bytes / (ms * 1e-3) / 1e9,
+            "roofline": {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"],
+                         "traffic": None, "peak_source": kind,
+                         "per_launch": f"{layer_bytes // world} algorithmic KV bytes per rank / partial-kernel time (no collective)"}}))
+    kv.free()
+    eng.close()
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def case_kivi(args):
+    """BASELINE.json configs[2]: 2-bit group-32 KIVI cache, context 32768, batch 16, one layer."""
+    torch, fb, dist, eng, stream, rank, world, local = _setup(args)
+    nh, nkv, hd, ctx, B = 32, 8, 64, 32768, 16
+    kv = eng.kv_alloc(1, B, ctx, nkv, hd, fb.KV_KIVI_G32)
+    gen = torch.Generator(device="cuda").manual_seed(2 + rank)
+    for b in range(B):
+        k = torch.randn(ctx - 1, nkv * hd, device="cuda", generator=gen)
+        v = torch.randn(ctx - 1, nkv * hd, device="cuda", generator=gen)
+        outl = torch.randperm(nkv * hd, device="cuda", generator=gen)[:6]      # 1 % of key channels x8
+        k[:, outl] *= 8
+        kv.append(0, b, k.data_ptr(), v.data_ptr(), n_rows=ctx - 1)
+        kv.advance(b, ctx - 1)
+    q = torch.randn(B, 1, nh, hd, device="cuda", generator=gen) * 0.125
+    knew = torch.randn(B, nkv * hd, device="cuda", generator=gen)
+    o = torch.empty(B, 1, nh, hd, device="cuda")
+    kv.write_step(0, knew.data_ptr(), knew.data_ptr())
+    fn = lambda: eng.decode(kv, 0, nh, q.data_ptr(), out=o.data_ptr())
+    ms = _timed(torch, dist, stream, fn, args.steps, max(3, args.warmup))
+    per_seq = (ctx - 128) * 384 + 128 * nkv * hd * 2 * 2
+    nbytes = B * per_seq
+    if rank == 0:
+        peaks, kind = measured_peaks()
+        ach = nbytes / (ms * 1e-3) / 1e9
+        print(json.dumps({
+            "metric": "kivi_decode_attn_tokens_per_s", "value": world * B / (ms * 1e-3), "unit": "tok/s (one layer)", "n_gpus": world,
+            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "KIVI 2-bit (group 32, f16 scale+zero, 128-token f16 residual) decode attention, 32q/8kv, head_dim 64, ctx 32768, batch 16, 1 layer"},
+            "roofline": {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"],
+                         "traffic": None, "peak_source": kind, "per_launch": f"{nbytes} algorithmic bytes (384 B per quantised token + residual rows)"}}))
+    kv.free()
+    eng.close()
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def case_f32(args):
+    """BASELINE.json configs[0]: SmolLM2-135M-shaped f32 decode, 512 cached + 1, batch 1: latency."""
+    torch, fb, dist, eng, stream, rank, world, local = _setup(args)
+    nh, nkv, hd, L = 9, 3, 64, 512
+    rng = np.random.default_rng(0)
+    q = rng.standard_normal(nh * hd, dtype=np.float32) * np.float32(0.125)
+    k = rng.standard_normal((L + 1, nkv * hd), dtype=np.float32) * np.float32(0.125)
+    v = rng.standard_normal((L + 1, nkv * hd), dtype=np.float32) * np.float32(0.125)
+    kv = eng.kv_alloc(1, 1, 1024, nkv, hd, fb.KV_F32)
+    kv.append(0, 0, k[:L], v[:L]); kv.advance(0, L); kv.write(0, 0, L, k[L], v[L])
+    qd = torch.from_numpy(q).cuda()
+    od = torch.empty(nh * hd, device="cuda")
+    fn = lambda: eng.decode(kv, 0, nh, qd.data_ptr(), out=od.data_ptr())
+    ms = _timed(torch, dist, stream, fn, max(args.steps, 200), 10)
+    t0 = time.perf_counter()
+    for _ in range(200):
+        host = eng.decode(kv, 0, nh, q.reshape(1, 1, nh, hd))
+    ms_host = (time.perf_counter() - t0) / 200 * 1e3
+    if rank == 0:
+        import oracle
+        want = oracle.gqa_decode(q, k, v, nh, nkv, hd, L + 1)
+        t0 = time.perf_counter()
+        for _ in range(200):
+            oracle.gqa_decode(q, k, v, nh, nkv, hd, L + 1)
+        ms_cpu = (time.perf_counter() - t0) / 200 * 1e3
+        err = float(np.max(np.abs(host.reshape(-1) - want)))
+        print(json.dumps({
+            "metric": "f32_decode_attn_latency_us", "value": ms * 1e3, "unit": "us per call (device, stream-pipelined)", "n_gpus": 1,
+            "steps": max(args.steps, 200), "warmup": 10, "ms_per_step": ms, "higher_is_better": False, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "smollm2-135m-shaped f32 decode attention: 9q/3kv heads, head_dim 64, 512 cached + 1, batch 1, 1 layer",
+                       "note": "787,968 B of K+V: latency-bound, a roofline fraction is not meaningful"},
+            "host_call_us": ms_host * 1e3, "cpu_oracle_us": ms_cpu * 1e3, "max_abs_err": err}))
+    kv.free()
+    eng.close()
+
+
+CASES = {"prefill": case_prefill, "longctx": case_longctx, "kivi": case_kivi, "f32": case_f32}
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--case", default="decode", choices=["decode"] + sorted(CASES))
+    ap.add_argument("--window", type=int, default=0, help="prefill: sliding window (4096 selects the S=8192 variant)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
@@ -162,6 +385,8 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.case != "decode":
+        return CASES[args.case](args)
 
     import torch
     import flarellm_b200 as fb
