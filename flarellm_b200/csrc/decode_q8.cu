@@ -88,31 +88,48 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // Log-sum-exp merge of the split partials of this path ([row][split][HD + 2], reference max in
-// log2 units); one CTA per (sequence, head) row.
+// log2 units); one CTA per (sequence, head) row.  The per-split weights are computed once, in
+// parallel over the splits, so that a long-context call with more than a hundred splits does not
+// serialise on dependent loads.
 __global__ void merge_q8_kernel(const float* __restrict__ work, int n_split, int hd, float* __restrict__ out,
                                 int want_partial) {
+    __shared__ float s_w[256];          // weight of each split (n_split <= 256)
+    __shared__ float s_red[8];
     pdl_trigger();          // the next layer's kernel may begin its prologue
     pdl_wait();             // the decode kernel has written every partial
-    const int row = blockIdx.x;
+    const int row = blockIdx.x, tid = threadIdx.x, nthr = blockDim.x;
     const float* base = work + (size_t)row * n_split * (hd + 2);
+    // reference max over the non-empty splits
     float mm = -CUDART_INF_F;
-    for (int r = 0; r < n_split; r++)
+    for (int r = tid; r < n_split; r += nthr)
         if (base[r * (hd + 2) + 1] > 0.0f) mm = fmaxf(mm, base[r * (hd + 2)]);
+#pragma unroll
+    for (int off = 16; off; off >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, off));
+    if ((tid & 31) == 0) s_red[tid >> 5] = mm;
+    __syncthreads();
+    mm = s_red[0];
+    for (int w = 1; w < (nthr + 31) / 32; w++) mm = fmaxf(mm, s_red[w]);
+    __syncthreads();
     float ll = 0.0f;
-    for (int r = 0; r < n_split; r++) {
-        const float* pr = base + r * (hd + 2);
-        if (pr[1] > 0.0f) ll += pr[1] * fast_exp2(pr[0] - mm);
+    for (int r = tid; r < n_split; r += nthr) {
+        const float l_r = base[r * (hd + 2) + 1];
+        const float w = l_r > 0.0f ? fast_exp2(base[r * (hd + 2)] - mm) : 0.0f;
+        s_w[r] = w;
+        ll += l_r * w;
     }
-    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+#pragma unroll
+    for (int off = 16; off; off >>= 1) ll += __shfl_xor_sync(0xffffffffu, ll, off);
+    if ((tid & 31) == 0) s_red[tid >> 5] = ll;
+    __syncthreads();
+    ll = 0.0f;
+    for (int w = 0; w < (nthr + 31) / 32; w++) ll += s_red[w];
+    for (int d = tid; d < hd; d += nthr) {
         float acc = 0.0f;
-        for (int r = 0; r < n_split; r++) {
-            const float* pr = base + r * (hd + 2);
-            if (pr[1] > 0.0f) acc += pr[2 + d] * fast_exp2(pr[0] - mm);
-        }
+        for (int r = 0; r < n_split; r++) acc = fmaf(base[r * (hd + 2) + 2 + d], s_w[r], acc);
         if (want_partial) out[(size_t)row * (hd + 2) + 2 + d] = acc;
         else out[(size_t)row * hd + d] = ll > 0.0f ? acc / ll : 0.0f;
     }
-    if (want_partial && threadIdx.x == 0) {
+    if (want_partial && tid == 0) {
         out[(size_t)row * (hd + 2)] = mm * 0.6931471805599453f;
         out[(size_t)row * (hd + 2) + 1] = ll;
     }
