@@ -16,7 +16,8 @@ import os
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libflare_attn.so")
+# FLARE_ATTN_LIB selects another build of the same library (e.g. a variant under test)
+LIB_PATH = os.environ.get("FLARE_ATTN_LIB") or os.path.join(_HERE, "libflare_attn.so")
 
 OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_OOM, ERR_CUDA, ERR_TIMEOUT, ERR_STATE = range(7)
 KV_F32, KV_Q8_0, KV_KIVI_REF, KV_KIVI_G32 = range(4)

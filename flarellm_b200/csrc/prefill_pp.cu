@@ -22,6 +22,9 @@ using namespace tc5;
 namespace {
 
 constexpr int BN = 128;
+#ifndef POLY_EVERY
+#define POLY_EVERY 0      // one exponential in POLY_EVERY is evaluated on the FMA pipe (0: none; measured: none is fastest)
+#endif
 constexpr uint32_t kWaitLimit = 1u << 20;
 
 struct PPParams {
@@ -62,7 +65,37 @@ __device__ __forceinline__ void tile_range(int r0, int S, int window, int& j0, i
     j1 = last_row / BN + 1;
 }
 
+// 2^x for x <= 0 on the FMA pipe (Cody-Waite split + cubic), used for part of the elements so that
+// the MUFU is not the only unit computing exponentials.  Relative error < 1e-4, far below the bf16
+// rounding of P (2^-9).
+__device__ __forceinline__ float exp2_poly(float x) {
+    x = fmaxf(x, -126.0f);                                   // also maps -inf (masked) to ~1e-38
+    const float xr = x + 12582912.0f;                        // 1.5 * 2^23: integer part lands in the low mantissa bits
+    const float f = x - (xr - 12582912.0f);                  // f in [-0.5, 0.5]
+    float p = fmaf(f, 0.055170249f, 0.24260791f);            // minimax cubic of 2^f on [-0.5, 0.5], rel. error 7.5e-5
+    p = fmaf(p, f, 0.69326091f);
+    p = fmaf(p, f, 0.99992830f);
+    return __int_as_float(__float_as_int(p) + (__float_as_int(xr) << 23));
+}
+
+// packed-pair f32 arithmetic and the 3-input maximum of sm_100: half the issue slots per element
+__device__ __forceinline__ void ffma2(float& d0, float& d1, float a0, float a1, float b, float c) {
+    asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %4};\n\tmov.b64 rc, {%5, %5};\n\t"
+        "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b), "f"(c));
+}
+__device__ __forceinline__ void fadd2(float& d0, float& d1, float a0, float a1, float b0, float b1) {
+    asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tadd.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
 template <int HD>
+// 10 warps are allocated as 12 (granularity 4): 12 x 32 x 168 registers is what one SM holds
 __global__ void __launch_bounds__(320, 1) prefill_pp_kernel(const __grid_constant__ CUtensorMap qmap,
                                                             const __grid_constant__ CUtensorMap kmap,
                                                             const __grid_constant__ CUtensorMap vmap, PPParams p) {
@@ -220,9 +253,17 @@ __global__ void __launch_bounds__(320, 1) prefill_pp_kernel(const __grid_constan
                     if (col > grow || col < row_lo || col >= S) v[i] = 0xff800000u;   // -inf
                 }
             }
-            float tmax = -CUDART_INF_F;
+            // eight independent chains instead of one 128-long dependency chain
+            float mx[8];
 #pragma unroll
-            for (int i = 0; i < 128; i++) tmax = fmaxf(tmax, __uint_as_float(v[i]));
+            for (int c = 0; c < 8; c++) mx[c] = __uint_as_float(v[c]);
+#pragma unroll
+            for (int i = 8; i < 120; i += 16)
+#pragma unroll
+                for (int c = 0; c < 8; c++) mx[c] = fmax3(mx[c], __uint_as_float(v[i + c]), __uint_as_float(v[i + 8 + c]));
+#pragma unroll
+            for (int c = 0; c < 8; c++) mx[c] = fmaxf(mx[c], __uint_as_float(v[120 + c]));
+            float tmax = fmax3(fmax3(mx[0], mx[1], mx[2]), fmax3(mx[3], mx[4], mx[5]), fmaxf(mx[6], mx[7]));
             tmax *= p.scale_log2;
             const bool bump = tmax > m_ref + 8.0f;
             float alpha = 1.0f;
@@ -242,20 +283,25 @@ __global__ void __launch_bounds__(320, 1) prefill_pp_kernel(const __grid_constan
             }
             l_sum *= alpha;
             const float neg_m = (m_ref == -CUDART_INF_F) ? 0.0f : -m_ref;
-            // p = exp2(s * scale - m) -> bf16 pairs, written over the first 64 columns of S_x
+            // p = exp2(s * scale - m) -> bf16 pairs, written over the first 64 columns of S_x.  Of every
+            // two exponentials one goes to the MUFU and one to the FMA-pipe polynomial.
+            float ls[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
             for (int half = 0; half < 2; half++) {
-                uint32_t pk[32];
 #pragma unroll
                 for (int i = 0; i < 32; i++) {
-                    const float p0 = fast_exp2(fmaf(__uint_as_float(v[half * 64 + 2 * i]), p.scale_log2, neg_m));
-                    const float p1 = fast_exp2(fmaf(__uint_as_float(v[half * 64 + 2 * i + 1]), p.scale_log2, neg_m));
-                    l_sum += p0 + p1;
-                    __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
-                    pk[i] = *reinterpret_cast<uint32_t*>(&pb);
+                    float x0, x1;
+                    ffma2(x0, x1, __uint_as_float(v[half * 64 + 2 * i]), __uint_as_float(v[half * 64 + 2 * i + 1]), p.scale_log2, neg_m);
+                    const float p0 = fast_exp2(x0);
+                    const float p1 = (POLY_EVERY > 0 && (i % (POLY_EVERY / 2 > 0 ? POLY_EVERY / 2 : 1)) == 0) ? exp2_poly(x1) : fast_exp2(x1);
+                    fadd2(ls[(2 * i) & 3], ls[(2 * i + 1) & 3], ls[(2 * i) & 3], ls[(2 * i + 1) & 3], p0, p1);
+                    uint32_t w;
+                    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(w) : "f"(p1), "f"(p0));
+                    v[half * 32 + i] = w;          // packed in place: slot half*32+i was consumed already
                 }
-                tmem_st32(tS + half * 32, pk);
+                tmem_st32(tS + half * 32, *reinterpret_cast<uint32_t(*)[32]>(&v[half * 32]));
             }
+            l_sum += (ls[0] + ls[1]) + (ls[2] + ls[3]);
             tmem_wait_st();
             tc_fence_before();
             ptx::mbar_arrive(&bars->p_full[x]);
