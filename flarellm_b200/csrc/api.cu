@@ -106,6 +106,8 @@ int flare_attn_destroy(flare_attn_ctx* ctx) {
     cudaFree(ctx->d_misc2); cudaFree(ctx->d_conv);
     cudaFree(ctx->d_work); cudaFree(ctx->d_stage_in); cudaFree(ctx->d_stage_out); cudaFree(ctx->d_misc);
     if (ctx->h_pinned) cudaFreeHost(ctx->h_pinned);
+    if (ctx->h_rows) cudaFreeHost(ctx->h_rows);
+    for (int i = 0; i < FLARE_ROW_SLOTS; i++) if (ctx->rows_events[i]) cudaEventDestroy(ctx->rows_events[i]);
     for (int i = 0; i < FLARE_SMALL_SLOTS; i++) if (ctx->small_events[i]) cudaEventDestroy(ctx->small_events[i]);
     if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
     delete ctx;
@@ -242,16 +244,37 @@ static int check_layer_seq(const flare_kv* kv, int layer, int seq) {
 }
 
 // stage two host row blocks on the device; returns device pointers
+// *synced is set when the host buffers have NOT been fully consumed yet and the caller must
+// synchronise the stream before returning.
 static int stage_rows(flare_attn_ctx* ctx, const float* key, const float* value, size_t n_floats, int on_device,
-                      const float** dk, const float** dv) {
+                      const float** dk, const float** dv, bool* must_sync) {
+    *must_sync = false;
     if (on_device) { *dk = key; *dv = value; return FLARE_OK; }
     size_t bytes = n_floats * sizeof(float);
     FLARE_TRY(flare_ensure(ctx, &ctx->d_stage_in, &ctx->stage_in_bytes, 2 * bytes));
     float* d = (float*)ctx->d_stage_in;
+    *dk = d; *dv = d + n_floats;
+    if (2 * bytes <= (1u << 20)) {
+        // small: CPU copy into a page-locked slot, then a truly asynchronous transfer; nothing to wait for
+        const size_t slot_bytes = 1u << 20;
+        if (!ctx->h_rows) {
+            FLARE_CUDA_OK(ctx, cudaMallocHost(&ctx->h_rows, slot_bytes * FLARE_ROW_SLOTS));
+            ctx->rows_slot_bytes = slot_bytes;
+        }
+        const int slot = (int)(ctx->rows_counter++ % FLARE_ROW_SLOTS);
+        if (!ctx->rows_events[slot]) FLARE_CUDA_OK(ctx, cudaEventCreateWithFlags(&ctx->rows_events[slot], cudaEventDisableTiming));
+        else FLARE_CUDA_OK(ctx, cudaEventSynchronize(ctx->rows_events[slot]));
+        char* h = (char*)ctx->h_rows + (size_t)slot * slot_bytes;
+        memcpy(h, key, bytes);
+        memcpy(h + bytes, value, bytes);
+        FLARE_CUDA_OK(ctx, cudaMemcpyAsync(d, h, 2 * bytes, cudaMemcpyHostToDevice, ctx->stream));
+        FLARE_CUDA_OK(ctx, cudaEventRecord(ctx->rows_events[slot], ctx->stream));
+        ctx->last_launch_overlappable = false;
+        return FLARE_OK;
+    }
     FLARE_CUDA_OK(ctx, cudaMemcpyAsync(d, key, bytes, cudaMemcpyHostToDevice, ctx->stream));
     FLARE_CUDA_OK(ctx, cudaMemcpyAsync(d + n_floats, value, bytes, cudaMemcpyHostToDevice, ctx->stream));
-    // pageable host memory: the copy has consumed the buffer once the call returns only after a sync
-    *dk = d; *dv = d + n_floats;
+    *must_sync = true;      // the caller's (possibly pageable) buffers are still being read
     return FLARE_OK;
 }
 
@@ -262,7 +285,8 @@ int flare_kv_write_f32(flare_kv* kv, int layer, int seq, int64_t abs_position, c
     if (!key || !value || abs_position < 0) return flare_set_error(ctx, FLARE_ERR_INVALID_ARG, "flare_kv_write_f32: bad argument");
     BIND(ctx);
     const float *dk, *dv;
-    FLARE_TRY(stage_rows(ctx, key, value, kv->kv_dim, on_device, &dk, &dv));
+    bool must_sync;
+    FLARE_TRY(stage_rows(ctx, key, value, kv->kv_dim, on_device, &dk, &dv, &must_sync));
     // how many tokens are pending (written, not yet advanced) before this one
     int64_t slot = abs_position % kv->max_seq_len;
     int64_t pending = slot - kv->position[seq];
@@ -270,7 +294,7 @@ int flare_kv_write_f32(flare_kv* kv, int layer, int seq, int64_t abs_position, c
     int64_t len_before = kv->length[seq] + pending;
     if (len_before > kv->max_seq_len) len_before = kv->max_seq_len;
     FLARE_TRY(flare_launch_kv_write(kv, layer, seq, abs_position, len_before, 1, dk, dv));
-    if (!on_device) FLARE_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
+    if (must_sync) FLARE_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
     return FLARE_OK;
 }
 
@@ -282,11 +306,12 @@ int flare_kv_append_f32(flare_kv* kv, int layer, int seq, int n_rows, const floa
     if (n_rows == 0) return FLARE_OK;
     BIND(ctx);
     const float *dk, *dv;
-    FLARE_TRY(stage_rows(ctx, key, value, (size_t)n_rows * kv->kv_dim, on_device, &dk, &dv));
+    bool must_sync;
+    FLARE_TRY(stage_rows(ctx, key, value, (size_t)n_rows * kv->kv_dim, on_device, &dk, &dv, &must_sync));
     // an absolute index congruent to the ring position (and to the token count before the wrap)
     int64_t first = kv->length[seq] < kv->max_seq_len ? kv->length[seq] : kv->max_seq_len + kv->position[seq];
     FLARE_TRY(flare_launch_kv_write(kv, layer, seq, first, kv->length[seq], n_rows, dk, dv));
-    if (!on_device) FLARE_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
+    if (must_sync) FLARE_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
     return FLARE_OK;
 }
 
@@ -301,9 +326,10 @@ int flare_kv_write_step_f32(flare_kv* kv, int layer, const float* key, const flo
     const int* d_att; const int2* d_ring; int mx;
     FLARE_TRY(upload_small(ctx, kv, 1, nullptr, &d_att, &d_ring, &mx));
     const float *dk, *dv;
-    FLARE_TRY(stage_rows(ctx, key, value, (size_t)kv->batch * kv->kv_dim, on_device, &dk, &dv));
+    bool must_sync;
+    FLARE_TRY(stage_rows(ctx, key, value, (size_t)kv->batch * kv->kv_dim, on_device, &dk, &dv, &must_sync));
     FLARE_TRY(flare_launch_kv_write_step(kv, layer, d_ring, dk, dv));
-    if (!on_device) FLARE_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
+    if (must_sync) FLARE_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
     return FLARE_OK;
 }
 

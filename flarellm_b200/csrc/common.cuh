@@ -16,6 +16,7 @@
 #define FLARE_G32_RESIDUAL 128
 #define FLARE_REF_RESIDUAL 32
 #define FLARE_SMALL_SLOTS 64
+#define FLARE_ROW_SLOTS 8
 
 struct flare_attn_ctx {
     int device = 0;
@@ -31,6 +32,11 @@ struct flare_attn_ctx {
     void* d_misc2 = nullptr;     size_t misc2_bytes = 0;    // small arrays of the prefill path
     void* d_conv = nullptr;      size_t conv_bytes = 0;     // dtype-converted prefill operands
     void* h_pinned = nullptr;    size_t pinned_bytes = 0;
+    // ring of page-locked staging slots for small host inputs (new K/V rows): the caller's buffer is
+    // copied here by the CPU, the transfer to the device is then asynchronous and the call need not wait
+    void* h_rows = nullptr;      size_t rows_slot_bytes = 0;
+    cudaEvent_t rows_events[FLARE_ROW_SLOTS] = {};
+    uint64_t rows_counter = 0;
     uint64_t small_counter = 0;
     std::vector<int> small_last;       // host copy of the last uploaded (ring, attend) arrays
     const void* small_last_dev = nullptr;
