@@ -31,6 +31,7 @@ struct flare_attn_ctx {
     void* d_misc = nullptr;      size_t misc_bytes = 0;     // attend_len and other small arrays
     void* d_misc2 = nullptr;     size_t misc2_bytes = 0;    // small arrays of the prefill path
     void* d_conv = nullptr;      size_t conv_bytes = 0;     // dtype-converted prefill operands
+    void* d_parts = nullptr;     size_t parts_bytes = 0;    // [2][rows][head_dim+2] records of a two-kernel decode
     void* h_pinned = nullptr;    size_t pinned_bytes = 0;
     // ring of page-locked staging slots for small host inputs (new K/V rows): the caller's buffer is
     // copied here by the CPU, the transfer to the device is then asynchronous and the call need not wait
@@ -61,6 +62,9 @@ struct flare_kv {
     CUtensorMap kq_map, vq_map;
     bool has_maps = false;
     bool maps_whole_rows = false;
+    // TMA maps of the group-32 KIVI code planes: (16 bytes = 64 codes of one head, slot, kv head, layer*batch + seq)
+    CUtensorMap g32_kmap, g32_vmap;
+    bool has_g32_maps = false;
     inline char* plane_ptr(int p, int layer, int seq) const {
         return (char*)plane[p] + ((size_t)layer * batch + seq) * plane_bytes[p];
     }
@@ -119,12 +123,16 @@ struct DecodeArgs {
     int layer;
     const CUtensorMap *kmap, *vmap;   // Q8_0 payload maps (null when the cache has none)
     int whole_rows;                   // maps deliver [head][32 slots][head_dim] in one copy
+    const int* h_attend;              // host copy of attend_len (valid during the call)
+    const flare_kv* kv_obj;           // the cache itself (tensor maps, ring state)
 };
 int flare_launch_decode(flare_attn_ctx* ctx, const DecodeArgs& a);
 int flare_launch_decode_generic(flare_attn_ctx* ctx, const DecodeArgs& a);
 bool flare_decode_q8_supported(const DecodeArgs& a);
 int flare_launch_decode_q8(flare_attn_ctx* ctx, const DecodeArgs& a);
 int flare_check_device_error(flare_attn_ctx* ctx);
+bool flare_decode_g32_supported(const DecodeArgs& a, const flare_kv* kv);
+int flare_launch_decode_g32_part(flare_attn_ctx* ctx, const DecodeArgs& a, const flare_kv* kv, float* part0);
 int flare_decode_noalloc(flare_attn_ctx* ctx, const flare_kv* kv, int layer, int num_heads, const float* q_dev,
                          int n_q, const int* attend_len, float* out_dev);
 size_t flare_noalloc_scratch_bytes();

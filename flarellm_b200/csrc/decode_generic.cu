@@ -117,15 +117,17 @@ template <bool IS_V> struct Row<FLARE_KV_KIVI_G32, IS_V> {
 #pragma unroll
             for (int i = 0; i < 8; i++) o[i] = q2_dequant((float)((w >> (2 * i)) & 3), m.x, m.y);
         } else {
-            int grp = slot >> 5, tin = slot & 31;
-            const uint8_t* cp = reinterpret_cast<const uint8_t*>(s.p[FLARE_PLANE_K_Q]) +
-                                ((size_t)grp * s.kv_dim + c0) * 8 + (tin >> 2);
-            const __half2* mp = reinterpret_cast<const __half2*>(s.p[FLARE_PLANE_K_SCALE]) + (size_t)grp * s.kv_dim + c0;
-            int sh = (tin & 3) * 2;
+            const int grp = slot >> 5;
+            const uint16_t* cp = reinterpret_cast<const uint16_t*>(s.p[FLARE_PLANE_K_Q] + (size_t)slot * (s.kv_dim / 4) + c0 / 4);
+            const uint32_t w = __ldg(cp);
+            // the 8 channels' (scale, zero) pairs of this 32-slot group: 32 contiguous bytes
+            const uint4* mp = reinterpret_cast<const uint4*>(reinterpret_cast<const __half2*>(s.p[FLARE_PLANE_K_SCALE]) + (size_t)grp * s.kv_dim + c0);
+            const uint4 m0 = __ldg(mp), m1 = __ldg(mp + 1);
+            const uint32_t mw[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
 #pragma unroll
             for (int i = 0; i < 8; i++) {
-                float2 m = __half22float2(__ldg(mp + i));
-                o[i] = q2_dequant((float)((__ldg(cp + 8 * i) >> sh) & 3), m.x, m.y);
+                const float2 m = __half22float2(*reinterpret_cast<const __half2*>(&mw[i]));
+                o[i] = q2_dequant((float)((w >> (2 * i)) & 3), m.x, m.y);
             }
         }
     }

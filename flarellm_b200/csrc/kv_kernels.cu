@@ -204,6 +204,7 @@ __global__ void write_g32_groups_kernel(uint8_t* __restrict__ Kq, __half2* __res
     const int cb = blockIdx.y * 32;
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
     const int grp = (int)((tok0 % max_seq) / 32);
+    __shared__ uint8_t s_code[32][33];   // [token][channel of this 32-block]
     {   // keys: warp w handles channel cb + w, lane = token within the group
         const int c = cb + w;
         float v = g32_token_value(Kres, key, tok0 + lane, first_pos, c, kv_dim);
@@ -215,11 +216,15 @@ __global__ void write_g32_groups_kernel(uint8_t* __restrict__ Kq, __half2* __res
             if (b > mx) mx = b;
         }
         const Q2Stats st = q2_stats_from_minmax(mn, mx);
-        uint32_t code = q2_code_of(v, st) << ((lane & 3) * 2);
-        code |= __shfl_xor_sync(0xffffffffu, code, 1);
-        code |= __shfl_xor_sync(0xffffffffu, code, 2);
-        if ((lane & 3) == 0) Kq[((size_t)grp * kv_dim + c) * 8 + (lane >> 2)] = (uint8_t)code;
+        s_code[lane][w] = (uint8_t)q2_code_of(v, st);
         if (lane == 0) Kmeta[(size_t)grp * kv_dim + c] = __halves2half2(__float2half_rn(st.scale), __float2half_rn(st.mn));
+    }
+    __syncthreads();
+    if (threadIdx.x < 256) {   // pack 4 channels per byte: token t = tid / 8, byte j = tid % 8 of this 32-channel block
+        const int t = threadIdx.x >> 3, j = threadIdx.x & 7;
+        const uint32_t byte = s_code[t][4 * j] | (s_code[t][4 * j + 1] << 2) | (s_code[t][4 * j + 2] << 4) | (s_code[t][4 * j + 3] << 6);
+        const int slot = (int)((tok0 + t) % max_seq);
+        Kq[(size_t)slot * (kv_dim / 4) + cb / 4 + j] = (uint8_t)byte;
     }
     {   // values: warp w handles token tok0 + w, lane = channel within the 32-channel group
         const int64_t tok = tok0 + w;
@@ -294,10 +299,10 @@ __device__ float dq_element(const DqView& s, bool is_v, int slot, int c) {
                 float2 m = __half22float2(reinterpret_cast<const __half2*>(s.p[FLARE_PLANE_V_SCALE])[(size_t)slot * (s.kv_dim / 32) + c / 32]);
                 return q2_dequant(q2_code(pk, c), m.x, m.y);
             }
-            int grp = slot >> 5, tin = slot & 31;
-            const uint8_t* pk = reinterpret_cast<const uint8_t*>(s.p[FLARE_PLANE_K_Q]) + ((size_t)grp * s.kv_dim + c) * 8;
+            int grp = slot >> 5;
+            const uint8_t* pk = reinterpret_cast<const uint8_t*>(s.p[FLARE_PLANE_K_Q]) + (size_t)slot * (s.kv_dim / 4);
             float2 m = __half22float2(reinterpret_cast<const __half2*>(s.p[FLARE_PLANE_K_SCALE])[(size_t)grp * s.kv_dim + c]);
-            return q2_dequant(q2_code(pk, tin), m.x, m.y);
+            return q2_dequant(q2_code(pk, c), m.x, m.y);
         }
     }
 }

@@ -76,7 +76,7 @@ typedef enum { FLARE_DT_F32 = 0, FLARE_DT_BF16 = 1 } flare_dtype;
  *             K_SCALE, K_MIN       f32  [kv_dim]                 running per-channel stats
  *             V_SCALE, V_MIN       f32  [max_seq]                per-token
  *             K_RES, V_RES         f32  [32][kv_dim]             residual window
- *   KIVI_G32  K_Q                  u8   [max_seq/32][kv_dim][8]  byte j holds slots 4j..4j+3 of the group
+ *   KIVI_G32  K_Q                  u8   [max_seq][kv_dim/4]      byte j of a slot holds channels 4j..4j+3
  *             K_SCALE              f16x2 [max_seq/32][kv_dim]    (scale, zero)
  *             V_Q                  u8   [max_seq][kv_dim/4]
  *             V_SCALE              f16x2 [max_seq][kv_dim/32]    (scale, zero)

@@ -428,7 +428,7 @@ class G32Cache:
 
     def plane(self, name):
         ms, kv = self.max_seq_len, self.kv
-        shapes = {"k_codes": ms // 32 * kv * 8, "v_codes": ms * kv // 4, "k_meta": ms // 32 * kv * 2,
+        shapes = {"k_codes": ms * kv // 4, "v_codes": ms * kv // 4, "k_meta": ms // 32 * kv * 2,
                   "v_meta": ms * kv // 32 * 2, "res_k": 128 * kv, "res_v": 128 * kv}
         ptr = getattr(self.L, "orc_g32_" + name)(self.h)
         return np.ctypeslib.as_array(ptr, shape=(shapes[name],)).copy()

@@ -702,7 +702,8 @@ ORC_API const float* orc_qkv_residual_values(const orc_qkv_cache* c, size_t l) {
  * when it leaves the 128-token f16 residual ring.
  *
  * Planes for one layer of one sequence (max_seq_len a multiple of 32):
- *   k_codes [max_seq/32][kv_dim][8]      byte j of a (group, channel) holds slots 4j..4j+3
+ *   k_codes [max_seq][kv_dim/4]          byte j of a slot holds channels 4j..4j+3 (as v_codes);
+ *                                        the 32 slots of a group share one (scale, zero) per channel
  *   k_meta  [max_seq/32][kv_dim][2] u16  (scale, zero) as f16 bits
  *   v_codes [max_seq][kv_dim/4]          byte j of a slot holds channels 4j..4j+3
  *   v_meta  [max_seq][kv_dim/32][2] u16
@@ -722,10 +723,17 @@ static void g32_quant_group(const float* vals, uint8_t* codes8, uint16_t* meta2)
  * rows_f16[32][kv_dim] (as f32 values). */
 ORC_API void orc_g32_quant_key_group(const float* rows, size_t kv_dim, uint8_t* k_codes_group,
                                      uint16_t* k_meta_group) {
+    /* k_codes_group: the 32 slot rows of the group, [32][kv_dim/4] */
     float col[G32];
+    uint8_t codes8[8];
+    memset(k_codes_group, 0, G32 * kv_dim / 4);
     for (size_t c = 0; c < kv_dim; c++) {
         for (int t = 0; t < G32; t++) col[t] = rows[(size_t)t * kv_dim + c];
-        g32_quant_group(col, k_codes_group + c * 8, k_meta_group + c * 2);
+        g32_quant_group(col, codes8, k_meta_group + c * 2);          /* codes8: slot t at byte t/4, bits (t%4)*2 */
+        for (int t = 0; t < G32; t++) {
+            uint8_t q = (uint8_t)((codes8[t / 4] >> ((t % 4) * 2)) & 3);
+            k_codes_group[(size_t)t * (kv_dim / 4) + c / 4] |= (uint8_t)(q << ((c % 4) * 2));
+        }
     }
 }
 /* Quantise one value row. */
@@ -739,7 +747,7 @@ ORC_API void orc_g32_dequant_key_group(const uint8_t* k_codes_group, const uint1
     for (size_t c = 0; c < kv_dim; c++) {
         float s = orc_f16_to_f32(k_meta_group[c * 2]), z = orc_f16_to_f32(k_meta_group[c * 2 + 1]);
         for (int t = 0; t < G32; t++) {
-            float q = (float)((k_codes_group[c * 8 + t / 4] >> ((t % 4) * 2)) & 3);
+            float q = (float)((k_codes_group[(size_t)t * (kv_dim / 4) + c / 4] >> ((c % 4) * 2)) & 3);
             rows_out[(size_t)t * kv_dim + c] = q * s + z;
         }
     }
@@ -761,7 +769,7 @@ typedef struct {
 ORC_API orc_g32_cache* orc_g32_new(size_t max_seq_len, size_t kv_dim) {
     orc_g32_cache* c = (orc_g32_cache*)calloc(1, sizeof(*c));
     c->max_seq_len = max_seq_len; c->kv_dim = kv_dim;
-    c->k_codes = (uint8_t*)calloc(max_seq_len / G32 * kv_dim * 8 + 1, 1);
+    c->k_codes = (uint8_t*)calloc(max_seq_len * kv_dim / 4 + 1, 1);
     c->k_meta = (uint16_t*)calloc(max_seq_len / G32 * kv_dim * 2 + 1, 2);
     c->v_codes = (uint8_t*)calloc(max_seq_len * kv_dim / 4 + 1, 1);
     c->v_meta = (uint16_t*)calloc(max_seq_len * kv_dim / G32 * 2 + 1, 2);
@@ -787,7 +795,7 @@ ORC_API void orc_g32_write_advance(orc_g32_cache* c, const float* key, const flo
         for (int t = 0; t < G32; t++)
             for (size_t i = 0; i < kv; i++)
                 rows[(size_t)t * kv + i] = orc_f16_to_f32(c->res_k[((first + t) % G32_RESIDUAL) * kv + i]);
-        orc_g32_quant_key_group(rows, kv, c->k_codes + group * kv * 8, c->k_meta + group * kv * 2);
+        orc_g32_quant_key_group(rows, kv, c->k_codes + group * G32 * kv / 4, c->k_meta + group * kv * 2);
         for (int t = 0; t < G32; t++) {
             size_t slot = (first + t) % c->max_seq_len;
             for (size_t i = 0; i < kv; i++)
@@ -815,7 +823,7 @@ ORC_API void orc_g32_dequant(const orc_g32_cache* c, float* out_k, float* out_v)
     memset(out_v, 0, c->max_seq_len * kv * 4);
     float* rows = (float*)malloc(G32 * kv * 4);
     for (size_t g = 0; g < c->max_seq_len / G32; g++) {
-        orc_g32_dequant_key_group(c->k_codes + g * kv * 8, c->k_meta + g * kv * 2, kv, rows);
+        orc_g32_dequant_key_group(c->k_codes + g * G32 * kv / 4, c->k_meta + g * kv * 2, kv, rows);
         for (int t = 0; t < G32; t++) memcpy(out_k + (g * G32 + t) * kv, rows + (size_t)t * kv, kv * 4);
     }
     free(rows);

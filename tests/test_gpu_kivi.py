@@ -171,6 +171,55 @@ def test_g32_decode_step(eng, fb, orc):
     kv.free()
 
 
+@pytest.mark.parametrize("nh,nkv,layers,B,n0", [(32, 8, 2, 2, 1500), (8, 4, 1, 3, 1100), (8, 8, 1, 1, 2000), (4, 2, 3, 2, 1333)])
+def test_g32_long_context_decode_takes_the_tensor_core_path(eng, fb, orc, nh, nkv, layers, B, n0):
+    """From 1024 attended tokens on, equal-length batches at head_dim 64 run the code-tile kernel for the
+    quantised prefix plus the general kernel for the newest tokens; results must still match the CPU."""
+    hd, ms = 64, 2048
+    kvd = nkv * hd
+    layer = layers - 1
+    kv = eng.kv_alloc(layers, B, ms, nkv, hd, fb.KV_KIVI_G32)
+    ks, vs = [], []
+    for b in range(B):
+        k, v = _g32_inputs(17 + 10 * b + nh, n0 + 36, kvd)
+        ks.append(k); vs.append(v)
+        kv.append(layer, b, k[:n0], v[:n0]); kv.advance(b, n0)
+    for step in range(36):
+        t = n0 + step
+        q = normal(300 + step, (B, 1, nh, hd), 0.4)
+        for b in range(B):
+            kv.write(layer, b, t, ks[b][t], vs[b][t])
+        got = eng.decode(kv, layer, nh, q)
+        if step % 7 == 0 or step == 35:
+            for b in range(B):
+                oc = _g32_oracle(orc, ms, kvd, ks[b][:t + 1], vs[b][:t + 1])
+                ok, ov = oc.dequant()
+                want = orc.gqa_decode(q[b], ok, ov, nh, nkv, hd, oc.attend_len())
+                assert_close(got[b], want, f"g32 long step {step} seq {b}")
+        kv.advance()
+    kv.free()
+
+
+def test_g32_ragged_batch_long_context(eng, fb, orc):
+    """Sequences of different lengths (one long, one short) in one call."""
+    nh, nkv, hd, ms, B = 8, 2, 64, 2048, 2
+    kvd = nkv * hd
+    lens = [1700, 300]
+    kv = eng.kv_alloc(1, B, ms, nkv, hd, fb.KV_KIVI_G32)
+    q = normal(77, (B, 1, nh, hd), 0.4)
+    for b in range(B):
+        k, v = _g32_inputs(5 + b, lens[b] + 1, kvd)
+        kv.append(0, b, k[:lens[b]], v[:lens[b]]); kv.advance(b, lens[b])
+        kv.write(0, b, lens[b], k[lens[b]], v[lens[b]])
+    got = eng.decode(kv, 0, nh, q)
+    for b in range(B):
+        k, v = _g32_inputs(5 + b, lens[b] + 1, kvd)
+        oc = _g32_oracle(orc, ms, kvd, k, v)
+        ok, ov = oc.dequant()
+        assert_close(got[b], orc.gqa_decode(q[b], ok, ov, nh, nkv, hd, oc.attend_len()), f"ragged seq {b}")
+    kv.free()
+
+
 def test_g32_rollback_is_refused_after_eviction(eng, fb):
     kv = eng.kv_alloc(1, 1, 256, 1, 64, fb.KV_KIVI_G32)
     rows = normal(5, (200, 64))
