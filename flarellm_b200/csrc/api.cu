@@ -52,23 +52,7 @@ KvLayerView flare_layer_view(const flare_kv* kv, int layer) {
 
 int flare_launch_decode(flare_attn_ctx* ctx, const DecodeArgs& a) {
     if (flare_decode_q8_supported(a)) return flare_launch_decode_q8(ctx, a);
-    if (a.kv_obj && a.h_attend && flare_decode_g32_supported(a, a.kv_obj)) {
-        // every sequence must have the same length for the fixed split between the two kernels
-        bool uniform = true;
-        for (int b = 1; b < a.batch; b++) uniform = uniform && a.h_attend[b] == a.h_attend[0];
-        if (uniform) {
-            const int n = a.h_attend[0], hd = a.kv.head_dim, rows = a.batch * a.num_heads;
-            const int lim = n > 128 ? (n - 128) / 32 * 32 : 0;
-            const size_t rec = (size_t)rows * (hd + 2);
-            FLARE_TRY(flare_ensure(ctx, &ctx->d_parts, &ctx->parts_bytes, 2 * rec * sizeof(float)));
-            float* parts = (float*)ctx->d_parts;
-            FLARE_TRY(flare_launch_decode_g32_part(ctx, a, a.kv_obj, parts));           // quantised slots [0, lim)
-            DecodeArgs tail = a;                                                       // newest slots [lim, n)
-            tail.slot_begin = lim; tail.slot_end = n; tail.want_partial = 1; tail.out = parts + rec;
-            FLARE_TRY(flare_launch_decode_generic(ctx, tail));
-            return flare_launch_merge(ctx, parts, rec, 2, rows, hd, a.out, 0);
-        }
-    }
+    if (a.kv_obj && flare_decode_g32_supported(a, a.kv_obj)) return flare_launch_decode_g32(ctx, a, a.kv_obj);
     return flare_launch_decode_generic(ctx, a);
 }
 
@@ -120,7 +104,7 @@ int flare_attn_destroy(flare_attn_ctx* ctx) {
     cudaStreamSynchronize(ctx->stream);
     if (ctx->backend_kv) flare_kv_free(ctx->backend_kv);
     cudaFree(ctx->d_err);
-    cudaFree(ctx->d_misc2); cudaFree(ctx->d_conv); cudaFree(ctx->d_parts);
+    cudaFree(ctx->d_misc2); cudaFree(ctx->d_conv);
     cudaFree(ctx->d_work); cudaFree(ctx->d_stage_in); cudaFree(ctx->d_stage_out); cudaFree(ctx->d_misc);
     if (ctx->h_pinned) cudaFreeHost(ctx->h_pinned);
     if (ctx->h_rows) cudaFreeHost(ctx->h_rows);
@@ -570,11 +554,9 @@ static int decode_common(flare_attn_ctx* ctx, flare_kv* kv, int layer, int num_h
     a.vmap = kv->has_maps ? &kv->vq_map : nullptr;
     a.whole_rows = kv->maps_whole_rows ? 1 : 0;
     a.kv_obj = kv;
-    a.h_attend = nullptr;
     a.batch = kv->batch; a.n_q = n_q; a.num_heads = num_heads;
     a.slot_begin = slot_begin; a.slot_end = slot_end; a.want_partial = want_partial; a.causal_q = causal_q;
     FLARE_TRY(upload_small(ctx, kv, n_q, attend_len, &a.attend_len, &a.ring, &a.max_attend));
-    a.h_attend = ctx->small_last.data() + 2 * (size_t)kv->batch;     // the attend lengths just uploaded
     const size_t rows = (size_t)kv->batch * n_q * num_heads;
     const size_t q_bytes = rows * kv->head_dim * 4;
     const size_t o_bytes = rows * (kv->head_dim + (want_partial ? 2 : 0)) * 4;

@@ -14,6 +14,11 @@
 #include "../../include/flare_attn.h"
 
 #define FLARE_G32_RESIDUAL 128
+// Group-32 KIVI key metadata: per 32-slot group a row of kv_dim (scale, zero) f16 pairs stored per block of
+// 16 channels as 16 scales then 16 zero points, channel r of the block at position 2 (r mod 8) + r div 8 —
+// the pair (r, r + 8), whose 2-bit codes sit 16 bits apart in a code word, is adjacent.  Index of the scale
+// in f16 units; the zero point is 16 entries further.
+#define FLARE_G32_KMETA_INDEX(c) ((((c) >> 4) << 5) + (((c) & 7) << 1) + (((c) >> 3) & 1))
 #define FLARE_REF_RESIDUAL 32
 #define FLARE_SMALL_SLOTS 64
 #define FLARE_ROW_SLOTS 8
@@ -31,7 +36,6 @@ struct flare_attn_ctx {
     void* d_misc = nullptr;      size_t misc_bytes = 0;     // attend_len and other small arrays
     void* d_misc2 = nullptr;     size_t misc2_bytes = 0;    // small arrays of the prefill path
     void* d_conv = nullptr;      size_t conv_bytes = 0;     // dtype-converted prefill operands
-    void* d_parts = nullptr;     size_t parts_bytes = 0;    // [2][rows][head_dim+2] records of a two-kernel decode
     void* h_pinned = nullptr;    size_t pinned_bytes = 0;
     // ring of page-locked staging slots for small host inputs (new K/V rows): the caller's buffer is
     // copied here by the CPU, the transfer to the device is then asynchronous and the call need not wait
@@ -123,7 +127,6 @@ struct DecodeArgs {
     int layer;
     const CUtensorMap *kmap, *vmap;   // Q8_0 payload maps (null when the cache has none)
     int whole_rows;                   // maps deliver [head][32 slots][head_dim] in one copy
-    const int* h_attend;              // host copy of attend_len (valid during the call)
     const flare_kv* kv_obj;           // the cache itself (tensor maps, ring state)
 };
 int flare_launch_decode(flare_attn_ctx* ctx, const DecodeArgs& a);
@@ -132,7 +135,7 @@ bool flare_decode_q8_supported(const DecodeArgs& a);
 int flare_launch_decode_q8(flare_attn_ctx* ctx, const DecodeArgs& a);
 int flare_check_device_error(flare_attn_ctx* ctx);
 bool flare_decode_g32_supported(const DecodeArgs& a, const flare_kv* kv);
-int flare_launch_decode_g32_part(flare_attn_ctx* ctx, const DecodeArgs& a, const flare_kv* kv, float* part0);
+int flare_launch_decode_g32(flare_attn_ctx* ctx, const DecodeArgs& a, const flare_kv* kv);
 int flare_decode_noalloc(flare_attn_ctx* ctx, const flare_kv* kv, int layer, int num_heads, const float* q_dev,
                          int n_q, const int* attend_len, float* out_dev);
 size_t flare_noalloc_scratch_bytes();

@@ -9,13 +9,19 @@
 // (scale, zero) pairs as plain bulk copies — each stage behind an mbarrier, refilled by the last
 // warp that finishes with it.
 //
-// Dequantisation never happens per element.  With c the 2-bit code:
-//   scores  S[h, t] = sum_ch q[h,ch] (c[t,ch] s[ch] + z[ch]) = sum_ch (q s)[h,ch] c[t,ch] + sum_ch q[h,ch] z[ch]
-//           q*s is rebuilt per key group as f16 hi + lo (A operand rows g and g+8, m16n8k16), the codes
-//           become exact f16 values with one shift, one mask-or and one subtract per pair;
-//   output  O[h, ch] = sum_t (p[t] s[t,blk]) c[t,ch] + sum_t p[t] z[t,blk]
-//           weights p*s in f16, codes transposed by ldmatrix.trans (16-bit units hold 8 codes of a slot)
-//           and expanded the same way, the zero-point term is one scalar per (head, 32-channel block).
+// Dequantisation never happens per element, and both products run "transposed" so that the codes are
+// the 16-row A operand and the 8 columns carry the (at most 4) query heads.  With c the 2-bit code:
+//   scores  S[t, h] = sum_ch c[t,ch] (q s)[ch,h]  +  sum_ch z[ch] q[ch,h]
+//           A = codes of 16 slots (exact f16 after one mask-or and one fma per pair; lane tig works on
+//           word tig of a slot's 16 code bytes, i.e. channels 16 tig .. 16 tig + 15),
+//           B = q*s rebuilt per key group with packed f16 arithmetic as an exact hi + lo pair
+//           (column 2h = hi, 2h+1 = lo; q is pre-scaled by a power of two so q*s cannot overflow);
+//           the zero-point term is one more MMA whose A holds z in row 0 and whose B is q itself.
+//   output  O[ch, (h, blk)] = sum_t c[t,ch] (p[t,h] s_v[t,blk])  +  sum_t p[t,h] z_v[t,blk]
+//           A = V codes transposed by ldmatrix.trans (16-bit units hold 8 codes of a slot), left with
+//           their 1024 bias and position weight 4^k (both removed once at the end), B = the f16 weights
+//           p*s_v moved into operand layout by movmatrix; column 2h+blk serves channel block blk;
+//           a row of ones gives the bias sum, the zero-point term is one f32 scalar per (head, block).
 #include "common.cuh"
 #include "tma.cuh"
 #include <math_constants.h>
@@ -26,6 +32,7 @@ constexpr int T = 32;
 constexpr int STAGES = 4;
 constexpr int HD = 64;
 constexpr float kLog2e = 1.4426950408889634f;
+constexpr uint32_t kMagic = 0x64006400u;      // half2 (1024, 1024): a code OR-ed into the mantissa is 1024 + code * 2^bit
 
 struct G32Params {
     const float* q;
@@ -34,18 +41,30 @@ struct G32Params {
     const unsigned char* k_meta;     // layer base, sequence 0: [group][kv_dim] half2
     const unsigned char* v_meta;     // [slot][kv_dim/32] half2
     size_t k_meta_seq_stride, v_meta_seq_stride;   // bytes
-    int layer_seq0, num_heads, nkv, G, n_split;
+    // for the newest tokens: code planes [slot][kv_dim/4], f16 residual rings [128][kv_dim], ring state
+    const unsigned char *k_codes, *v_codes, *k_res, *v_res;
+    size_t codes_seq_stride, res_seq_stride;       // bytes
+    const int2* ring;
+    int layer_seq0, num_heads, nkv, G, n_split;    // records per row: n_split + 1, the last one from the newest tokens
     int* err;
+    // 0x64006400 and 0x00030003, passed as arguments so that they live in registers: a logic instruction takes
+    // one immediate only, and with both known at compile time every mask-or would become two instructions
+    uint32_t magic, mask3;
 };
 
-__device__ __forceinline__ void mma_f16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+__device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
 }
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
     uint32_t u;
@@ -58,20 +77,138 @@ __device__ __forceinline__ float2 unpack_half2(uint32_t u) {
         : "=f"(f.x), "=f"(f.y) : "r"(u));
     return f;
 }
-// two 2-bit codes that sit 16 bits apart in `w` (at bit `sh` of each half) -> half2 of their values
-__device__ __forceinline__ uint32_t codes_to_half2(uint32_t w, int sh) {
-    uint32_t u = ((w >> sh) & 0x00030003u) | 0x64006400u;      // 1024 + code in each half
-    asm("sub.f16x2 %0, %0, %1;" : "+r"(u) : "r"(0x64006400u));   // exact
-    return u;
+__device__ __forceinline__ uint32_t hmul2(uint32_t a, uint32_t b) {
+    uint32_t d; asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d;
 }
-__device__ __forceinline__ uint32_t codes_to_half2_biased(uint32_t w, int sh) {
-    return ((w >> sh) & 0x00030003u) | 0x64006400u;             // 1024 + code; the bias is removed at the end
+__device__ __forceinline__ uint32_t hfma2(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d; asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c)); return d;
+}
+// (a & b) | c in one logic instruction
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d; asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c)); return d;
+}
+__device__ __forceinline__ uint32_t hneg2(uint32_t a) {
+    uint32_t d; asm("neg.f16x2 %0, %1;" : "=r"(d) : "r"(a)); return d;
 }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-__global__ void __launch_bounds__(256) decode_g32_kernel(const __grid_constant__ CUtensorMap kmap,
-                                                         const __grid_constant__ CUtensorMap vmap, G32Params p) {
+// weight of the V code of channel 8 g + cc inside the biased f16 value (see the output product)
+__host__ __device__ constexpr float v_code_weight(int cc) { return cc <= 4 ? (float)(1 << (2 * cc)) : (float)(1 << (2 * cc - 6)); }
+
+// The newest tokens of a sequence (slots lim .. n-1, at most 159): the f16 residual ring for the last 128
+// and 2-bit codes for the few older ones whose group-aligned prefix the tile loop does not cover.  One warp
+// per KV head on CUDA cores: lanes own slots for the scores, then channel pairs for the output.
+__device__ void g32_newest_tokens(const G32Params& p, int b, int kvh, int lane, int lim, int n, float* ws) {
+    constexpr int MAXT = 160;
+    const int kv_dim = p.nkv * HD, G = p.G;
+    float* q_s = ws;                 // [4][HD]
+    float* p_s = ws + 4 * HD;        // [4][MAXT]
+    const int newest = p.ring[b].x;  // ring not wrapped: slot index = token index
+    const float sc = rsqrtf((float)HD) * kLog2e;
+    for (int i = lane; i < 4 * HD; i += 32) {
+        const int h = i / HD;
+        q_s[i] = h < G ? __ldg(p.q + ((size_t)b * p.num_heads + kvh * G + h) * HD + (i % HD)) * sc : 0.0f;
+    }
+    __syncwarp();
+    const unsigned char* kres = p.k_res + (size_t)b * p.res_seq_stride;
+    const unsigned char* vres = p.v_res + (size_t)b * p.res_seq_stride;
+    const unsigned char* kcod = p.k_codes + (size_t)b * p.codes_seq_stride;
+    const unsigned char* vcod = p.v_codes + (size_t)b * p.codes_seq_stride;
+    const __half* kmeta = reinterpret_cast<const __half*>(p.k_meta + (size_t)b * p.k_meta_seq_stride);
+    const __half2* vmeta = reinterpret_cast<const __half2*>(p.v_meta + (size_t)b * p.v_meta_seq_stride);
+    const int count = n - lim;
+
+    float mx[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+    for (int i0 = 0; i0 < count; i0 += 32) {
+        const int t = lim + i0 + lane;
+        float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        if (t < n) {
+            if (newest - t < FLARE_G32_RESIDUAL) {
+                const uint4* row = reinterpret_cast<const uint4*>(kres + ((size_t)(t % FLARE_G32_RESIDUAL) * kv_dim + kvh * HD) * 2);
+#pragma unroll
+                for (int c8 = 0; c8 < HD / 8; c8++) {
+                    const uint4 w = __ldg(row + c8);
+                    const __half2* h2 = reinterpret_cast<const __half2*>(&w);
+                    float k[8];
+#pragma unroll
+                    for (int j = 0; j < 4; j++) { const float2 f = __half22float2(h2[j]); k[2 * j] = f.x; k[2 * j + 1] = f.y; }
+#pragma unroll
+                    for (int h = 0; h < 4; h++)
+#pragma unroll
+                        for (int j = 0; j < 8; j++) s[h] = fmaf(q_s[h * HD + c8 * 8 + j], k[j], s[h]);
+                }
+            } else {
+                const uint4 cw = __ldg(reinterpret_cast<const uint4*>(kcod + (size_t)t * (kv_dim / 4) + kvh * (HD / 4)));
+                const uint32_t w4[4] = {cw.x, cw.y, cw.z, cw.w};
+                const __half* mrow = kmeta + (size_t)(t >> 5) * kv_dim * 2;
+#pragma unroll
+                for (int wi = 0; wi < 4; wi++)
+#pragma unroll 4
+                    for (int j = 0; j < 16; j++) {
+                        const int c = kvh * HD + wi * 16 + j;
+                        const float k = q2_dequant((float)((w4[wi] >> (2 * j)) & 3u), __half2float(__ldg(mrow + FLARE_G32_KMETA_INDEX(c))),
+                                                   __half2float(__ldg(mrow + FLARE_G32_KMETA_INDEX(c) + 16)));
+#pragma unroll
+                        for (int h = 0; h < 4; h++) s[h] = fmaf(q_s[h * HD + wi * 16 + j], k, s[h]);
+                    }
+            }
+        }
+#pragma unroll
+        for (int h = 0; h < 4; h++) {
+            const float v = t < n ? s[h] : -CUDART_INF_F;
+            p_s[h * MAXT + i0 + lane] = v;
+            mx[h] = fmaxf(mx[h], v);
+        }
+    }
+    float l[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+    for (int h = 0; h < 4; h++) {
+#pragma unroll
+        for (int o = 16; o; o >>= 1) mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], o));
+        for (int i = lane; i < count; i += 32) {
+            const float e = fast_exp2(p_s[h * MAXT + i] - mx[h]);
+            p_s[h * MAXT + i] = e;
+            l[h] += e;
+        }
+#pragma unroll
+        for (int o = 16; o; o >>= 1) l[h] += __shfl_xor_sync(0xffffffffu, l[h], o);
+    }
+    __syncwarp();
+    // output: this lane owns channels 2 lane, 2 lane + 1 of the head
+    float acc[4][2] = {};
+    for (int i = 0; i < count; i++) {
+        const int t = lim + i;
+        float v0, v1;
+        if (newest - t < FLARE_G32_RESIDUAL) {
+            const float2 f = __half22float2(__ldg(reinterpret_cast<const __half2*>(vres + ((size_t)(t % FLARE_G32_RESIDUAL) * kv_dim + kvh * HD) * 2) + lane));
+            v0 = f.x; v1 = f.y;
+        } else {
+            const uint32_t byte = __ldg(vcod + (size_t)t * (kv_dim / 4) + kvh * (HD / 4) + (lane >> 1));
+            const float2 m = __half22float2(__ldg(vmeta + (size_t)t * (kv_dim / 32) + kvh * (HD / 32) + (lane >> 4)));
+            v0 = q2_dequant((float)((byte >> ((lane & 1) * 4)) & 3u), m.x, m.y);
+            v1 = q2_dequant((float)((byte >> ((lane & 1) * 4 + 2)) & 3u), m.x, m.y);
+        }
+#pragma unroll
+        for (int h = 0; h < 4; h++) {
+            const float w = p_s[h * MAXT + i];
+            acc[h][0] = fmaf(w, v0, acc[h][0]);
+            acc[h][1] = fmaf(w, v1, acc[h][1]);
+        }
+    }
+#pragma unroll
+    for (int h = 0; h < 4; h++) {
+        if (h >= G) break;
+        const size_t row = (size_t)b * p.num_heads + kvh * G + h;
+        float* wrec = p.work + (row * (p.n_split + 1) + p.n_split) * (HD + 2);
+        *reinterpret_cast<float2*>(wrec + 2 + 2 * lane) = make_float2(acc[h][0], acc[h][1]);
+        if (lane == 0) { wrec[0] = count > 0 ? mx[h] : 0.0f; wrec[1] = l[h]; }
+    }
+}
+
+
+__global__ void __launch_bounds__(256, 2) decode_g32_kernel(const __grid_constant__ CUtensorMap kmap,
+                                                            const __grid_constant__ CUtensorMap vmap, G32Params p) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     __shared__ uint64_t full_bar[STAGES];
     __shared__ int done_cnt[STAGES];
@@ -90,6 +227,12 @@ __global__ void __launch_bounds__(256) decode_g32_kernel(const __grid_constant__
     // quantised slots of this sequence: everything older than the newest 128 tokens, in whole groups
     const int n = p.attend_len[b];
     const int lim_tiles = n > 128 ? (n - 128) / T : 0;
+    if (split == p.n_split) {            // the CTA of the newest tokens
+        pdl_wait();
+        g32_newest_tokens(p, b, kvh, lane, lim_tiles * T, n, reinterpret_cast<float*>(sbase) + warp * (4 * HD + 4 * 160));
+        pdl_trigger();
+        return;
+    }
     const int t_begin = (int)(((long long)split * lim_tiles) / p.n_split);
     const int t_end = (int)(((long long)(split + 1) * lim_tiles) / p.n_split);
     const int n_tiles = t_end - t_begin;
@@ -115,26 +258,57 @@ __global__ void __launch_bounds__(256) decode_g32_kernel(const __grid_constant__
     __syncthreads();
     pdl_wait();
 
-    // ---- this lane's 16 channels of q (scaled): channel(ks, u) = 16 ks + tig + 4 u ------------------
-    const int hq = g & 3;
-    const bool head_ok = hq < p.G;
-    const size_t row = (size_t)b * p.num_heads + kvh * p.G + (head_ok ? hq : 0);
-    float qv[4][4];
+    // ---- the q side (B operand, column g): head g >> 1, hi part in even columns, lo part in odd ones.
+    //      Lane tig owns channels 16 tig .. 16 tig + 15 (one 32-bit code word of a slot).  In k-step ks its
+    //      logical k (2tig, 2tig+1 | 2tig+8, 2tig+9) are channels 16 tig + (ks, ks+8 | ks+4, ks+12): two codes
+    //      16 bits apart in the word pair up, at bit 2 ks of the word or of the word shifted down by 8.
+    const int hB = g >> 1;
+    const bool lo_col = g & 1;
+    uint32_t qx[4][2], qhz[4][2];          // qx: this column's part of q (hi or lo); qhz: hi part in lo columns, else 0
+    float unscale;                         // 2^e that undoes the power-of-two pre-scaling of head `tig`
     {
+        const bool ok = hB < p.G;
+        const float* qrow = p.q + ((size_t)b * p.num_heads + kvh * p.G + (ok ? hB : 0)) * HD + 16 * tig;
         const float sc = rsqrtf((float)HD) * kLog2e;
+        float qv[16], mx = 0.0f;
+#pragma unroll
+        for (int r = 0; r < 16; r++) {
+            qv[r] = ok ? __ldg(qrow + r) * sc : 0.0f;
+            mx = fmaxf(mx, fabsf(qv[r]));
+        }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        // |q| * 2^-e <= 1/2, so q*s stays below the f16 maximum for every f16 scale
+        int e = (mx > 0.0f && mx < CUDART_INF_F) ? ilogbf(mx) + 2 : 0;
+        e = max(-100, min(100, e));
+        const float down = exp2f((float)-e);
+        const float up = exp2f((float)e);
+        unscale = __shfl_sync(0xffffffffu, up, 8 * tig);          // lane with g = 2 tig holds head tig
 #pragma unroll
         for (int ks = 0; ks < 4; ks++)
 #pragma unroll
-            for (int u = 0; u < 4; u++) qv[ks][u] = head_ok ? __ldg(p.q + row * HD + 16 * ks + tig + 4 * u) * sc : 0.0f;
+            for (int bb = 0; bb < 2; bb++) {
+                const float x0 = qv[ks + 4 * bb] * down, x1 = qv[ks + 4 * bb + 8] * down;
+                const uint32_t h = pack_half2(x0, x1);
+                const float2 hf = unpack_half2(h);
+                const uint32_t l = pack_half2(x0 - hf.x, x1 - hf.y);
+                qx[ks][bb] = lo_col ? l : h;
+                qhz[ks][bb] = lo_col ? h : 0u;
+            }
     }
+    const uint32_t ones = g == 0 ? 0x3c003c00u : 0u;               // half2 (1, 1) in row 0 of an A operand
+    const uint32_t magic = p.magic;
+    uint32_t cmask[5];                                             // a code at bit 0, 2, 4, 6, 8 of both halves
+#pragma unroll
+    for (int k = 0; k < 5; k++) cmask[k] = p.mask3 << (2 * k);
 
-    float acc[8][4];                      // n-tile cc: columns g <-> channel 8 g + cc
+    float acc[4][4];                      // m-tile j: rows g, g+8 <-> channels 8g + 2j, 8g + 2j + 1; columns (head tig, blk 0 | 1)
 #pragma unroll
-    for (int cc = 0; cc < 8; cc++)
+    for (int j = 0; j < 4; j++)
 #pragma unroll
-        for (int k = 0; k < 4; k++) acc[cc][k] = 0.0f;
-    float m_run = -CUDART_INF_F, l_run = 0.0f, lb = 0.0f, zacc = 0.0f;
-    const int lane_blk = g >> 2;          // rows g < 4 weight channel block 0, rows 4..7 block 1
+        for (int k = 0; k < 4; k++) acc[j][k] = 0.0f;
+    float dl[4] = {0.0f, 0.0f, 0.0f, 0.0f};     // row 0: sum of the f16 weights per column
+    float m_run = -CUDART_INF_F, l_run = 0.0f, zacc0 = 0.0f, zacc1 = 0.0f;
 
     bool failed = false;
     for (int i = 0; i < n_tiles; i++) {
@@ -143,82 +317,101 @@ __global__ void __launch_bounds__(256) decode_g32_kernel(const __grid_constant__
         const unsigned char* st = sbase + (size_t)s * stage_bytes;
         const unsigned char* kc = st + kvh * (T * 16);
         const uint32_t vc = ptx::smem_u32(st + codes + kvh * (T * 16));
-        const uint32_t* kmeta = reinterpret_cast<const uint32_t*>(st + 2 * codes) + kvh * HD;
-        const uint32_t* vmeta = reinterpret_cast<const uint32_t*>(st + 2 * codes + kmeta_bytes);
+        const uint4* kmeta = reinterpret_cast<const uint4*>(st + 2 * codes + (kvh * 4 + tig) * 64);   // 16 scales, 16 zeros
+        const uint2* vmeta = reinterpret_cast<const uint2*>(st + 2 * codes + kmeta_bytes) + kvh;
 
-        // ---- A operand of the score product: (q s) as f16 hi + lo, and the zero-point term ---------
-        uint32_t qa[4][4];
-        float bias = 0.0f;
+        // ---- B = (q s) hi/lo for this group; the zero-point term as row 0 of one more product ---------
+        uint32_t bq[4][2];
+        float dz[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        {
+            const uint4 sa = kmeta[0], sb = kmeta[1];
+            uint4 za = make_uint4(0u, 0u, 0u, 0u), zb = za;
+            if (g == 0) { za = kmeta[2]; zb = kmeta[3]; }
+            const uint32_t s2[8] = {sa.x, sa.y, sa.z, sa.w, sb.x, sb.y, sb.z, sb.w};     // pair p: channels (p, p + 8)
+            const uint32_t z2[8] = {za.x, za.y, za.z, za.w, zb.x, zb.y, zb.z, zb.w};
 #pragma unroll
-        for (int ks = 0; ks < 4; ks++) {
-            float qs[4];
+            for (int ks = 0; ks < 4; ks++) {
 #pragma unroll
-            for (int u = 0; u < 4; u++) {
-                const float2 m = unpack_half2(kmeta[16 * ks + tig + 4 * u]);     // (scale, zero) of the channel
-                qs[u] = qv[ks][u] * m.x;
-                bias = fmaf(qv[ks][u], m.y, bias);
+                for (int bb = 0; bb < 2; bb++) {
+                    const uint32_t sv = s2[ks + 4 * bb];
+                    const uint32_t ph = hmul2(qhz[ks][bb], sv);                  // lo columns: rounded hi product
+                    const uint32_t er = hfma2(qhz[ks][bb], sv, hneg2(ph));       //             its exact rounding error
+                    bq[ks][bb] = hfma2(qx[ks][bb], sv, er);                      // hi columns: round(q_hi s); lo: q_lo s + error
+                }
+                mma_f16(dz, z2[ks], 0u, z2[ks + 4], 0u, qx[ks][0], qx[ks][1]);
             }
-            // logical k (2tig, 2tig+1) <-> channels (tig, tig+8) = u 0, 2;  k (2tig+8, +9) <-> (tig+4, tig+12) = u 1, 3
-            const uint32_t h0 = pack_half2(qs[0], qs[2]), h1 = pack_half2(qs[1], qs[3]);
-            const float2 f0 = unpack_half2(h0), f1 = unpack_half2(h1);
-            qa[ks][0] = h0;                                          // row g,   k low half  (hi part)
-            qa[ks][1] = pack_half2(qs[0] - f0.x, qs[2] - f0.y);      // row g+8              (lo part)
-            qa[ks][2] = h1;                                          // row g,   k high half
-            qa[ks][3] = pack_half2(qs[1] - f1.x, qs[3] - f1.y);
         }
-        bias += __shfl_xor_sync(0xffffffffu, bias, 1);
-        bias += __shfl_xor_sync(0xffffffffu, bias, 2);
+        const float zd = __shfl_sync(0xffffffffu, dz[0] + dz[1], tig);           // row 0 lives in lanes g = 0
 
-        // ---- scores ---------------------------------------------------------------------------------
-        float sc[4][2];
-        float tmax = -CUDART_INF_F;
+        // ---- scores of slots 16 mt + g and 16 mt + 8 + g for head tig -----------------------------------
+        float sc[4];
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const uint4 w = *reinterpret_cast<const uint4*>(kc + (8 * j + g) * 16);   // 64 codes of slot 8j+g
-            const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+        for (int mt = 0; mt < 2; mt++) {
+            const uint32_t wa = *reinterpret_cast<const uint32_t*>(kc + (16 * mt + g) * 16 + 4 * tig);
+            const uint32_t wb = *reinterpret_cast<const uint32_t*>(kc + (16 * mt + 8 + g) * 16 + 4 * tig);
+            const uint32_t wa8 = wa >> 8, wb8 = wb >> 8;
             float d[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-            for (int ks = 0; ks < 4; ks++)
-                mma_f16(d, qa[ks], codes_to_half2(ww[ks], 2 * tig), codes_to_half2(ww[ks], 2 * tig + 8));
-            sc[j][0] = d[0] + d[2] + bias;        // slot 8j + 2tig
-            sc[j][1] = d[1] + d[3] + bias;        // slot 8j + 2tig + 1
-            tmax = fmaxf(tmax, fmaxf(sc[j][0], sc[j][1]));
+            for (int ks = 0; ks < 4; ks++) {
+                // a code at bit 2 ks of a half becomes 1024 + 4^ks code; one fma scales and removes the bias exactly
+                const uint32_t mul = ks == 0 ? 0x3c003c00u : ks == 1 ? 0x34003400u : ks == 2 ? 0x2c002c00u : 0x24002400u;
+                const uint32_t sub = ks == 0 ? 0xe400e400u : ks == 1 ? 0xdc00dc00u : ks == 2 ? 0xd400d400u : 0xcc00cc00u;
+                const uint32_t a0 = hfma2(and_or(wa, cmask[ks], magic), mul, sub);
+                const uint32_t a1 = hfma2(and_or(wb, cmask[ks], magic), mul, sub);
+                const uint32_t a2 = hfma2(and_or(wa8, cmask[ks], magic), mul, sub);
+                const uint32_t a3 = hfma2(and_or(wb8, cmask[ks], magic), mul, sub);
+                mma_f16(d, a0, a1, a2, a3, bq[ks][0], bq[ks][1]);
+            }
+            sc[2 * mt] = (d[0] + d[1] + zd) * unscale;
+            sc[2 * mt + 1] = (d[2] + d[3] + zd) * unscale;
         }
-        tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
-        tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+        float tmax = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
+        tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 4));
+        tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 8));
+        tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 16));
         const bool bump = tmax > m_run + 8.0f;
         if (__any_sync(0xffffffffu, bump)) {
             const float alpha = bump ? fast_exp2(m_run - tmax) : 1.0f;
             if (bump) m_run = tmax;
-            l_run *= alpha; lb *= alpha; zacc *= alpha;
+            l_run *= alpha; zacc0 *= alpha; zacc1 *= alpha;
 #pragma unroll
-            for (int cc = 0; cc < 8; cc++)
+            for (int k = 0; k < 4; k++) dl[k] *= alpha;
 #pragma unroll
-                for (int k = 0; k < 4; k++) acc[cc][k] *= alpha;
+            for (int j = 0; j < 4; j++)
+#pragma unroll
+                for (int k = 0; k < 4; k++) acc[j][k] *= alpha;
         }
-        // ---- weights p * s[t, blk] (f16) and the zero-point sum ---------------------------------------
-        uint32_t pa[2][4];
+        // ---- weights p * s_v[t, blk] as f16 (column 2 tig + blk of the 8x8 slot-by-column matrices) ----
+        uint32_t bp[4];
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const float p0 = fast_exp2(sc[j][0] - m_run), p1 = fast_exp2(sc[j][1] - m_run);
-            l_run += p0 + p1;
-            const float2 m0 = unpack_half2(vmeta[(8 * j + 2 * tig) * (nkv * 2) + kvh * 2 + lane_blk]);
-            const float2 m1 = unpack_half2(vmeta[(8 * j + 2 * tig + 1) * (nkv * 2) + kvh * 2 + lane_blk]);
-            zacc = fmaf(p0, m0.y, fmaf(p1, m1.y, zacc));
-            const uint32_t wb = pack_half2(p0 * m0.x, p1 * m1.x);
-            const float2 wf = unpack_half2(wb);
-            lb += wf.x + wf.y;
-            pa[j >> 1][(j & 1) * 2] = wb;
-            pa[j >> 1][(j & 1) * 2 + 1] = 0u;
+        for (int r = 0; r < 4; r++) {                       // slot 8 r + g
+            const float pr = fast_exp2(sc[r] - m_run);
+            l_run += pr;
+            const uint2 mv = vmeta[(size_t)(8 * r + g) * nkv];          // (scale, zero) of blocks 0 and 1
+            const float2 m0 = unpack_half2(mv.x), m1 = unpack_half2(mv.y);
+            zacc0 = fmaf(pr, m0.y, zacc0);
+            zacc1 = fmaf(pr, m1.y, zacc1);
+            bp[r] = movmatrix_trans(pack_half2(pr * m0.x, pr * m1.x));
         }
-        // ---- output -------------------------------------------------------------------------------------
+        // ---- output ----------------------------------------------------------------------------------------
         uint32_t rr[4];
         ldmatrix_x4_trans(rr, vc + lane * 16);          // matrix m = slots 8m .. 8m+7, 16 bytes (64 codes) per slot
 #pragma unroll
-        for (int kstep = 0; kstep < 2; kstep++)
+        for (int kstep = 0; kstep < 2; kstep++) {
+            const uint32_t r0 = rr[2 * kstep], r1 = rr[2 * kstep + 1];
+            const uint32_t r0s = r0 >> 6, r1s = r1 >> 6;
+            mma_f16(dl, ones, 0u, ones, 0u, bp[2 * kstep], bp[2 * kstep + 1]);
 #pragma unroll
-            for (int cc = 0; cc < 8; cc++)
-                mma_f16(acc[cc], pa[kstep], codes_to_half2_biased(rr[2 * kstep], 2 * cc), codes_to_half2_biased(rr[2 * kstep + 1], 2 * cc));
+            for (int j = 0; j < 4; j++) {
+                const int c0 = 2 * j, c1 = 2 * j + 1;
+                const uint32_t m0 = cmask[c0 <= 4 ? c0 : c0 - 3], m1 = cmask[c1 <= 4 ? c1 : c1 - 3];
+                const uint32_t a0 = and_or(c0 <= 4 ? r0 : r0s, m0, magic);
+                const uint32_t a1 = and_or(c1 <= 4 ? r0 : r0s, m1, magic);
+                const uint32_t a2 = and_or(c0 <= 4 ? r1 : r1s, m0, magic);
+                const uint32_t a3 = and_or(c1 <= 4 ? r1 : r1s, m1, magic);
+                mma_f16(acc[j], a0, a1, a2, a3, bp[2 * kstep], bp[2 * kstep + 1]);
+            }
+        }
 
         __syncwarp();
         if (lane == 0 && i + STAGES < n_tiles) {
@@ -234,51 +427,55 @@ __global__ void __launch_bounds__(256) decode_g32_kernel(const __grid_constant__
         if (lane == 0) atomicExch(p.err, FLARE_ERR_TIMEOUT);
         return;
     }
-    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
-    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
-    lb += __shfl_xor_sync(0xffffffffu, lb, 1);
-    lb += __shfl_xor_sync(0xffffffffu, lb, 2);
-    zacc += __shfl_xor_sync(0xffffffffu, zacc, 1);
-    zacc += __shfl_xor_sync(0xffffffffu, zacc, 2);
-    if (!head_ok) return;
-    // this lane's columns are channels 16 tig + cc (c0) and 16 tig + 8 + cc (c1): block tig >> 1; its rows
-    // weight block g >> 2 -> the accumulators are meaningful where the two agree
-    float* wrec = p.work + (row * p.n_split + split) * (HD + 2);
-    if ((tig >> 1) == lane_blk) {
-        const float fix = zacc - 1024.0f * lb;
 #pragma unroll
-        for (int cc = 0; cc < 8; cc++) {
-            wrec[2 + 16 * tig + cc] = acc[cc][0] + fix;
-            wrec[2 + 16 * tig + 8 + cc] = acc[cc][1] + fix;
-        }
+    for (int o = 4; o <= 16; o <<= 1) {
+        l_run += __shfl_xor_sync(0xffffffffu, l_run, o);
+        zacc0 += __shfl_xor_sync(0xffffffffu, zacc0, o);
+        zacc1 += __shfl_xor_sync(0xffffffffu, zacc1, o);
     }
-    if (g < 4 && tig == 0) { wrec[0] = m_run; wrec[1] = l_run; }
+    const int blk = g >> 2;                                            // channels 8g .. 8g+7 lie in block g >> 2
+    const float lb0 = __shfl_sync(0xffffffffu, dl[0], tig), lb1 = __shfl_sync(0xffffffffu, dl[1], tig);
+    if (tig >= p.G) return;
+    const float bias = 1024.0f * (blk ? lb1 : lb0), zp = blk ? zacc1 : zacc0;
+    const size_t row = (size_t)b * p.num_heads + kvh * p.G + tig;
+    float* wrec = p.work + (row * (p.n_split + 1) + split) * (HD + 2);
+    float o8[8];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        o8[2 * j] = ((blk ? acc[j][1] : acc[j][0]) - bias) * (1.0f / v_code_weight(2 * j)) + zp;
+        o8[2 * j + 1] = ((blk ? acc[j][3] : acc[j][2]) - bias) * (1.0f / v_code_weight(2 * j + 1)) + zp;
+    }
+#pragma unroll
+    for (int k = 0; k < 8; k++) wrec[2 + 8 * g + k] = o8[k];
+    if (g == 0) { wrec[0] = m_run; wrec[1] = l_run; }
 }
 
-// merge of this path's split partials into one [m (natural log units), l, o] record per row
-__global__ void merge_g32_kernel(const float* __restrict__ work, int n_split, float* __restrict__ out) {
+// merge of the records of a row (m in log2 units, l, unnormalised o) into the attention output
+__global__ void __launch_bounds__(HD) merge_g32_kernel(const float* __restrict__ work, int n_rec, float* __restrict__ out) {
+    __shared__ float s_m[264], s_l[264];
     pdl_wait();
     const int row = blockIdx.x, d = threadIdx.x;
-    const float* base = work + (size_t)row * n_split * (HD + 2);
+    const float* base = work + (size_t)row * n_rec * (HD + 2);
+    for (int r = d; r < n_rec; r += HD) { s_m[r] = base[r * (HD + 2)]; s_l[r] = base[r * (HD + 2) + 1]; }
+    __syncthreads();
     float mm = -CUDART_INF_F;
-    for (int r = 0; r < n_split; r++)
-        if (base[r * (HD + 2) + 1] > 0.0f) mm = fmaxf(mm, base[r * (HD + 2)]);
+    for (int r = 0; r < n_rec; r++)
+        if (s_l[r] > 0.0f) mm = fmaxf(mm, s_m[r]);
     float ll = 0.0f, a = 0.0f;
-    for (int r = 0; r < n_split; r++) {
-        const float l_r = base[r * (HD + 2) + 1];
-        const float w = l_r > 0.0f ? fast_exp2(base[r * (HD + 2)] - mm) : 0.0f;
-        ll += l_r * w;
+#pragma unroll 8
+    for (int r = 0; r < n_rec; r++) {
+        const float w = s_l[r] > 0.0f ? fast_exp2(s_m[r] - mm) : 0.0f;
+        ll = fmaf(s_l[r], w, ll);
         a = fmaf(base[r * (HD + 2) + 2 + d], w, a);
     }
-    out[(size_t)row * (HD + 2) + 2 + d] = a;
-    if (d == 0) { out[(size_t)row * (HD + 2)] = mm * 0.6931471805599453f; out[(size_t)row * (HD + 2) + 1] = ll; }
+    out[(size_t)row * HD + d] = ll > 0.0f ? a / ll : 0.0f;
 }
 
 }  // namespace
 
 bool flare_decode_g32_supported(const DecodeArgs& a, const flare_kv* kv) {
     if (a.kv.dtype != FLARE_KV_KIVI_G32 || a.kv.head_dim != 64 || a.n_q != 1 || a.kv.num_kv_heads > 8 ||
-        a.num_heads / a.kv.num_kv_heads > 4 || !kv->has_g32_maps || a.slot_end >= 0 || a.want_partial)
+        a.num_heads / a.kv.num_kv_heads > 4 || !kv->has_g32_maps || a.slot_end >= 0 || a.want_partial || a.window > 0)
         return false;
     // the quantised slots form a prefix only while the ring has not wrapped; and it has to be worth it
     for (int b = 0; b < kv->batch; b++)
@@ -286,28 +483,38 @@ bool flare_decode_g32_supported(const DecodeArgs& a, const flare_kv* kv) {
     return a.max_attend >= 1024;
 }
 
-// records [2][rows][HD + 2]: part 0 from this kernel (quantised slots), part 1 from the general kernel
-// (the newest slots); the caller merges them.
-int flare_launch_decode_g32_part(flare_attn_ctx* ctx, const DecodeArgs& a, const flare_kv* kv, float* part0) {
+// One CTA per (sequence, slot range) over the quantised prefix plus one CTA per sequence for the newest
+// tokens, then the merge of their records into a.out.
+int flare_launch_decode_g32(flare_attn_ctx* ctx, const DecodeArgs& a, const flare_kv* kv) {
     const int nkv = a.kv.num_kv_heads, rows = a.batch * a.num_heads;
     G32Params p;
-    p.q = a.q; p.attend_len = a.attend_len;
+    p.q = a.q; p.attend_len = a.attend_len; p.ring = a.ring;
     p.k_meta = reinterpret_cast<const unsigned char*>(a.kv.plane[FLARE_PLANE_K_SCALE]);
     p.v_meta = reinterpret_cast<const unsigned char*>(a.kv.plane[FLARE_PLANE_V_SCALE]);
     p.k_meta_seq_stride = a.kv.stride[FLARE_PLANE_K_SCALE];
     p.v_meta_seq_stride = a.kv.stride[FLARE_PLANE_V_SCALE];
+    p.k_codes = reinterpret_cast<const unsigned char*>(a.kv.plane[FLARE_PLANE_K_Q]);
+    p.v_codes = reinterpret_cast<const unsigned char*>(a.kv.plane[FLARE_PLANE_V_Q]);
+    p.codes_seq_stride = a.kv.stride[FLARE_PLANE_K_Q];
+    p.k_res = reinterpret_cast<const unsigned char*>(a.kv.plane[FLARE_PLANE_K_RES]);
+    p.v_res = reinterpret_cast<const unsigned char*>(a.kv.plane[FLARE_PLANE_V_RES]);
+    p.res_seq_stride = a.kv.stride[FLARE_PLANE_K_RES];
     p.layer_seq0 = a.layer * a.batch;
     p.num_heads = a.num_heads; p.nkv = nkv; p.G = a.num_heads / nkv;
     p.err = ctx->d_err;
+    p.magic = kMagic; p.mask3 = 0x00030003u;
     const size_t stage = 2 * (size_t)nkv * T * 16 + (size_t)nkv * HD * 4 + (size_t)T * nkv * 2 * 4;
-    const size_t smem = STAGES * stage + 128;
-    int n_split = (ctx->sm_count * 2) / a.batch;
+    size_t smem = STAGES * stage + 128;
+    const size_t tail_smem = (size_t)nkv * (4 * HD + 4 * 160) * sizeof(float) + 128;
+    if (smem < tail_smem) smem = tail_smem;
+    // all CTAs resident at once (two per SM): n_split ranges and one newest-token CTA per sequence
+    int n_split = (ctx->sm_count * 2) / a.batch - 1;
     const int max_split = (a.max_attend / T + 7) / 8;
     if (n_split > max_split) n_split = max_split;
     if (n_split < 1) n_split = 1;
-    if (n_split > 256) n_split = 256;
+    if (n_split > 255) n_split = 255;
     p.n_split = n_split;
-    size_t need = ((size_t)rows * n_split * (HD + 2) * sizeof(float) + 255) / 256 * 256;
+    size_t need = ((size_t)rows * (n_split + 1) * (HD + 2) * sizeof(float) + 255) / 256 * 256;
     FLARE_TRY(flare_ensure(ctx, &ctx->d_work, &ctx->work_bytes, 2 * need));
     ctx->work_phase ^= 1;
     p.work = (float*)((char*)ctx->d_work + (size_t)ctx->work_phase * need);
@@ -317,9 +524,28 @@ int flare_launch_decode_g32_part(flare_attn_ctx* ctx, const DecodeArgs& a, const
                                                 (int)(STAGES * (2 * 8 * T * 16 + 8 * HD * 4 + T * 8 * 2 * 4) + 128)));
         attr_done[ctx->device & 63] = true;
     }
-    decode_g32_kernel<<<dim3(n_split, a.batch), 32 * nkv, smem, ctx->stream>>>(kv->g32_kmap, kv->g32_vmap, p);
+    // Programmatic dependent launch as in the Q8_0 path: after one of this library's own attention kernels
+    // (which never write the cache) the next one may start early; both wait before touching q or records.
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n_split + 1, a.batch);
+    cfg.blockDim = dim3(32 * nkv);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = ctx->last_launch_overlappable ? 1 : 0;
+    FLARE_CUDA_OK(ctx, cudaLaunchKernelEx(&cfg, decode_g32_kernel, kv->g32_kmap, kv->g32_vmap, p));
     FLARE_LAUNCH_CHECK(ctx);
-    merge_g32_kernel<<<rows, HD, 0, ctx->stream>>>(p.work, n_split, part0);
+    cudaLaunchConfig_t mcfg = {};
+    mcfg.gridDim = dim3(rows);
+    mcfg.blockDim = dim3(HD);
+    mcfg.stream = ctx->stream;
+    mcfg.attrs = attr;
+    mcfg.numAttrs = 1;
+    FLARE_CUDA_OK(ctx, cudaLaunchKernelEx(&mcfg, merge_g32_kernel, (const float*)p.work, n_split + 1, a.out));
     FLARE_LAUNCH_CHECK(ctx);
+    ctx->last_launch_overlappable = true;
     return FLARE_OK;
 }

@@ -120,14 +120,19 @@ template <bool IS_V> struct Row<FLARE_KV_KIVI_G32, IS_V> {
             const int grp = slot >> 5;
             const uint16_t* cp = reinterpret_cast<const uint16_t*>(s.p[FLARE_PLANE_K_Q] + (size_t)slot * (s.kv_dim / 4) + c0 / 4);
             const uint32_t w = __ldg(cp);
-            // the 8 channels' (scale, zero) pairs of this 32-slot group: 32 contiguous bytes
-            const uint4* mp = reinterpret_cast<const uint4*>(reinterpret_cast<const __half2*>(s.p[FLARE_PLANE_K_SCALE]) + (size_t)grp * s.kv_dim + c0);
-            const uint4 m0 = __ldg(mp), m1 = __ldg(mp + 1);
-            const uint32_t mw[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+            // channels c0 .. c0+7 are the even (or, for the upper 8 of a 16-block, odd) f16 entries of the
+            // block's 16 scales and 16 zero points: 64 contiguous bytes
+            const uint4* mp = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(s.p[FLARE_PLANE_K_SCALE]) +
+                                                             (size_t)grp * s.kv_dim * 2 + (c0 >> 4) * 32);
+            const uint4 s0 = __ldg(mp), s1 = __ldg(mp + 1), z0 = __ldg(mp + 2), z1 = __ldg(mp + 3);
+            const uint32_t sw[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+            const uint32_t zw[8] = {z0.x, z0.y, z0.z, z0.w, z1.x, z1.y, z1.z, z1.w};
+            const bool upper = (c0 >> 3) & 1;
 #pragma unroll
             for (int i = 0; i < 8; i++) {
-                const float2 m = __half22float2(*reinterpret_cast<const __half2*>(&mw[i]));
-                o[i] = q2_dequant((float)((w >> (2 * i)) & 3), m.x, m.y);
+                const float2 sf = __half22float2(*reinterpret_cast<const __half2*>(&sw[i]));
+                const float2 zf = __half22float2(*reinterpret_cast<const __half2*>(&zw[i]));
+                o[i] = q2_dequant((float)((w >> (2 * i)) & 3), upper ? sf.y : sf.x, upper ? zf.y : zf.x);
             }
         }
     }

@@ -217,7 +217,11 @@ __global__ void write_g32_groups_kernel(uint8_t* __restrict__ Kq, __half2* __res
         }
         const Q2Stats st = q2_stats_from_minmax(mn, mx);
         s_code[lane][w] = (uint8_t)q2_code_of(v, st);
-        if (lane == 0) Kmeta[(size_t)grp * kv_dim + c] = __halves2half2(__float2half_rn(st.scale), __float2half_rn(st.mn));
+        if (lane == 0) {
+            __half* row = reinterpret_cast<__half*>(Kmeta + (size_t)grp * kv_dim);
+            row[FLARE_G32_KMETA_INDEX(c)] = __float2half_rn(st.scale);
+            row[FLARE_G32_KMETA_INDEX(c) + 16] = __float2half_rn(st.mn);
+        }
     }
     __syncthreads();
     if (threadIdx.x < 256) {   // pack 4 channels per byte: token t = tid / 8, byte j = tid % 8 of this 32-channel block
@@ -301,8 +305,8 @@ __device__ float dq_element(const DqView& s, bool is_v, int slot, int c) {
             }
             int grp = slot >> 5;
             const uint8_t* pk = reinterpret_cast<const uint8_t*>(s.p[FLARE_PLANE_K_Q]) + (size_t)slot * (s.kv_dim / 4);
-            float2 m = __half22float2(reinterpret_cast<const __half2*>(s.p[FLARE_PLANE_K_SCALE])[(size_t)grp * s.kv_dim + c]);
-            return q2_dequant(q2_code(pk, c), m.x, m.y);
+            const __half* row = reinterpret_cast<const __half*>(s.p[FLARE_PLANE_K_SCALE]) + (size_t)grp * s.kv_dim * 2;
+            return q2_dequant(q2_code(pk, c), __half2float(row[FLARE_G32_KMETA_INDEX(c)]), __half2float(row[FLARE_G32_KMETA_INDEX(c) + 16]));
         }
     }
 }

@@ -77,7 +77,9 @@ typedef enum { FLARE_DT_F32 = 0, FLARE_DT_BF16 = 1 } flare_dtype;
  *             V_SCALE, V_MIN       f32  [max_seq]                per-token
  *             K_RES, V_RES         f32  [32][kv_dim]             residual window
  *   KIVI_G32  K_Q                  u8   [max_seq][kv_dim/4]      byte j of a slot holds channels 4j..4j+3
- *             K_SCALE              f16x2 [max_seq/32][kv_dim]    (scale, zero)
+ *             K_SCALE              f16  [max_seq/32][kv_dim/16][2][16]  per 32-slot group and block of 16
+ *                                       channels: 16 scales, then 16 zero points; channel r of the block at
+ *                                       position 2 (r mod 8) + r div 8
  *             V_Q                  u8   [max_seq][kv_dim/4]
  *             V_SCALE              f16x2 [max_seq][kv_dim/32]    (scale, zero)
  *             K_RES, V_RES         f16  [128][kv_dim]            residual ring, slot % 128

@@ -719,6 +719,12 @@ static void g32_quant_group(const float* vals, uint8_t* codes8, uint16_t* meta2)
     meta2[1] = orc_f32_to_f16(m);
 }
 
+/* Index (in f16 units) of channel c's scale inside a group's key metadata row: per block of 16
+ * channels 16 scales then 16 zero points, channel r of the block at position 2 (r mod 8) + r div 8
+ * (so the pair (r, r+8), whose codes sit 16 bits apart in a code word, is adjacent).  The zero
+ * point is 16 entries further. */
+static size_t g32_kmeta_index(size_t c) { return (c >> 4) * 32 + 2 * (c & 7) + ((c >> 3) & 1); }
+
 /* Quantise key group `group` (ring slots 32*group .. +31) from f16-rounded rows
  * rows_f16[32][kv_dim] (as f32 values). */
 ORC_API void orc_g32_quant_key_group(const float* rows, size_t kv_dim, uint8_t* k_codes_group,
@@ -729,7 +735,10 @@ ORC_API void orc_g32_quant_key_group(const float* rows, size_t kv_dim, uint8_t* 
     memset(k_codes_group, 0, G32 * kv_dim / 4);
     for (size_t c = 0; c < kv_dim; c++) {
         for (int t = 0; t < G32; t++) col[t] = rows[(size_t)t * kv_dim + c];
-        g32_quant_group(col, codes8, k_meta_group + c * 2);          /* codes8: slot t at byte t/4, bits (t%4)*2 */
+        uint16_t meta[2];
+        g32_quant_group(col, codes8, meta);                          /* codes8: slot t at byte t/4, bits (t%4)*2 */
+        k_meta_group[g32_kmeta_index(c)] = meta[0];
+        k_meta_group[g32_kmeta_index(c) + 16] = meta[1];
         for (int t = 0; t < G32; t++) {
             uint8_t q = (uint8_t)((codes8[t / 4] >> ((t % 4) * 2)) & 3);
             k_codes_group[(size_t)t * (kv_dim / 4) + c / 4] |= (uint8_t)(q << ((c % 4) * 2));
@@ -745,7 +754,7 @@ ORC_API void orc_g32_quant_value_row(const float* row, size_t kv_dim, uint8_t* v
 ORC_API void orc_g32_dequant_key_group(const uint8_t* k_codes_group, const uint16_t* k_meta_group,
                                        size_t kv_dim, float* rows_out) {
     for (size_t c = 0; c < kv_dim; c++) {
-        float s = orc_f16_to_f32(k_meta_group[c * 2]), z = orc_f16_to_f32(k_meta_group[c * 2 + 1]);
+        float s = orc_f16_to_f32(k_meta_group[g32_kmeta_index(c)]), z = orc_f16_to_f32(k_meta_group[g32_kmeta_index(c) + 16]);
         for (int t = 0; t < G32; t++) {
             float q = (float)((k_codes_group[(size_t)t * (kv_dim / 4) + c / 4] >> ((c % 4) * 2)) & 3);
             rows_out[(size_t)t * kv_dim + c] = q * s + z;

@@ -201,10 +201,10 @@ def test_g32_long_context_decode_takes_the_tensor_core_path(eng, fb, orc, nh, nk
 
 
 def test_g32_ragged_batch_long_context(eng, fb, orc):
-    """Sequences of different lengths (one long, one short) in one call."""
-    nh, nkv, hd, ms, B = 8, 2, 64, 2048, 2
+    """Sequences of different lengths (long, short, shorter than the residual ring) in one call."""
+    nh, nkv, hd, ms, B = 8, 2, 64, 2048, 3
     kvd = nkv * hd
-    lens = [1700, 300]
+    lens = [1700, 300, 77]
     kv = eng.kv_alloc(1, B, ms, nkv, hd, fb.KV_KIVI_G32)
     q = normal(77, (B, 1, nh, hd), 0.4)
     for b in range(B):
