@@ -225,7 +225,7 @@ int flare_kv_alloc(flare_attn_ctx* ctx, int num_layers, int batch, int max_seq_l
     if (kv_dtype == FLARE_KV_KIVI_G32 && head_dim == 64 && num_kv_heads <= 8) {
         const uint64_t dims[4] = {16, (uint64_t)max_seq_len, (uint64_t)num_kv_heads, (uint64_t)num_layers * batch};
         const uint64_t strides[3] = {(uint64_t)kvd / 4, 16, (uint64_t)max_seq_len * (kvd / 4)};
-        const uint32_t box[4] = {16, 32, (uint32_t)num_kv_heads, 1};
+        const uint32_t box[4] = {16, FLARE_G32_TILE, (uint32_t)num_kv_heads, 1};
         int r1 = flare_make_tensor_map(&kv->g32_kmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, kv->plane[FLARE_PLANE_K_Q], dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
         int r2 = flare_make_tensor_map(&kv->g32_vmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, kv->plane[FLARE_PLANE_V_Q], dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
         kv->has_g32_maps = (r1 == 0 && r2 == 0);     // without them the general kernel serves the cache

@@ -14,6 +14,7 @@
 #include "../../include/flare_attn.h"
 
 #define FLARE_G32_RESIDUAL 128
+#define FLARE_G32_TILE 64          // slots per tile of the group-32 tensor-core decode kernel (TMA box)
 // Group-32 KIVI key metadata: per 32-slot group a row of kv_dim (scale, zero) f16 pairs stored per block of
 // 16 channels as 16 scales then 16 zero points, channel r of the block at position 2 (r mod 8) + r div 8 —
 // the pair (r, r + 8), whose 2-bit codes sit 16 bits apart in a code word, is adjacent.  Index of the scale

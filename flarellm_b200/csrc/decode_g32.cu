@@ -1,6 +1,6 @@
 // Group-32 KIVI (2-bit) split-KV decode attention on tensor cores, for the quantised part of the
 // cache (head_dim 64, up to 4 query heads per KV head, one query per sequence, ring not wrapped).
-// The newest <= 159 tokens (the f16 residual ring and the group that is still filling) go through
+// The newest <= 127 + tile tokens (the f16 residual ring and the group that is still filling) go through
 // the general kernel; the two partial results are merged by log-sum-exp.
 //
 // Same skeleton as the Q8_0 path: one CTA per (sequence, slot range), one warp per KV head, 32-slot
@@ -18,18 +18,18 @@
 //           (column 2h = hi, 2h+1 = lo; q is pre-scaled by a power of two so q*s cannot overflow);
 //           the zero-point term is one more MMA whose A holds z in row 0 and whose B is q itself.
 //   output  O[ch, (h, blk)] = sum_t c[t,ch] (p[t,h] s_v[t,blk])  +  sum_t p[t,h] z_v[t,blk]
-//           A = V codes transposed by ldmatrix.trans (16-bit units hold 8 codes of a slot), left with
-//           their 1024 bias and position weight 4^k (both removed once at the end), B = the f16 weights
-//           p*s_v moved into operand layout by movmatrix; column 2h+blk serves channel block blk;
-//           a row of ones gives the bias sum, the zero-point term is one f32 scalar per (head, block).
+//           A = V codes transposed by ldmatrix.trans (16-bit units hold 8 codes of a slot) and made exact
+//           f16 the same way, B = the f16 weights p*s_v moved into operand layout by movmatrix; column
+//           2h+blk serves channel block blk; the zero-point term is one f32 scalar per (head, block).
 #include "common.cuh"
 #include "tma.cuh"
 #include <math_constants.h>
 
 namespace {
 
-constexpr int T = 32;
-constexpr int STAGES = 4;
+constexpr int T = FLARE_G32_TILE;      // slots per tile: NG key groups
+constexpr int NG = T / 32;
+constexpr int STAGES = FLARE_G32_TILE == 64 ? 3 : 4;
 constexpr int HD = 64;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr uint32_t kMagic = 0x64006400u;      // half2 (1024, 1024): a code OR-ed into the mantissa is 1024 + code * 2^bit
@@ -45,7 +45,7 @@ struct G32Params {
     const unsigned char *k_codes, *v_codes, *k_res, *v_res;
     size_t codes_seq_stride, res_seq_stride;       // bytes
     const int2* ring;
-    int layer_seq0, num_heads, nkv, G, n_split;    // records per row: n_split + 1, the last one from the newest tokens
+    int layer_seq0, num_heads, nkv, G, n_split;
     int* err;
     // 0x64006400 and 0x00030003, passed as arguments so that they live in registers: a logic instruction takes
     // one immediate only, and with both known at compile time every mask-or would become two instructions
@@ -93,119 +93,173 @@ __device__ __forceinline__ uint32_t hneg2(uint32_t a) {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-// weight of the V code of channel 8 g + cc inside the biased f16 value (see the output product)
-__host__ __device__ constexpr float v_code_weight(int cc) { return cc <= 4 ? (float)(1 << (2 * cc)) : (float)(1 << (2 * cc - 6)); }
+// A 2-bit code c masked out at bit 2k of an f16 mantissa and OR-ed with 0x6400 reads 1024 + 4^k c;
+// fma(x, code_mul(k), code_sub(k)) = x / 4^k - 1024 / 4^k = c exactly (half2 constants, k = 0..4).
+__device__ __forceinline__ constexpr uint32_t code_mul(int k) {
+    return k == 0 ? 0x3c003c00u : k == 1 ? 0x34003400u : k == 2 ? 0x2c002c00u : k == 3 ? 0x24002400u : 0x1c001c00u;
+}
+__device__ __forceinline__ constexpr uint32_t code_sub(int k) {
+    return k == 0 ? 0xe400e400u : k == 1 ? 0xdc00dc00u : k == 2 ? 0xd400d400u : k == 3 ? 0xcc00cc00u : 0xc400c400u;
+}
 
-// The newest tokens of a sequence (slots lim .. n-1, at most 159): the f16 residual ring for the last 128
-// and 2-bit codes for the few older ones whose group-aligned prefix the tile loop does not cover.  One warp
-// per KV head on CUDA cores: lanes own slots for the scores, then channel pairs for the output.
-__device__ void g32_newest_tokens(const G32Params& p, int b, int kvh, int lane, int lim, int n, float* ws) {
-    constexpr int MAXT = 160;
+// Scratch of one warp for its share of the newest tokens, kept until the end of the kernel.
+struct NewestScratch {
+    float qo[4 * HD];      // q of the warp's (up to) 4 heads, later their unnormalised outputs
+    float p[4 * 32];       // weights of the current 32-slot chunk
+    float m[4], l[4];      // running maximum (log2 units) and sum per head
+};
+
+// State of the newest-token routine across chunks.
+struct NewestState {
+    float m[4], l[4], acc[4][2];
+};
+
+// One chunk of up to 32 slots c0 .. c0+cn-1, all served by the f16 ring (RING) or all by 2-bit codes.
+// Lanes own slots for the scores, then channels 2 lane, 2 lane + 1 for the output.  Every global load of
+// the chunk is issued before the first use, so that they are in flight together.
+template <bool RING>
+__device__ __forceinline__ void g32_newest_chunk(const G32Params& p, int b, int kvh, int lane, int c0, int cn, bool& have_q,
+                                                 NewestScratch* ws, NewestState& st) {
     const int kv_dim = p.nkv * HD, G = p.G;
-    float* q_s = ws;                 // [4][HD]
-    float* p_s = ws + 4 * HD;        // [4][MAXT]
-    const int newest = p.ring[b].x;  // ring not wrapped: slot index = token index
-    const float sc = rsqrtf((float)HD) * kLog2e;
-    for (int i = lane; i < 4 * HD; i += 32) {
-        const int h = i / HD;
-        q_s[i] = h < G ? __ldg(p.q + ((size_t)b * p.num_heads + kvh * G + h) * HD + (i % HD)) * sc : 0.0f;
+    float* q_s = ws->qo;
+    float* p_s = ws->p;
+    const int t = c0 + lane;
+    const bool mine = lane < cn;
+    // values
+    uint32_t va[32], vb[RING ? 1 : 32];
+    if (RING) {
+        const unsigned char* vres = p.v_res + (size_t)b * p.res_seq_stride + (size_t)kvh * HD * 2 + lane * 4;
+#pragma unroll
+        for (int u = 0; u < 32; u++)
+            va[u] = u < cn ? __ldg(reinterpret_cast<const uint32_t*>(vres + (size_t)((c0 + u) % FLARE_G32_RESIDUAL) * kv_dim * 2)) : 0u;
+    } else {
+        const unsigned char* vcod = p.v_codes + (size_t)b * p.codes_seq_stride + kvh * (HD / 4) + ((lane >> 1) & ~3);
+        const unsigned char* vmeta = p.v_meta + (size_t)b * p.v_meta_seq_stride + (size_t)(kvh * (HD / 32) + (lane >> 4)) * 4;
+#pragma unroll
+        for (int u = 0; u < 32; u++) {
+            va[u] = u < cn ? __ldg(reinterpret_cast<const uint32_t*>(vcod + (size_t)(c0 + u) * (kv_dim / 4))) : 0u;
+            vb[u] = u < cn ? __ldg(reinterpret_cast<const uint32_t*>(vmeta + (size_t)(c0 + u) * (kv_dim / 32) * 4)) : 0u;
+        }
     }
-    __syncwarp();
-    const unsigned char* kres = p.k_res + (size_t)b * p.res_seq_stride;
-    const unsigned char* vres = p.v_res + (size_t)b * p.res_seq_stride;
-    const unsigned char* kcod = p.k_codes + (size_t)b * p.codes_seq_stride;
-    const unsigned char* vcod = p.v_codes + (size_t)b * p.codes_seq_stride;
-    const __half* kmeta = reinterpret_cast<const __half*>(p.k_meta + (size_t)b * p.k_meta_seq_stride);
-    const __half2* vmeta = reinterpret_cast<const __half2*>(p.v_meta + (size_t)b * p.v_meta_seq_stride);
-    const int count = n - lim;
-
-    float mx[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
-    for (int i0 = 0; i0 < count; i0 += 32) {
-        const int t = lim + i0 + lane;
-        float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        if (t < n) {
-            if (newest - t < FLARE_G32_RESIDUAL) {
-                const uint4* row = reinterpret_cast<const uint4*>(kres + ((size_t)(t % FLARE_G32_RESIDUAL) * kv_dim + kvh * HD) * 2);
+    // keys of this lane's slot: the f16 row, or the 16 code bytes
+    uint4 w[RING ? HD / 8 : 1];
+    if (RING) {
+        const uint4* row = reinterpret_cast<const uint4*>(p.k_res + (size_t)b * p.res_seq_stride + ((size_t)(t % FLARE_G32_RESIDUAL) * kv_dim + kvh * HD) * 2);
 #pragma unroll
-                for (int c8 = 0; c8 < HD / 8; c8++) {
-                    const uint4 w = __ldg(row + c8);
-                    const __half2* h2 = reinterpret_cast<const __half2*>(&w);
-                    float k[8];
+        for (int c8 = 0; c8 < HD / 8; c8++) w[c8] = mine ? __ldg(row + c8) : make_uint4(0u, 0u, 0u, 0u);
+    } else {
+        w[0] = mine ? __ldg(reinterpret_cast<const uint4*>(p.k_codes + (size_t)b * p.codes_seq_stride + (size_t)t * (kv_dim / 4) + kvh * (HD / 4)))
+                    : make_uint4(0u, 0u, 0u, 0u);
+    }
+    if (!have_q) {
+        const float sc = rsqrtf((float)HD) * kLog2e;
+        float qr[4 * HD / 32];
 #pragma unroll
-                    for (int j = 0; j < 4; j++) { const float2 f = __half22float2(h2[j]); k[2 * j] = f.x; k[2 * j + 1] = f.y; }
+        for (int k = 0; k < 4 * HD / 32; k++) {
+            const int i = lane + 32 * k, h = i / HD;
+            qr[k] = h < G ? __ldg(p.q + ((size_t)b * p.num_heads + kvh * G + h) * HD + (i % HD)) : 0.0f;
+        }
 #pragma unroll
-                    for (int h = 0; h < 4; h++)
+        for (int k = 0; k < 4 * HD / 32; k++) q_s[lane + 32 * k] = qr[k] * sc;
+        have_q = true;
+    }
+    __syncwarp();                                   // q is there; the previous chunk's weights have been consumed
+    // ---- scores ----------------------------------------------------------------------------------------
+    float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    if (RING) {
 #pragma unroll
-                        for (int j = 0; j < 8; j++) s[h] = fmaf(q_s[h * HD + c8 * 8 + j], k[j], s[h]);
-                }
-            } else {
-                const uint4 cw = __ldg(reinterpret_cast<const uint4*>(kcod + (size_t)t * (kv_dim / 4) + kvh * (HD / 4)));
-                const uint32_t w4[4] = {cw.x, cw.y, cw.z, cw.w};
-                const __half* mrow = kmeta + (size_t)(t >> 5) * kv_dim * 2;
+        for (int c8 = 0; c8 < HD / 8; c8++) {
+            const __half2* h2 = reinterpret_cast<const __half2*>(&w[c8]);
+            float k[8];
 #pragma unroll
-                for (int wi = 0; wi < 4; wi++)
-#pragma unroll 4
-                    for (int j = 0; j < 16; j++) {
-                        const int c = kvh * HD + wi * 16 + j;
-                        const float k = q2_dequant((float)((w4[wi] >> (2 * j)) & 3u), __half2float(__ldg(mrow + FLARE_G32_KMETA_INDEX(c))),
-                                                   __half2float(__ldg(mrow + FLARE_G32_KMETA_INDEX(c) + 16)));
+            for (int j = 0; j < 4; j++) { const float2 f = __half22float2(h2[j]); k[2 * j] = f.x; k[2 * j + 1] = f.y; }
 #pragma unroll
-                        for (int h = 0; h < 4; h++) s[h] = fmaf(q_s[h * HD + wi * 16 + j], k, s[h]);
-                    }
+            for (int h = 0; h < 4; h++)
+#pragma unroll
+                for (int j = 0; j < 8; j++) s[h] = fmaf(q_s[h * HD + c8 * 8 + j], k[j], s[h]);
+        }
+    } else if (mine) {
+        const uint32_t w4[4] = {w[0].x, w[0].y, w[0].z, w[0].w};
+        // the group's metadata: per 16-channel block 16 scales then 16 zero points, pair (r, r+8) adjacent
+        const uint4* mrow = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(p.k_meta + (size_t)b * p.k_meta_seq_stride) +
+                                                           (size_t)(t >> 5) * kv_dim * 2 + (size_t)kvh * (HD / 16) * 32);
+#pragma unroll
+        for (int wi = 0; wi < 4; wi++) {
+            const uint4 m4[4] = {__ldg(mrow + 4 * wi), __ldg(mrow + 4 * wi + 1), __ldg(mrow + 4 * wi + 2), __ldg(mrow + 4 * wi + 3)};
+            const __half2* sp = reinterpret_cast<const __half2*>(&m4[0]);
+            const __half2* zp = reinterpret_cast<const __half2*>(&m4[2]);
+#pragma unroll
+            for (int r = 0; r < 8; r++) {
+                const float2 sf = __half22float2(sp[r]), zf = __half22float2(zp[r]);
+                const float k0 = q2_dequant((float)((w4[wi] >> (2 * r)) & 3u), sf.x, zf.x);            // channel r
+                const float k1 = q2_dequant((float)((w4[wi] >> (2 * r + 16)) & 3u), sf.y, zf.y);       // channel r + 8
+#pragma unroll
+                for (int h = 0; h < 4; h++)
+                    s[h] = fmaf(q_s[h * HD + wi * 16 + r + 8], k1, fmaf(q_s[h * HD + wi * 16 + r], k0, s[h]));
             }
         }
-#pragma unroll
-        for (int h = 0; h < 4; h++) {
-            const float v = t < n ? s[h] : -CUDART_INF_F;
-            p_s[h * MAXT + i0 + lane] = v;
-            mx[h] = fmaxf(mx[h], v);
-        }
     }
-    float l[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    // ---- online softmax over the chunk -------------------------------------------------------------
 #pragma unroll
     for (int h = 0; h < 4; h++) {
+        float v = mine ? s[h] : -CUDART_INF_F, cm = v;
 #pragma unroll
-        for (int o = 16; o; o >>= 1) mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], o));
-        for (int i = lane; i < count; i += 32) {
-            const float e = fast_exp2(p_s[h * MAXT + i] - mx[h]);
-            p_s[h * MAXT + i] = e;
-            l[h] += e;
-        }
+        for (int o = 16; o; o >>= 1) cm = fmaxf(cm, __shfl_xor_sync(0xffffffffu, cm, o));
+        const float m_new = fmaxf(st.m[h], cm);     // finite: the chunk is not empty
+        const float alpha = fast_exp2(st.m[h] - m_new);
+        const float e = mine ? fast_exp2(v - m_new) : 0.0f;
+        float sum = e;
 #pragma unroll
-        for (int o = 16; o; o >>= 1) l[h] += __shfl_xor_sync(0xffffffffu, l[h], o);
+        for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        p_s[h * 32 + lane] = e;
+        st.l[h] = st.l[h] * alpha + sum;
+        st.acc[h][0] *= alpha; st.acc[h][1] *= alpha;
+        st.m[h] = m_new;
     }
     __syncwarp();
-    // output: this lane owns channels 2 lane, 2 lane + 1 of the head
-    float acc[4][2] = {};
-    for (int i = 0; i < count; i++) {
-        const int t = lim + i;
+    // ---- output --------------------------------------------------------------------------------------
+#pragma unroll
+    for (int u = 0; u < 32; u++) {
         float v0, v1;
-        if (newest - t < FLARE_G32_RESIDUAL) {
-            const float2 f = __half22float2(__ldg(reinterpret_cast<const __half2*>(vres + ((size_t)(t % FLARE_G32_RESIDUAL) * kv_dim + kvh * HD) * 2) + lane));
-            v0 = f.x; v1 = f.y;
+        if (RING) {
+            const float2 fr = __half22float2(*reinterpret_cast<const __half2*>(&va[u]));
+            v0 = fr.x; v1 = fr.y;
         } else {
-            const uint32_t byte = __ldg(vcod + (size_t)t * (kv_dim / 4) + kvh * (HD / 4) + (lane >> 1));
-            const float2 m = __half22float2(__ldg(vmeta + (size_t)t * (kv_dim / 32) + kvh * (HD / 32) + (lane >> 4)));
-            v0 = q2_dequant((float)((byte >> ((lane & 1) * 4)) & 3u), m.x, m.y);
-            v1 = q2_dequant((float)((byte >> ((lane & 1) * 4 + 2)) & 3u), m.x, m.y);
+            const float2 mz = __half22float2(*reinterpret_cast<const __half2*>(&vb[u]));
+            const uint32_t byte = va[u] >> (((lane >> 1) & 3) * 8);
+            v0 = q2_dequant((float)((byte >> ((lane & 1) * 4)) & 3u), mz.x, mz.y);
+            v1 = q2_dequant((float)((byte >> ((lane & 1) * 4 + 2)) & 3u), mz.x, mz.y);
         }
 #pragma unroll
         for (int h = 0; h < 4; h++) {
-            const float w = p_s[h * MAXT + i];
-            acc[h][0] = fmaf(w, v0, acc[h][0]);
-            acc[h][1] = fmaf(w, v1, acc[h][1]);
+            const float wgt = p_s[h * 32 + u];       // 0 beyond the chunk
+            st.acc[h][0] = fmaf(wgt, v0, st.acc[h][0]);
+            st.acc[h][1] = fmaf(wgt, v1, st.acc[h][1]);
         }
-    }
-#pragma unroll
-    for (int h = 0; h < 4; h++) {
-        if (h >= G) break;
-        const size_t row = (size_t)b * p.num_heads + kvh * G + h;
-        float* wrec = p.work + (row * (p.n_split + 1) + p.n_split) * (HD + 2);
-        *reinterpret_cast<float2*>(wrec + 2 + 2 * lane) = make_float2(acc[h][0], acc[h][1]);
-        if (lane == 0) { wrec[0] = count > 0 ? mx[h] : 0.0f; wrec[1] = l[h]; }
     }
 }
 
+// The newest tokens [t0, t1) of a sequence — 2-bit codes for the few that are older than the residual
+// ring and that the group-aligned tile loop does not cover, then the f16 ring for the last 128.  One warp
+// per KV head on CUDA cores, 32 slots at a time with an online softmax.  Leaves (m, l, o) per head in `ws`.
+__device__ __noinline__ void g32_newest_tokens(const G32Params& p, int b, int kvh, int lane, int t0, int t1, NewestScratch* ws) {
+    const int newest = p.ring[b].x;  // ring not wrapped: slot index = token index
+    NewestState st;
+#pragma unroll
+    for (int h = 0; h < 4; h++) { st.m[h] = -CUDART_INF_F; st.l[h] = 0.0f; st.acc[h][0] = st.acc[h][1] = 0.0f; }
+    int t_ring = newest - (FLARE_G32_RESIDUAL - 1);          // first slot that the ring serves
+    t_ring = t_ring < t0 ? t0 : (t_ring > t1 ? t1 : t_ring);
+    bool have_q = false;
+    for (int c0 = t0; c0 < t_ring; c0 += 32) g32_newest_chunk<false>(p, b, kvh, lane, c0, min(32, t_ring - c0), have_q, ws, st);
+    for (int c0 = t_ring; c0 < t1; c0 += 32) g32_newest_chunk<true>(p, b, kvh, lane, c0, min(32, t1 - c0), have_q, ws, st);
+    __syncwarp();                                       // q is dead: its place takes the outputs
+#pragma unroll
+    for (int h = 0; h < 4; h++) {
+        *reinterpret_cast<float2*>(ws->qo + h * HD + 2 * lane) = make_float2(st.acc[h][0], st.acc[h][1]);
+        if (lane == 0) { ws->m[h] = st.m[h]; ws->l[h] = st.l[h]; }
+    }
+    __syncwarp();
+}
 
 __global__ void __launch_bounds__(256, 2) decode_g32_kernel(const __grid_constant__ CUtensorMap kmap,
                                                             const __grid_constant__ CUtensorMap vmap, G32Params p) {
@@ -218,19 +272,26 @@ __global__ void __launch_bounds__(256, 2) decode_g32_kernel(const __grid_constan
     const int split = blockIdx.x, b = blockIdx.y;
     const int nkv = p.nkv, kvh = warp;
     const int kv_dim = nkv * HD;
-    // stage: K codes [nkv][T][16], V codes [nkv][T][16], K meta [kv_dim] half2, V meta [T][nkv*2] half2
+    // stage: K codes [nkv][T][16], V codes [nkv][T][16], K meta of NG groups [NG][kv_dim] x 4 B, V meta [T][nkv*2] half2
     const int codes = nkv * T * 16;
-    const int kmeta_bytes = kv_dim * 4, vmeta_bytes = T * nkv * 2 * 4;
+    const int kmeta_bytes = NG * kv_dim * 4, vmeta_bytes = T * nkv * 2 * 4;
     const int stage_bytes = 2 * codes + kmeta_bytes + vmeta_bytes;
     unsigned char* sbase = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
 
     // quantised slots of this sequence: everything older than the newest 128 tokens, in whole groups
     const int n = p.attend_len[b];
     const int lim_tiles = n > 128 ? (n - 128) / T : 0;
-    if (split == p.n_split) {            // the CTA of the newest tokens
+    if (split == p.n_split) {            // the CTA of the newest tokens: one more record per row
         pdl_wait();
-        g32_newest_tokens(p, b, kvh, lane, lim_tiles * T, n, reinterpret_cast<float*>(sbase) + warp * (4 * HD + 4 * 160));
+        NewestScratch* ws = reinterpret_cast<NewestScratch*>(sbase) + warp;
+        g32_newest_tokens(p, b, kvh, lane, lim_tiles * T, n, ws);
         pdl_trigger();
+        for (int h = 0; h < p.G; h++) {
+            const size_t row = (size_t)b * p.num_heads + kvh * p.G + h;
+            float* wrec = p.work + (row * (p.n_split + 1) + split) * (HD + 2);
+            *reinterpret_cast<float2*>(wrec + 2 + 2 * lane) = *reinterpret_cast<const float2*>(ws->qo + h * HD + 2 * lane);
+            if (lane == 0) { wrec[0] = ws->l[h] > 0.0f ? ws->m[h] : 0.0f; wrec[1] = ws->l[h]; }
+        }
         return;
     }
     const int t_begin = (int)(((long long)split * lim_tiles) / p.n_split);
@@ -296,7 +357,6 @@ __global__ void __launch_bounds__(256, 2) decode_g32_kernel(const __grid_constan
                 qhz[ks][bb] = lo_col ? h : 0u;
             }
     }
-    const uint32_t ones = g == 0 ? 0x3c003c00u : 0u;               // half2 (1, 1) in row 0 of an A operand
     const uint32_t magic = p.magic;
     uint32_t cmask[5];                                             // a code at bit 0, 2, 4, 6, 8 of both halves
 #pragma unroll
@@ -307,7 +367,6 @@ __global__ void __launch_bounds__(256, 2) decode_g32_kernel(const __grid_constan
     for (int j = 0; j < 4; j++)
 #pragma unroll
         for (int k = 0; k < 4; k++) acc[j][k] = 0.0f;
-    float dl[4] = {0.0f, 0.0f, 0.0f, 0.0f};     // row 0: sum of the f16 weights per column
     float m_run = -CUDART_INF_F, l_run = 0.0f, zacc0 = 0.0f, zacc1 = 0.0f;
 
     bool failed = false;
@@ -317,55 +376,60 @@ __global__ void __launch_bounds__(256, 2) decode_g32_kernel(const __grid_constan
         const unsigned char* st = sbase + (size_t)s * stage_bytes;
         const unsigned char* kc = st + kvh * (T * 16);
         const uint32_t vc = ptx::smem_u32(st + codes + kvh * (T * 16));
-        const uint4* kmeta = reinterpret_cast<const uint4*>(st + 2 * codes + (kvh * 4 + tig) * 64);   // 16 scales, 16 zeros
+        const unsigned char* kmeta0 = st + 2 * codes + (kvh * 4 + tig) * 64;                        // 16 scales, 16 zeros
         const uint2* vmeta = reinterpret_cast<const uint2*>(st + 2 * codes + kmeta_bytes) + kvh;
 
-        // ---- B = (q s) hi/lo for this group; the zero-point term as row 0 of one more product ---------
-        uint32_t bq[4][2];
-        float dz[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        {
-            const uint4 sa = kmeta[0], sb = kmeta[1];
-            uint4 za = make_uint4(0u, 0u, 0u, 0u), zb = za;
-            if (g == 0) { za = kmeta[2]; zb = kmeta[3]; }
-            const uint32_t s2[8] = {sa.x, sa.y, sa.z, sa.w, sb.x, sb.y, sb.z, sb.w};     // pair p: channels (p, p + 8)
-            const uint32_t z2[8] = {za.x, za.y, za.z, za.w, zb.x, zb.y, zb.z, zb.w};
+        float sc[4 * NG];                                   // sc[r]: slot 8 r + g of the tile, head tig
 #pragma unroll
-            for (int ks = 0; ks < 4; ks++) {
+        for (int gi = 0; gi < NG; gi++) {
+            // ---- B = (q s) hi/lo for this group; the zero-point term as row 0 of one more product ---------
+            const uint4* kmeta = reinterpret_cast<const uint4*>(kmeta0 + gi * (kmeta_bytes / NG));
+            uint32_t bq[4][2];
+            float dz[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            {
+                const uint4 sa = kmeta[0], sb = kmeta[1];
+                uint4 za = make_uint4(0u, 0u, 0u, 0u), zb = za;
+                if (g == 0) { za = kmeta[2]; zb = kmeta[3]; }
+                const uint32_t s2[8] = {sa.x, sa.y, sa.z, sa.w, sb.x, sb.y, sb.z, sb.w};     // pair p: channels (p, p + 8)
+                const uint32_t z2[8] = {za.x, za.y, za.z, za.w, zb.x, zb.y, zb.z, zb.w};
 #pragma unroll
-                for (int bb = 0; bb < 2; bb++) {
-                    const uint32_t sv = s2[ks + 4 * bb];
-                    const uint32_t ph = hmul2(qhz[ks][bb], sv);                  // lo columns: rounded hi product
-                    const uint32_t er = hfma2(qhz[ks][bb], sv, hneg2(ph));       //             its exact rounding error
-                    bq[ks][bb] = hfma2(qx[ks][bb], sv, er);                      // hi columns: round(q_hi s); lo: q_lo s + error
+                for (int ks = 0; ks < 4; ks++) {
+#pragma unroll
+                    for (int bb = 0; bb < 2; bb++) {
+                        const uint32_t sv = s2[ks + 4 * bb];
+                        const uint32_t ph = hmul2(qhz[ks][bb], sv);                  // lo columns: rounded hi product
+                        const uint32_t er = hfma2(qhz[ks][bb], sv, hneg2(ph));       //             its exact rounding error
+                        bq[ks][bb] = hfma2(qx[ks][bb], sv, er);                      // hi columns: round(q_hi s); lo: q_lo s + error
+                    }
+                    mma_f16(dz, z2[ks], 0u, z2[ks + 4], 0u, qx[ks][0], qx[ks][1]);
                 }
-                mma_f16(dz, z2[ks], 0u, z2[ks + 4], 0u, qx[ks][0], qx[ks][1]);
             }
-        }
-        const float zd = __shfl_sync(0xffffffffu, dz[0] + dz[1], tig);           // row 0 lives in lanes g = 0
+            const float zd = __shfl_sync(0xffffffffu, dz[0] + dz[1], tig);           // row 0 lives in lanes g = 0
 
-        // ---- scores of slots 16 mt + g and 16 mt + 8 + g for head tig -----------------------------------
-        float sc[4];
+            // ---- scores of slots 32 gi + 16 mt + g and + 8 for head tig -----------------------------------
 #pragma unroll
-        for (int mt = 0; mt < 2; mt++) {
-            const uint32_t wa = *reinterpret_cast<const uint32_t*>(kc + (16 * mt + g) * 16 + 4 * tig);
-            const uint32_t wb = *reinterpret_cast<const uint32_t*>(kc + (16 * mt + 8 + g) * 16 + 4 * tig);
-            const uint32_t wa8 = wa >> 8, wb8 = wb >> 8;
-            float d[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            for (int mt = 0; mt < 2; mt++) {
+                const uint32_t wa = *reinterpret_cast<const uint32_t*>(kc + (32 * gi + 16 * mt + g) * 16 + 4 * tig);
+                const uint32_t wb = *reinterpret_cast<const uint32_t*>(kc + (32 * gi + 16 * mt + 8 + g) * 16 + 4 * tig);
+                const uint32_t wa8 = wa >> 8, wb8 = wb >> 8;
+                float d[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-            for (int ks = 0; ks < 4; ks++) {
-                // a code at bit 2 ks of a half becomes 1024 + 4^ks code; one fma scales and removes the bias exactly
-                const uint32_t mul = ks == 0 ? 0x3c003c00u : ks == 1 ? 0x34003400u : ks == 2 ? 0x2c002c00u : 0x24002400u;
-                const uint32_t sub = ks == 0 ? 0xe400e400u : ks == 1 ? 0xdc00dc00u : ks == 2 ? 0xd400d400u : 0xcc00cc00u;
-                const uint32_t a0 = hfma2(and_or(wa, cmask[ks], magic), mul, sub);
-                const uint32_t a1 = hfma2(and_or(wb, cmask[ks], magic), mul, sub);
-                const uint32_t a2 = hfma2(and_or(wa8, cmask[ks], magic), mul, sub);
-                const uint32_t a3 = hfma2(and_or(wb8, cmask[ks], magic), mul, sub);
-                mma_f16(d, a0, a1, a2, a3, bq[ks][0], bq[ks][1]);
+                for (int ks = 0; ks < 4; ks++) {
+                    // a code at bit 2 ks of a half becomes 1024 + 4^ks code; one fma scales and removes the bias exactly
+                    const uint32_t mul = code_mul(ks), sub = code_sub(ks);
+                    const uint32_t a0 = hfma2(and_or(wa, cmask[ks], magic), mul, sub);
+                    const uint32_t a1 = hfma2(and_or(wb, cmask[ks], magic), mul, sub);
+                    const uint32_t a2 = hfma2(and_or(wa8, cmask[ks], magic), mul, sub);
+                    const uint32_t a3 = hfma2(and_or(wb8, cmask[ks], magic), mul, sub);
+                    mma_f16(d, a0, a1, a2, a3, bq[ks][0], bq[ks][1]);
+                }
+                sc[4 * gi + 2 * mt] = (d[0] + d[1] + zd) * unscale;
+                sc[4 * gi + 2 * mt + 1] = (d[2] + d[3] + zd) * unscale;
             }
-            sc[2 * mt] = (d[0] + d[1] + zd) * unscale;
-            sc[2 * mt + 1] = (d[2] + d[3] + zd) * unscale;
         }
-        float tmax = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
+        float tmax = sc[0];
+#pragma unroll
+        for (int r = 1; r < 4 * NG; r++) tmax = fmaxf(tmax, sc[r]);
         tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 4));
         tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 8));
         tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 16));
@@ -375,16 +439,14 @@ __global__ void __launch_bounds__(256, 2) decode_g32_kernel(const __grid_constan
             if (bump) m_run = tmax;
             l_run *= alpha; zacc0 *= alpha; zacc1 *= alpha;
 #pragma unroll
-            for (int k = 0; k < 4; k++) dl[k] *= alpha;
-#pragma unroll
             for (int j = 0; j < 4; j++)
 #pragma unroll
                 for (int k = 0; k < 4; k++) acc[j][k] *= alpha;
         }
         // ---- weights p * s_v[t, blk] as f16 (column 2 tig + blk of the 8x8 slot-by-column matrices) ----
-        uint32_t bp[4];
+        uint32_t bp[4 * NG];
 #pragma unroll
-        for (int r = 0; r < 4; r++) {                       // slot 8 r + g
+        for (int r = 0; r < 4 * NG; r++) {                  // slot 8 r + g
             const float pr = fast_exp2(sc[r] - m_run);
             l_run += pr;
             const uint2 mv = vmeta[(size_t)(8 * r + g) * nkv];          // (scale, zero) of blocks 0 and 1
@@ -394,22 +456,26 @@ __global__ void __launch_bounds__(256, 2) decode_g32_kernel(const __grid_constan
             bp[r] = movmatrix_trans(pack_half2(pr * m0.x, pr * m1.x));
         }
         // ---- output ----------------------------------------------------------------------------------------
-        uint32_t rr[4];
-        ldmatrix_x4_trans(rr, vc + lane * 16);          // matrix m = slots 8m .. 8m+7, 16 bytes (64 codes) per slot
 #pragma unroll
-        for (int kstep = 0; kstep < 2; kstep++) {
-            const uint32_t r0 = rr[2 * kstep], r1 = rr[2 * kstep + 1];
-            const uint32_t r0s = r0 >> 6, r1s = r1 >> 6;
-            mma_f16(dl, ones, 0u, ones, 0u, bp[2 * kstep], bp[2 * kstep + 1]);
+        for (int gi = 0; gi < NG; gi++) {
+            uint32_t rr[4];
+            ldmatrix_x4_trans(rr, vc + gi * 512 + lane * 16);   // matrix m = slots 32 gi + 8m .. +7, 16 bytes (64 codes) per slot
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const int c0 = 2 * j, c1 = 2 * j + 1;
-                const uint32_t m0 = cmask[c0 <= 4 ? c0 : c0 - 3], m1 = cmask[c1 <= 4 ? c1 : c1 - 3];
-                const uint32_t a0 = and_or(c0 <= 4 ? r0 : r0s, m0, magic);
-                const uint32_t a1 = and_or(c1 <= 4 ? r0 : r0s, m1, magic);
-                const uint32_t a2 = and_or(c0 <= 4 ? r1 : r1s, m0, magic);
-                const uint32_t a3 = and_or(c1 <= 4 ? r1 : r1s, m1, magic);
-                mma_f16(acc[j], a0, a1, a2, a3, bp[2 * kstep], bp[2 * kstep + 1]);
+            for (int kstep = 0; kstep < 2; kstep++) {
+                const uint32_t r0 = rr[2 * kstep], r1 = rr[2 * kstep + 1];
+                const uint32_t r0s = r0 >> 6, r1s = r1 >> 6;
+                const uint32_t b0 = bp[4 * gi + 2 * kstep], b1 = bp[4 * gi + 2 * kstep + 1];
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    // channel 8g + c: its code sits at bit 2c of the 16-bit unit, or at bit 2c - 6 after the shift
+                    const int c0 = 2 * j, c1 = 2 * j + 1;
+                    const int k0 = c0 <= 4 ? c0 : c0 - 3, k1 = c1 <= 4 ? c1 : c1 - 3;
+                    const uint32_t a0 = hfma2(and_or(c0 <= 4 ? r0 : r0s, cmask[k0], magic), code_mul(k0), code_sub(k0));
+                    const uint32_t a1 = hfma2(and_or(c1 <= 4 ? r0 : r0s, cmask[k1], magic), code_mul(k1), code_sub(k1));
+                    const uint32_t a2 = hfma2(and_or(c0 <= 4 ? r1 : r1s, cmask[k0], magic), code_mul(k0), code_sub(k0));
+                    const uint32_t a3 = hfma2(and_or(c1 <= 4 ? r1 : r1s, cmask[k1], magic), code_mul(k1), code_sub(k1));
+                    mma_f16(acc[j], a0, a1, a2, a3, b0, b1);
+                }
             }
         }
 
@@ -434,16 +500,15 @@ __global__ void __launch_bounds__(256, 2) decode_g32_kernel(const __grid_constan
         zacc1 += __shfl_xor_sync(0xffffffffu, zacc1, o);
     }
     const int blk = g >> 2;                                            // channels 8g .. 8g+7 lie in block g >> 2
-    const float lb0 = __shfl_sync(0xffffffffu, dl[0], tig), lb1 = __shfl_sync(0xffffffffu, dl[1], tig);
     if (tig >= p.G) return;
-    const float bias = 1024.0f * (blk ? lb1 : lb0), zp = blk ? zacc1 : zacc0;
+    const float zp = blk ? zacc1 : zacc0;
     const size_t row = (size_t)b * p.num_heads + kvh * p.G + tig;
     float* wrec = p.work + (row * (p.n_split + 1) + split) * (HD + 2);
     float o8[8];
 #pragma unroll
     for (int j = 0; j < 4; j++) {
-        o8[2 * j] = ((blk ? acc[j][1] : acc[j][0]) - bias) * (1.0f / v_code_weight(2 * j)) + zp;
-        o8[2 * j + 1] = ((blk ? acc[j][3] : acc[j][2]) - bias) * (1.0f / v_code_weight(2 * j + 1)) + zp;
+        o8[2 * j] = (blk ? acc[j][1] : acc[j][0]) + zp;
+        o8[2 * j + 1] = (blk ? acc[j][3] : acc[j][2]) + zp;
     }
 #pragma unroll
     for (int k = 0; k < 8; k++) wrec[2 + 8 * g + k] = o8[k];
@@ -483,8 +548,8 @@ bool flare_decode_g32_supported(const DecodeArgs& a, const flare_kv* kv) {
     return a.max_attend >= 1024;
 }
 
-// One CTA per (sequence, slot range) over the quantised prefix plus one CTA per sequence for the newest
-// tokens, then the merge of their records into a.out.
+// One CTA per (sequence, slot range of the quantised prefix) plus one per sequence for the newest tokens,
+// then the merge of their records into a.out.
 int flare_launch_decode_g32(flare_attn_ctx* ctx, const DecodeArgs& a, const flare_kv* kv) {
     const int nkv = a.kv.num_kv_heads, rows = a.batch * a.num_heads;
     G32Params p;
@@ -503,11 +568,10 @@ int flare_launch_decode_g32(flare_attn_ctx* ctx, const DecodeArgs& a, const flar
     p.num_heads = a.num_heads; p.nkv = nkv; p.G = a.num_heads / nkv;
     p.err = ctx->d_err;
     p.magic = kMagic; p.mask3 = 0x00030003u;
-    const size_t stage = 2 * (size_t)nkv * T * 16 + (size_t)nkv * HD * 4 + (size_t)T * nkv * 2 * 4;
+    const size_t stage = 2 * (size_t)nkv * T * 16 + (size_t)NG * nkv * HD * 4 + (size_t)T * nkv * 2 * 4;
     size_t smem = STAGES * stage + 128;
-    const size_t tail_smem = (size_t)nkv * (4 * HD + 4 * 160) * sizeof(float) + 128;
-    if (smem < tail_smem) smem = tail_smem;
-    // all CTAs resident at once (two per SM): n_split ranges and one newest-token CTA per sequence
+    if (smem < (size_t)nkv * sizeof(NewestScratch) + 128) smem = (size_t)nkv * sizeof(NewestScratch) + 128;
+    // all CTAs resident at once (two per SM): n_split slot ranges and one newest-token CTA per sequence
     int n_split = (ctx->sm_count * 2) / a.batch - 1;
     const int max_split = (a.max_attend / T + 7) / 8;
     if (n_split > max_split) n_split = max_split;
@@ -521,7 +585,7 @@ int flare_launch_decode_g32(flare_attn_ctx* ctx, const DecodeArgs& a, const flar
     static bool attr_done[64] = {};
     if (!attr_done[ctx->device & 63]) {
         FLARE_CUDA_OK(ctx, cudaFuncSetAttribute(decode_g32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                (int)(STAGES * (2 * 8 * T * 16 + 8 * HD * 4 + T * 8 * 2 * 4) + 128)));
+                                                (int)(STAGES * (2 * 8 * T * 16 + NG * 8 * HD * 4 + T * 8 * 2 * 4) + 128)));
         attr_done[ctx->device & 63] = true;
     }
     // Programmatic dependent launch as in the Q8_0 path: after one of this library's own attention kernels
