@@ -198,7 +198,7 @@ def case_prefill(args):
     """BASELINE.json configs[3]: Llama-3-8B-shaped causal prefill, bf16, S 4096, batch 4 per GPU
     (--window 4096: the sliding-window variant at S 8192).  Tensor-bound: flops over causal pairs."""
     torch, fb, dist, eng, stream, rank, world, local = _setup(args)
-    B, nh, nkv, hd = 4, 32, 8, 128
+    B, nh, nkv, hd = (args.batch if args.batch != BATCH else 4), 32, 8, 128     # --batch: smaller case for ncu
     W = args.window
     S = 8192 if W else 4096
     gen = torch.Generator(device="cuda").manual_seed(3 + rank)
@@ -312,7 +312,22 @@ def case_kivi(args):
     o = torch.empty(B, 1, nh, hd, device="cuda")
     kv.write_step(0, knew.data_ptr(), knew.data_ptr())
     fn = lambda: eng.decode(kv, 0, nh, q.data_ptr(), out=o.data_ptr())
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
     ms = _timed(torch, dist, stream, fn, args.steps, max(3, args.warmup))
+    clocks = sampler.stop() if sampler else None
+    check = None
+    if rank == 0 and not args.no_cpu:
+        import oracle
+        worst, ok = 0.0, True
+        for b in (0, B - 1):
+            kd, vd = kv.export_dequant(0, b)
+            want = oracle.gqa_decode(q[b].cpu().numpy().reshape(-1), kd, vd, nh, nkv, hd, ctx)
+            err = np.abs(o[b].cpu().numpy().reshape(-1) - want)
+            worst = max(worst, float(err.max()))
+            ok = ok and bool(np.all(err <= 2e-3 + 1e-3 * np.abs(want)))
+        check = {"sequences_checked": 2, "max_abs_err": worst, "within_tolerance": ok}
     per_seq = (ctx - 128) * 384 + 128 * nkv * hd * 2 * 2
     nbytes = B * per_seq
     if rank == 0:
@@ -324,7 +339,9 @@ def case_kivi(args):
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": "KIVI 2-bit (group 32, f16 scale+zero, 128-token f16 residual) decode attention, 32q/8kv, head_dim 64, ctx 32768, batch 16, 1 layer"},
             "roofline": {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"],
-                         "traffic": None, "peak_source": kind, "per_launch": f"{nbytes} algorithmic bytes (384 B per quantised token + residual rows)"}}))
+                         "traffic": 222.4e6, "traffic_source": "ncu dram read+write of decode_g32_kernel, profiles/decode_g32_kernel_c3_ctx32768.md",
+                         "peak_source": kind, "per_launch": f"{nbytes} algorithmic bytes (384 B per quantised token + residual rows)"},
+            "gpu_launches": 2 * args.steps, "clocks": clocks, "parity_check": check}))
     kv.free()
     eng.close()
     if dist is not None:
@@ -501,7 +518,10 @@ def main():
                        % (layers * layer_bytes / 1e9), "parallelism": f"{world} x independent batch-{batch} shards, no collective"},
             "hbm_gbs_total": world * achieved,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                         "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peak_kind,
+                         "frac": achieved / peaks["hbm_gbs"],
+                         "traffic": 147.4e6 if (layers, batch) == (LAYERS, BATCH) else None,
+                         "traffic_source": "ncu dram read+write per launch of decode_q8_kernel, profiles/decode_q8_kernel_c2_batch32.md",
+                         "peak_source": peak_kind,
                          "per_launch": f"{layer_bytes} algorithmic KV bytes per layer call / (step time / {layers} layers)"},
             "e2e": {"value": world * batch / (ms_e2e * 1e-3), "unit": "tok/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": int(layers * (batch * NH * HD * 4 + 2 * batch * KV_DIM * 4)),
