@@ -43,6 +43,7 @@ struct Q8Params {
     size_t scale_seq_stride;    // halves between sequences
     int layer_seq0;             // layer * batch: TMA coordinate of sequence 0
     int num_heads, nkv, G, max_seq, n_split, slot_begin, slot_end, want_partial, range_max;
+    int cluster;             // the n_split CTAs of a sequence form one thread-block cluster and merge through shared memory
     int whole_rows;             // 1: the maps deliver all heads of a tile in one copy; 0: one copy per head
     int* err;
 };
@@ -86,6 +87,20 @@ __device__ __forceinline__ float2 unpack_half2(uint32_t u) {
 // Both are no-ops for an ordinary launch.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// Thread-block cluster: hardware barrier over all threads of all CTAs of the cluster, and loads from a
+// peer CTA's shared memory (distributed shared memory).
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_map(uint32_t smem_addr, uint32_t cta_rank) {
+    uint32_t r; asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(cta_rank)); return r;
+}
+__device__ __forceinline__ float cluster_ld(uint32_t addr) {
+    float v; asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory"); return v;
+}
 
 // Log-sum-exp merge of the split partials of this path ([row][split][HD + 2], reference max in
 // log2 units); one CTA per (sequence, head) row.  The per-split weights are computed once, in
@@ -415,10 +430,10 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
             }
         }
     }
-    pdl_trigger();          // the merge kernel may be scheduled; it waits for this grid to finish
+    pdl_trigger();          // the next kernel in the stream may be scheduled; it waits for this grid to finish
     if (failed) {
         if (lane == 0) atomicExch(p.err, FLARE_ERR_TIMEOUT);
-        return;
+        if (!p.cluster) return;     // in a cluster every CTA still has to reach the barriers
     }
 
     // ---- finish: sums over the 4 lanes that share a row, remove the 1152 bias, write --------
@@ -428,6 +443,56 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
     for (int mt = 0; mt < MT; mt++) {
         lb[mt] += __shfl_xor_sync(0xffffffffu, lb[mt], 1);
         lb[mt] += __shfl_xor_sync(0xffffffffu, lb[mt], 2);
+    }
+    if (p.cluster) {
+        // The splits of this sequence are the CTAs of one cluster: every CTA leaves its (m, l, o) records
+        // in its own shared memory, then each merges a share of the rows by reading its peers' records.
+        __syncthreads();                                    // all warps are done with the stage buffers
+        float* rec = reinterpret_cast<float*>(sbase);       // [num_heads][HD + 2]
+        if (head_ok) {
+            float* r = rec + (kvh * p.G + hq) * (HD + 2);
+#pragma unroll
+            for (int mt = 0; mt < MT; mt++) {
+                const float bias = 1152.0f * lb[mt];
+#pragma unroll
+                for (int lc = 0; lc < 2; lc++) {
+                    const int d0 = 64 * mt + 16 * (2 * lane_blk + lc) + 4 * tig;
+                    r[2 + d0] = (lane_blk ? acc[mt][2 + lc][0][0] : acc[mt][lc][0][0]) - bias;
+                    r[2 + d0 + 1] = (lane_blk ? acc[mt][2 + lc][1][0] : acc[mt][lc][1][0]) - bias;
+                    r[2 + d0 + 2] = (lane_blk ? acc[mt][2 + lc][0][1] : acc[mt][lc][0][1]) - bias;
+                    r[2 + d0 + 3] = (lane_blk ? acc[mt][2 + lc][1][1] : acc[mt][lc][1][1]) - bias;
+                }
+            }
+            if (g < 4 && tig == 0) { r[0] = m_run; r[1] = failed ? 0.0f : l_run; }
+        }
+        cluster_sync_all();
+        const uint32_t rank = cluster_ctarank(), n = (uint32_t)p.n_split;
+        const uint32_t rec0 = ptx::smem_u32(rec);
+        for (int item = threadIdx.x;; item += blockDim.x) {
+            const int r = (int)rank + (item / HD) * (int)n, d = item % HD;
+            if (r >= p.num_heads) break;
+            float mv[8], lv[8], ov[8];
+#pragma unroll
+            for (uint32_t s2 = 0; s2 < 8; s2++) {
+                if (s2 < n) {
+                    const uint32_t a = cluster_map(rec0 + (uint32_t)r * (HD + 2) * 4, s2);
+                    mv[s2] = cluster_ld(a); lv[s2] = cluster_ld(a + 4); ov[s2] = cluster_ld(a + (2 + d) * 4);
+                } else { mv[s2] = 0.0f; lv[s2] = 0.0f; ov[s2] = 0.0f; }
+            }
+            float mm = -CUDART_INF_F;
+#pragma unroll
+            for (int s2 = 0; s2 < 8; s2++) if (lv[s2] > 0.0f) mm = fmaxf(mm, mv[s2]);
+            float ll = 0.0f, o = 0.0f;
+#pragma unroll
+            for (int s2 = 0; s2 < 8; s2++) {
+                const float w = lv[s2] > 0.0f ? fast_exp2(mv[s2] - mm) : 0.0f;
+                ll = fmaf(lv[s2], w, ll);
+                o = fmaf(ov[s2], w, o);
+            }
+            p.out[((size_t)b * p.num_heads + r) * HD + d] = ll > 0.0f ? o / ll : 0.0f;
+        }
+        cluster_sync_all();                                 // nobody leaves while a peer still reads its records
+        return;
     }
     if (!head_ok) return;
     const bool final_out = (p.n_split == 1) && !p.want_partial;
@@ -492,7 +557,41 @@ int flare_launch_decode_q8(flare_attn_ctx* ctx, const DecodeArgs& a) {
     if (n_split > max_split) n_split = max_split;
     if (n_split < 1) n_split = 1;
     if (n_split > 256) n_split = 256;
+    // Cluster mode: when about 8 (4, 2) splits per sequence fill the GPU anyway, the splits of a sequence
+    // become one thread-block cluster and merge through distributed shared memory: no second kernel, no
+    // round trip of the records through global memory.
+    int cluster = 0;
+    if (!a.want_partial && a.slot_end < 0 && n_split >= 2) {
+        const int c = n_split >= 8 ? 8 : (n_split >= 4 ? 4 : 2);
+        if (c * 5 >= n_split * 4) cluster = c;
+    }
+    if (cluster) {
+        // all clusters must be resident at once, or the second wave costs more than the merge kernel did
+        static int max_clusters[64][2][4] = {};            // [device][hd == 128][log2 c]: 0 = not asked yet
+        const int lg = cluster == 8 ? 3 : (cluster == 4 ? 2 : 1);
+        int& mc = max_clusters[ctx->device & 63][hd == 128][lg];
+        if (mc == 0) {
+            // the opt-in to large dynamic shared memory has to precede the occupancy query
+            const int max_smem = STAGES * (8 * 2 * T * hd + 2 * T * 8 * (hd / 32) * 2) + 1024;
+            if (hd == 64) cudaFuncSetAttribute(decode_q8_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+            else cudaFuncSetAttribute(decode_q8_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+            cudaLaunchAttribute ca[1];
+            ca[0].id = cudaLaunchAttributeClusterDimension;
+            ca[0].val.clusterDim.x = cluster; ca[0].val.clusterDim.y = 1; ca[0].val.clusterDim.z = 1;
+            cudaLaunchConfig_t qc = {};
+            qc.gridDim = dim3(cluster, 1); qc.blockDim = dim3(32 * 8); qc.dynamicSmemBytes = STAGES * (8 * 2 * T * hd + 2 * T * 8 * (hd / 32) * 2) + 1024;
+            qc.attrs = ca; qc.numAttrs = 1;
+            int n = 0;
+            cudaError_t e = hd == 64 ? cudaOccupancyMaxActiveClusters(&n, decode_q8_kernel<64>, &qc)
+                                     : cudaOccupancyMaxActiveClusters(&n, decode_q8_kernel<128>, &qc);
+            if (e != cudaSuccess) { cudaGetLastError(); n = 0; }
+            mc = n > 0 ? n : -1;
+        }
+        if (mc < a.batch) cluster = 0;
+    }
+    if (cluster) n_split = cluster;
     p.n_split = n_split;
+    p.cluster = cluster;
     // two workspaces used alternately: the merge of one call may still be reading while the next
     // call's decode kernel (started early, see below) writes
     size_t need = ((size_t)rows * n_split * (hd + 2) * sizeof(float) + 255) / 256 * 256;
@@ -512,21 +611,24 @@ int flare_launch_decode_q8(flare_attn_ctx* ctx, const DecodeArgs& a) {
     // Programmatic dependent launch: when the previous kernel on this stream is one of this path's
     // own kernels (it never writes the cache), this kernel may start early and request its first
     // K/V tiles while the predecessor drains; it waits (pdl_wait) before touching q.
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = cluster ? cluster : 1; attr[1].val.clusterDim.y = 1; attr[1].val.clusterDim.z = 1;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(n_split, a.batch);
     cfg.blockDim = dim3(32 * nkv);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = ctx->stream;
-    cfg.attrs = attr;
-    cfg.numAttrs = ctx->last_launch_overlappable ? 1 : 0;
+    // the attributes in use are a contiguous run of attr[]: [PDL][cluster]
+    cfg.attrs = ctx->last_launch_overlappable ? attr : attr + 1;
+    cfg.numAttrs = (ctx->last_launch_overlappable ? 1 : 0) + (cluster ? 1 : 0);
     if (hd == 64) FLARE_CUDA_OK(ctx, cudaLaunchKernelEx(&cfg, decode_q8_kernel<64>, *a.kmap, *a.vmap, p));
     else FLARE_CUDA_OK(ctx, cudaLaunchKernelEx(&cfg, decode_q8_kernel<128>, *a.kmap, *a.vmap, p));
     FLARE_LAUNCH_CHECK(ctx);
     ctx->last_launch_overlappable = true;
-    if (n_split > 1 || a.want_partial) {
+    if (!cluster && (n_split > 1 || a.want_partial)) {
         cudaLaunchConfig_t mcfg = {};
         mcfg.gridDim = dim3(rows);
         mcfg.blockDim = dim3(hd < 128 ? hd : 128);
