@@ -519,7 +519,7 @@ def main():
             "hbm_gbs_total": world * achieved,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": achieved / peaks["hbm_gbs"],
-                         "traffic": 147.4e6 if (layers, batch) == (LAYERS, BATCH) else None,
+                         "traffic": 148.5e6 if (layers, batch) == (LAYERS, BATCH) else None,
                          "traffic_source": "ncu dram read+write per launch of decode_q8_kernel, profiles/decode_q8_kernel_c2_batch32.md",
                          "peak_source": peak_kind,
                          "per_launch": f"{layer_bytes} algorithmic KV bytes per layer call / (step time / {layers} layers)"},
