@@ -13,6 +13,10 @@
 // Tensor memory (512 columns): S_A 0-127, S_B 128-255, O_A 256-383, O_B 384-511.  MMAs issued by
 // one thread execute in order, so S_X(j+1) = QK cannot overwrite P_X(j) before PV(X,j) has read it,
 // and when S_X(j+1) is signalled complete PV(X,j) has completed as well (O_X is stable).
+// Measured and rejected (causal S 4096, 897 TFLOP/s as is): S and P in two 64-column halves with
+// their own barriers (713: an N=64 SS-MMA re-reads Q from shared memory twice as often), P alone
+// handed over in halves (848: the extra store-wait, fence and arrive in the exponential loop cost
+// more than the earlier start of PV saves).
 #include "common.cuh"
 #include "tc5.cuh"
 #include <math_constants.h>

@@ -199,6 +199,32 @@ def test_q8_decode_llama1b_shape(eng, fb, orc, B):
     kv.free()
 
 
+@pytest.mark.parametrize("ctx,nh,nkv,hd", [(256, 8, 2, 64), (512, 32, 8, 64), (640, 16, 4, 64), (768, 8, 8, 64),
+                                          (1024, 32, 8, 64), (1280, 8, 2, 128), (1024, 12, 3, 64)])
+def test_q8_split_counts_and_ragged_lengths(eng, fb, orc, ctx, nh, nkv, hd):
+    """Contexts that give 2, 4, 5, 6, 8 and 10 slot ranges per sequence: with 2, 4 or 8 the ranges of a
+    sequence merge inside the kernel (thread-block cluster), otherwise a second kernel merges.  The
+    sequences of the batch have different lengths, one of them shorter than a tile."""
+    B = 3
+    lens = [ctx - 1, ctx // 3, 17]
+    kv = eng.kv_alloc(1, B, ctx, nkv, hd, fb.KV_Q8_0)
+    q = normal(61, (B, 1, nh, hd), 0.4)
+    ks, vs = [], []
+    for b in range(B):
+        k, v = normal(62 + b, (lens[b] + 1, nkv * hd)), normal(72 + b, (lens[b] + 1, nkv * hd))
+        ks.append(k); vs.append(v)
+        kv.append(0, b, k[:lens[b]], v[:lens[b]]); kv.advance(b, lens[b])
+        kv.write(0, b, lens[b], k[lens[b]], v[lens[b]])
+    for _ in range(2):                      # twice: the second call follows one of the path's own kernels
+        got = eng.decode(kv, 0, nh, q)
+    for b in range(B):
+        kd = orc.dequant_q8_0(orc.quantize_q8_0(ks[b]))
+        vd = orc.dequant_q8_0(orc.quantize_q8_0(vs[b]))
+        want = orc.gqa_decode(q[b].reshape(-1), kd, vd, nh, nkv, hd, lens[b] + 1)
+        assert_close(got[b], want, f"ctx {ctx} seq {b}")
+    kv.free()
+
+
 def test_q8_ring_wrap_4096_plus_256(eng, fb, orc):
     nh, nkv, hd, ms, n = 32, 8, 64, 4096, 4096 + 256
     kv = eng.kv_alloc(1, 1, ms, nkv, hd, fb.KV_Q8_0)
