@@ -58,9 +58,9 @@ int flare_launch_decode(flare_attn_ctx* ctx, const DecodeArgs& a) {
 
 // A kernel whose bounded wait gave up leaves a status in ctx->d_err; read and clear it.
 int flare_check_device_error(flare_attn_ctx* ctx) {
-    int h = 0;
-    FLARE_CUDA_OK(ctx, cudaMemcpyAsync(&h, ctx->d_err, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+    FLARE_CUDA_OK(ctx, cudaMemcpyAsync(ctx->h_err, ctx->d_err, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
     FLARE_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
+    const int h = *ctx->h_err;
     if (h != 0) {
         FLARE_CUDA_OK(ctx, cudaMemsetAsync(ctx->d_err, 0, sizeof(int), ctx->stream));
         return flare_set_error(ctx, h, "a kernel gave up waiting for its own memory copies (status %d)", h);
@@ -88,7 +88,8 @@ int flare_attn_create(int device, flare_attn_ctx** out_ctx) {
         return FLARE_ERR_CUDA;
     }
     ctx->stream = ctx->own_stream;
-    if (cudaMalloc(&ctx->d_err, sizeof(int)) != cudaSuccess || cudaMemset(ctx->d_err, 0, sizeof(int)) != cudaSuccess) {
+    if (cudaMalloc(&ctx->d_err, sizeof(int)) != cudaSuccess || cudaMemset(ctx->d_err, 0, sizeof(int)) != cudaSuccess ||
+        cudaMallocHost(&ctx->h_err, sizeof(int)) != cudaSuccess) {
         cudaStreamDestroy(ctx->own_stream);
         delete ctx;
         return FLARE_ERR_CUDA;
@@ -104,6 +105,7 @@ int flare_attn_destroy(flare_attn_ctx* ctx) {
     cudaStreamSynchronize(ctx->stream);
     if (ctx->backend_kv) flare_kv_free(ctx->backend_kv);
     cudaFree(ctx->d_err);
+    if (ctx->h_err) cudaFreeHost(ctx->h_err);
     cudaFree(ctx->d_misc2); cudaFree(ctx->d_conv);
     cudaFree(ctx->d_work); cudaFree(ctx->d_stage_in); cudaFree(ctx->d_stage_out); cudaFree(ctx->d_misc);
     if (ctx->h_pinned) cudaFreeHost(ctx->h_pinned);
@@ -560,16 +562,27 @@ static int decode_common(flare_attn_ctx* ctx, flare_kv* kv, int layer, int num_h
     const size_t rows = (size_t)kv->batch * n_q * num_heads;
     const size_t q_bytes = rows * kv->head_dim * 4;
     const size_t o_bytes = rows * (kv->head_dim + (want_partial ? 2 : 0)) * 4;
+    bool copy_out = false;
     if (on_device) { a.q = q; a.out = out; }
     else {
         FLARE_TRY(flare_ensure(ctx, &ctx->d_stage_in, &ctx->stage_in_bytes, q_bytes));
-        FLARE_TRY(flare_ensure(ctx, &ctx->d_stage_out, &ctx->stage_out_bytes, o_bytes));
         FLARE_CUDA_OK(ctx, cudaMemcpyAsync(ctx->d_stage_in, q, q_bytes, cudaMemcpyHostToDevice, ctx->stream));
-        a.q = (const float*)ctx->d_stage_in; a.out = (float*)ctx->d_stage_out;
+        a.q = (const float*)ctx->d_stage_in;
+        // A page-locked output buffer is written by the kernel itself over the bus (each element once, at the
+        // end of the kernel) instead of by a separate device-to-host copy after it.
+        cudaPointerAttributes pa;
+        if (cudaPointerGetAttributes(&pa, out) == cudaSuccess && pa.type == cudaMemoryTypeHost && pa.devicePointer) {
+            a.out = (float*)pa.devicePointer;
+        } else {
+            cudaGetLastError();
+            FLARE_TRY(flare_ensure(ctx, &ctx->d_stage_out, &ctx->stage_out_bytes, o_bytes));
+            a.out = (float*)ctx->d_stage_out;
+            copy_out = true;
+        }
     }
     FLARE_TRY(flare_launch_decode(ctx, a));
     if (!on_device) {
-        FLARE_CUDA_OK(ctx, cudaMemcpyAsync(out, a.out, o_bytes, cudaMemcpyDeviceToHost, ctx->stream));
+        if (copy_out) FLARE_CUDA_OK(ctx, cudaMemcpyAsync(out, a.out, o_bytes, cudaMemcpyDeviceToHost, ctx->stream));
         FLARE_TRY(flare_check_device_error(ctx));    // synchronises the stream
     }
     return FLARE_OK;

@@ -52,6 +52,7 @@ struct flare_attn_ctx {
     // next decode kernel may overlap its prologue with it (programmatic dependent launch)
     bool last_launch_overlappable = false;
     int* d_err = nullptr;            // device word a kernel sets when a bounded wait gives up
+    int* h_err = nullptr;            // page-locked host copy, so that reading it back costs no synchronous staging
     int sm_count = 148;
     flare_kv* backend_kv = nullptr;  // cache created by flare_backend_init_gpu_kv_cache
 };

@@ -1,8 +1,9 @@
 // Prefill attention, the fast tensor-core kernel: two 128-row query tiles per CTA that take turns
 // on the tensor core ("ping-pong"), with P kept in tensor memory.
 //
-//   warps 0-3   softmax of query tile A (thread r owns row r): S row out of tensor memory in one pass
-//               (128 registers), online softmax in log2 units with lazy rescaling, P written back as
+//   warps 0-3   softmax of query tile A (thread r owns row r): S row out of tensor memory once for the
+//               maximum (128 registers) and again, 64 columns at a time, for the exponentials, online
+//               softmax in log2 units with lazy rescaling, P written back as
 //               bf16 pairs into the first 64 columns of the same S buffer, O rescaled in place on
 //               the rare occasions the row maximum moved by more than 2^8; final O / l to global
 //   warps 4-7   the same for query tile B
@@ -27,7 +28,8 @@ namespace {
 
 constexpr int BN = 128;
 #ifndef POLY_EVERY
-#define POLY_EVERY 0      // one exponential in POLY_EVERY is evaluated on the FMA pipe (0: none; measured: none is fastest)
+#define POLY_EVERY 0      // one pair of exponentials in POLY_EVERY goes to the FMA-pipe polynomial (0: none; measured at
+                          // S 4096 causal: none 907, every 4th pair 902, every 2nd 856 TFLOP/s)
 #endif
 constexpr uint32_t kWaitLimit = 1u << 20;
 
@@ -80,6 +82,28 @@ __device__ __forceinline__ float exp2_poly(float x) {
     p = fmaf(p, f, 0.69326091f);
     p = fmaf(p, f, 0.99992830f);
     return __int_as_float(__float_as_int(p) + (__float_as_int(xr) << 23));
+}
+
+// The same for a pair, on packed f32x2 instructions: 2^x0, 2^x1 in 8 FMA-pipe instructions and 2 maxima.
+__device__ __forceinline__ void exp2_poly2(float& y0, float& y1, float x0, float x1) {
+    x0 = fmaxf(x0, -126.0f); x1 = fmaxf(x1, -126.0f);
+    float p0, p1, r0, r1;
+    asm("{\n\t.reg .b64 t, xr, fl, f, p, cm, cn, c3, c2, c1, c0, m1;\n\t"
+        "mov.b64 t, {%4, %5};\n\t"
+        "mov.b64 cm, {%6, %6};\n\tmov.b64 cn, {%7, %7};\n\tmov.b64 m1, {%8, %8};\n\t"
+        "mov.b64 c3, {%9, %9};\n\tmov.b64 c2, {%10, %10};\n\tmov.b64 c1, {%11, %11};\n\tmov.b64 c0, {%12, %12};\n\t"
+        "add.rn.f32x2 xr, t, cm;\n\t"          // integer part lands in the low mantissa bits
+        "add.rn.f32x2 fl, xr, cn;\n\t"         // round(x)
+        "fma.rn.f32x2 f, fl, m1, t;\n\t"       // f = x - round(x) in [-0.5, 0.5]
+        "fma.rn.f32x2 p, f, c3, c2;\n\t"
+        "fma.rn.f32x2 p, p, f, c1;\n\t"
+        "fma.rn.f32x2 p, p, f, c0;\n\t"
+        "mov.b64 {%0, %1}, p;\n\tmov.b64 {%2, %3}, xr;\n\t}"
+        : "=f"(p0), "=f"(p1), "=f"(r0), "=f"(r1)
+        : "f"(x0), "f"(x1), "f"(12582912.0f), "f"(-12582912.0f), "f"(-1.0f), "f"(0.055170249f), "f"(0.24260791f),
+          "f"(0.69326091f), "f"(0.99992830f));
+    y0 = __int_as_float(__float_as_int(p0) + (__float_as_int(r0) << 23));
+    y1 = __int_as_float(__float_as_int(p1) + (__float_as_int(r1) << 23));
 }
 
 // packed-pair f32 arithmetic and the 3-input maximum of sm_100: half the issue slots per element
@@ -243,31 +267,35 @@ __global__ void __launch_bounds__(320, 1) prefill_pp_kernel(const __grid_constan
             PP_WAIT(&bars->s_full[x], (uint32_t)(nd & 1));
             if (aborted) break;
             tc_fence_after();
-            uint32_t v[128];
-            tmem_ld32(tS, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
-            tmem_ld32(tS + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
-            tmem_ld32(tS + 64, *reinterpret_cast<uint32_t(*)[32]>(&v[64]));
-            tmem_ld32(tS + 96, *reinterpret_cast<uint32_t(*)[32]>(&v[96]));
-            tmem_wait_ld();
+            // Pass 1: the whole S row (128 registers) only for the row maximum; the registers are free again after it.
             const bool need_mask = (c0 + BN - 1 > r0) || (p.window > 0 && c0 < r0 + BM - p.window) || (c0 + BN > S);
-            if (need_mask) {
+            float tmax;
+            {
+                uint32_t v[128];
+                tmem_ld32(tS, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
+                tmem_ld32(tS + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
+                tmem_ld32(tS + 64, *reinterpret_cast<uint32_t(*)[32]>(&v[64]));
+                tmem_ld32(tS + 96, *reinterpret_cast<uint32_t(*)[32]>(&v[96]));
+                tmem_wait_ld();
+                if (need_mask) {
 #pragma unroll
-                for (int i = 0; i < 128; i++) {
-                    const int col = c0 + i;
-                    if (col > grow || col < row_lo || col >= S) v[i] = 0xff800000u;   // -inf
+                    for (int i = 0; i < 128; i++) {
+                        const int col = c0 + i;
+                        if (col > grow || col < row_lo || col >= S) v[i] = 0xff800000u;   // -inf
+                    }
                 }
+                // eight independent chains instead of one 128-long dependency chain
+                float mx[8];
+#pragma unroll
+                for (int c = 0; c < 8; c++) mx[c] = __uint_as_float(v[c]);
+#pragma unroll
+                for (int i = 8; i < 120; i += 16)
+#pragma unroll
+                    for (int c = 0; c < 8; c++) mx[c] = fmax3(mx[c], __uint_as_float(v[i + c]), __uint_as_float(v[i + 8 + c]));
+#pragma unroll
+                for (int c = 0; c < 8; c++) mx[c] = fmaxf(mx[c], __uint_as_float(v[120 + c]));
+                tmax = fmax3(fmax3(mx[0], mx[1], mx[2]), fmax3(mx[3], mx[4], mx[5]), fmaxf(mx[6], mx[7]));
             }
-            // eight independent chains instead of one 128-long dependency chain
-            float mx[8];
-#pragma unroll
-            for (int c = 0; c < 8; c++) mx[c] = __uint_as_float(v[c]);
-#pragma unroll
-            for (int i = 8; i < 120; i += 16)
-#pragma unroll
-                for (int c = 0; c < 8; c++) mx[c] = fmax3(mx[c], __uint_as_float(v[i + c]), __uint_as_float(v[i + 8 + c]));
-#pragma unroll
-            for (int c = 0; c < 8; c++) mx[c] = fmaxf(mx[c], __uint_as_float(v[120 + c]));
-            float tmax = fmax3(fmax3(mx[0], mx[1], mx[2]), fmax3(mx[3], mx[4], mx[5]), fmaxf(mx[6], mx[7]));
             tmax *= p.scale_log2;
             const bool bump = tmax > m_ref + 8.0f;
             float alpha = 1.0f;
@@ -287,23 +315,36 @@ __global__ void __launch_bounds__(320, 1) prefill_pp_kernel(const __grid_constan
             }
             l_sum *= alpha;
             const float neg_m = (m_ref == -CUDART_INF_F) ? 0.0f : -m_ref;
-            // p = exp2(s * scale - m) -> bf16 pairs, written over the first 64 columns of S_x.  Of every
-            // two exponentials one goes to the MUFU and one to the FMA-pipe polynomial.
+            // p = exp2(s * scale - m) -> bf16 pairs, written over the first 64 columns of S_x.
+            // Pass 2: the row again, 64 columns at a time (the second warp of the scheduler covers the load).
             float ls[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
             for (int half = 0; half < 2; half++) {
+                uint32_t u[64];
+                tmem_ld32(tS + half * 64, *reinterpret_cast<uint32_t(*)[32]>(&u[0]));
+                tmem_ld32(tS + half * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&u[32]));
+                tmem_wait_ld();
+                if (need_mask) {
+#pragma unroll
+                    for (int i = 0; i < 64; i++) {
+                        const int col = c0 + half * 64 + i;
+                        if (col > grow || col < row_lo || col >= S) u[i] = 0xff800000u;   // -inf
+                    }
+                }
 #pragma unroll
                 for (int i = 0; i < 32; i++) {
                     float x0, x1;
-                    ffma2(x0, x1, __uint_as_float(v[half * 64 + 2 * i]), __uint_as_float(v[half * 64 + 2 * i + 1]), p.scale_log2, neg_m);
-                    const float p0 = fast_exp2(x0);
-                    const float p1 = (POLY_EVERY > 0 && (i % (POLY_EVERY / 2 > 0 ? POLY_EVERY / 2 : 1)) == 0) ? exp2_poly(x1) : fast_exp2(x1);
+                    ffma2(x0, x1, __uint_as_float(u[2 * i]), __uint_as_float(u[2 * i + 1]), p.scale_log2, neg_m);
+                    float p0, p1;
+                    if (POLY_EVERY > 0 && (i % POLY_EVERY) == POLY_EVERY - 1) exp2_poly2(p0, p1, x0, x1);   // one pair in POLY_EVERY on the FMA pipe
+                    else { p0 = fast_exp2(x0); p1 = fast_exp2(x1); }
                     fadd2(ls[(2 * i) & 3], ls[(2 * i + 1) & 3], ls[(2 * i) & 3], ls[(2 * i + 1) & 3], p0, p1);
                     uint32_t w;
                     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(w) : "f"(p1), "f"(p0));
-                    v[half * 32 + i] = w;          // packed in place: slot half*32+i was consumed already
+                    u[i] = w;                      // packed in place: slot i was consumed already
                 }
-                tmem_st32(tS + half * 32, *reinterpret_cast<uint32_t(*)[32]>(&v[half * 32]));
+                // this half's P goes over columns [32 half, 32 half + 32): S columns that pass 2 has already read
+                tmem_st32(tS + half * 32, *reinterpret_cast<uint32_t(*)[32]>(&u[0]));
             }
             l_sum += (ls[0] + ls[1]) + (ls[2] + ls[3]);
             tmem_wait_st();

@@ -187,7 +187,9 @@ FLARE_API int flare_kv_export_dequant(flare_kv* kv, int layer, int seq, float* k
  *                  query i reads attend_len[b] - (n_q-1-i) slots.  NULL = ring state:
  *                  min(length + 1, max_seq_len)  (model.rs:2209; clamped once the ring is full).
  *   softcap        must be 0 (the wgpu backend asserts the same, backend.rs:4907-4910).
- * K/V are streamed once per kv head for all query heads that share it. */
+ * K/V are streamed once per kv head for all query heads that share it.  With host buffers
+ * (on_device = 0) the call returns when `out` is filled; an `out` in page-locked memory
+ * (cudaHostAlloc / cudaHostRegister) is written by the kernels directly, with no copy after them. */
 FLARE_API int flare_decode_attn(flare_attn_ctx* ctx, flare_kv* kv, int layer, int num_heads,
                                 const float* q, int n_q, const int* attend_len, float softcap,
                                 float* out, int on_device);

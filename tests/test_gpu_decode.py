@@ -225,6 +225,29 @@ def test_q8_split_counts_and_ragged_lengths(eng, fb, orc, ctx, nh, nkv, hd):
     kv.free()
 
 
+def test_host_output_in_page_locked_memory(eng, fb, orc):
+    """A page-locked output buffer is written by the kernels directly; a pageable one goes through a copy.
+    Both must hold the same result when the call returns (Q8_0 fast path and the general f32 path)."""
+    torch = pytest.importorskip("torch")
+    nh, nkv, hd, ctx, B = 32, 8, 64, 1024, 2
+    for dtype in (fb.KV_Q8_0, fb.KV_F32):
+        kv = eng.kv_alloc(1, B, ctx, nkv, hd, dtype)
+        for b in range(B):
+            kv.append(0, b, normal(81 + b, (ctx - 1, nkv * hd)), normal(91 + b, (ctx - 1, nkv * hd)))
+            kv.advance(b, ctx - 1)
+            kv.write(0, b, ctx - 1, normal(85, nkv * hd), normal(86, nkv * hd))
+        q = normal(99, (B, 1, nh, hd), 0.4)
+        pageable = eng.decode(kv, 0, nh, q)
+        q_pin = torch.from_numpy(q).pin_memory().numpy()
+        out_pin = torch.zeros(B, 1, nh, hd).pin_memory().numpy()
+        got = eng.decode(kv, 0, nh, q_pin, out=out_pin)
+        assert got is out_pin
+        assert_bits_equal(out_pin, pageable, "page-locked vs pageable output")
+        kd, vd = kv.export_dequant(0, 0)
+        assert_close(out_pin[0], orc.gqa_decode(q[0].reshape(-1), kd, vd, nh, nkv, hd, ctx), "page-locked output vs oracle")
+        kv.free()
+
+
 def test_q8_ring_wrap_4096_plus_256(eng, fb, orc):
     nh, nkv, hd, ms, n = 32, 8, 64, 4096, 4096 + 256
     kv = eng.kv_alloc(1, 1, ms, nkv, hd, fb.KV_Q8_0)
