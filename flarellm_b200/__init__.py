@@ -39,6 +39,7 @@ SYMBOLS = [
     ("flare_attn_last_error", C.c_char_p, [_vp]),
     ("flare_attn_launch_count", C.c_uint64, [_vp]),
     ("flare_attn_backend_name", C.c_char_p, []),
+    ("flare_attn_selftest_wait_timeout", _i, [_vp]),
     ("flare_kv_alloc", _i, [_vp, _i, _i, _i, _i, _i, _i, C.POINTER(_vp)]),
     ("flare_kv_free", _i, [_vp]),
     ("flare_kv_write_f32", _i, [_vp, _i, _i, _i64, _vp, _vp, _i]),
@@ -148,6 +149,11 @@ class Engine:
 
     def launch_count(self) -> int:
         return int(self.L.flare_attn_launch_count(self.h))
+
+    def selftest_wait_timeout(self) -> int:
+        """Runs the kernels' give-up path once (a bounded wait that nothing satisfies); returns the status,
+        ``ERR_TIMEOUT`` when the path works."""
+        return int(self.L.flare_attn_selftest_wait_timeout(self.h))
 
     def kv_alloc(self, num_layers, batch, max_seq_len, num_kv_heads, head_dim, dtype=KV_F32) -> "KvCache":
         return KvCache(self, num_layers, batch, max_seq_len, num_kv_heads, head_dim, dtype)

@@ -68,6 +68,16 @@ int flare_check_device_error(flare_attn_ctx* ctx) {
     return FLARE_OK;
 }
 
+// One warp waits, with the same bounded helper the attention kernels use, on a barrier that nothing completes.
+__global__ void selftest_wait_kernel(int* err, uint32_t limit) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(&bar, 1);
+        ptx::fence_barrier_init();
+        if (!ptx::mbar_wait(&bar, 0, limit)) atomicExch(err, FLARE_ERR_TIMEOUT);
+    }
+}
+
 #define CHECK_CTX(ctx) do { if (!(ctx)) return FLARE_ERR_INVALID_ARG; } while (0)
 #define BIND(ctx) FLARE_CUDA_OK(ctx, cudaSetDevice((ctx)->device))
 
@@ -130,6 +140,14 @@ int flare_attn_sync(flare_attn_ctx* ctx) {
     CHECK_CTX(ctx);
     BIND(ctx);
     FLARE_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
+    return flare_check_device_error(ctx);
+}
+
+int flare_attn_selftest_wait_timeout(flare_attn_ctx* ctx) {
+    CHECK_CTX(ctx);
+    BIND(ctx);
+    selftest_wait_kernel<<<1, 32, 0, ctx->stream>>>(ctx->d_err, 1u << 12);
+    FLARE_LAUNCH_CHECK(ctx);
     return flare_check_device_error(ctx);
 }
 

@@ -110,6 +110,13 @@ FLARE_API uint64_t flare_attn_launch_count(const flare_attn_ctx* ctx);
 /* ComputeBackend::name (flare-core/src/model.rs:615-617): "cuda". */
 FLARE_API const char* flare_attn_backend_name(void);
 
+/* No counterpart in the reference.  Every wait inside the kernels of this library (on a tile's
+ * mbarrier) is bounded: when it runs out the kernel records FLARE_ERR_TIMEOUT in the context's status
+ * word and returns, and the next host call that reads results reports it.  This call exercises that
+ * path without touching a cache: one warp waits on a barrier that nothing will ever complete, with a
+ * limit of a few milliseconds.  Expected return value: FLARE_ERR_TIMEOUT; the context stays usable. */
+FLARE_API int flare_attn_selftest_wait_timeout(flare_attn_ctx* ctx);
+
 /* ---------------------------------------------------------------- KV cache */
 
 /* Replaces KvCache::new / QuantizedKvCache::new / GpuKvCache::new

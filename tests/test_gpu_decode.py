@@ -320,6 +320,24 @@ def test_q8_head_dim_128_long_context_and_partials(eng, fb, orc):
     kv.free()
 
 
+def test_bounded_wait_gives_up_and_context_survives(fb, orc):
+    """A kernel wait that nothing satisfies runs out, the status reaches the host as ERR_TIMEOUT, and the
+    same context then computes a correct attention (nothing hung, nothing poisoned)."""
+    e = fb.Engine(0)
+    assert e.selftest_wait_timeout() == fb.ERR_TIMEOUT
+    assert e.selftest_wait_timeout() == fb.ERR_TIMEOUT      # the status word was cleared in between
+    nh, nkv, hd, ctx = 8, 2, 64, 300
+    kv = e.kv_alloc(1, 1, 512, nkv, hd, fb.KV_Q8_0)
+    k, v = normal(5, (ctx, nkv * hd)), normal(6, (ctx, nkv * hd))
+    kv.append(0, 0, k, v); kv.advance(0, ctx - 1)
+    q = normal(7, (1, 1, nh, hd), 0.4)
+    got = e.decode(kv, 0, nh, q)
+    kd, vd = kv.export_dequant(0, 0)
+    assert_close(got, orc.gqa_decode(q.reshape(-1), kd, vd, nh, nkv, hd, ctx), "after a timed-out wait")
+    kv.free()
+    e.close()
+
+
 def test_bad_arguments_are_rejected(eng, fb):
     with pytest.raises(fb.FlareError):
         eng.kv_alloc(1, 1, 64, 2, 48, fb.KV_Q8_0)        # head_dim % 32
