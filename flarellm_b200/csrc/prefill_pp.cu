@@ -40,19 +40,21 @@ struct PPParams {
     int* err;
 };
 
+constexpr int KS = 2;      // stages of the K ring (3 measured no faster: 902 vs 907 TFLOP/s)
+
 template <int HD>
 struct SmemPP {
     static constexpr int PANELS = HD / 64;
     static constexpr int Q_BYTES = BM * HD * 2;        // one query tile
     static constexpr int KV_BYTES = BN * HD * 2;
     static constexpr int Q_OFF = 0;                     // 2 query tiles
-    static constexpr int K_OFF = 2 * Q_BYTES;           // 2 stages
-    static constexpr int V_OFF = K_OFF + 2 * KV_BYTES;  // 2 stages
-    static constexpr int TOTAL = V_OFF + 2 * KV_BYTES;
+    static constexpr int K_OFF = 2 * Q_BYTES;           // KS stages: K tiles are needed one step before the V tile of the same rows
+    static constexpr int V_OFF = K_OFF + KS * KV_BYTES; // 2 stages
+    static constexpr int TOTAL = V_OFF + 2 * KV_BYTES;  // 224 KB at head_dim 128
 };
 
 struct BarsPP {
-    uint64_t q_full, k_full[2], v_full[2], k_empty[2], v_empty[2], s_full[2], p_full[2], o_final[2];
+    uint64_t q_full, k_full[KS], v_full[2], k_empty[KS], v_empty[2], s_full[2], p_full[2], o_final[2];
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -151,11 +153,11 @@ __global__ void __launch_bounds__(320, 1) prefill_pp_kernel(const __grid_constan
     if (threadIdx.x == 0) {
         ptx::mbar_init(&bars->q_full, 1);
         for (int s = 0; s < 2; s++) {
-            ptx::mbar_init(&bars->k_full[s], 1); ptx::mbar_init(&bars->v_full[s], 1);
-            ptx::mbar_init(&bars->k_empty[s], 1); ptx::mbar_init(&bars->v_empty[s], 1);
+            ptx::mbar_init(&bars->v_full[s], 1); ptx::mbar_init(&bars->v_empty[s], 1);
             ptx::mbar_init(&bars->s_full[s], 1); ptx::mbar_init(&bars->p_full[s], 128);
             ptx::mbar_init(&bars->o_final[s], 1);
         }
+        for (int s = 0; s < KS; s++) { ptx::mbar_init(&bars->k_full[s], 1); ptx::mbar_init(&bars->k_empty[s], 1); }
         bars->abort_flag = 0;
         ptx::fence_barrier_init();
         ptx::fence_proxy_async();
@@ -178,12 +180,12 @@ __global__ void __launch_bounds__(320, 1) prefill_pp_kernel(const __grid_constan
                 for (int pn = 0; pn < L::PANELS; pn++)
                     ptx::tma_load_4d(sm + L::Q_OFF + x * L::Q_BYTES + pn * (BM * 128), &qmap, &bars->q_full, pn * 64, h, rA + x * BM, b);
             for (int t = 0; t < n_tiles && !aborted; t++) {
-                const int s = t & 1, row = (j0 + t) * BN;
-                if (t >= 2) PP_WAIT(&bars->k_empty[s], (uint32_t)(((t >> 1) - 1) & 1));
+                const int s = t & 1, sk = t % KS, row = (j0 + t) * BN;
+                if (t >= KS) PP_WAIT(&bars->k_empty[sk], (uint32_t)((t / KS - 1) & 1));
                 if (aborted) break;
-                ptx::mbar_expect_tx(&bars->k_full[s], L::KV_BYTES);
+                ptx::mbar_expect_tx(&bars->k_full[sk], L::KV_BYTES);
                 for (int pn = 0; pn < L::PANELS; pn++)
-                    ptx::tma_load_4d(sm + L::K_OFF + s * L::KV_BYTES + pn * (BN * 128), &kmap, &bars->k_full[s], pn * 64, kvh, row, b);
+                    ptx::tma_load_4d(sm + L::K_OFF + sk * L::KV_BYTES + pn * (BN * 128), &kmap, &bars->k_full[sk], pn * 64, kvh, row, b);
                 if (t >= 2) PP_WAIT(&bars->v_empty[s], (uint32_t)(((t >> 1) - 1) & 1));
                 if (aborted) break;
                 ptx::mbar_expect_tx(&bars->v_full[s], L::KV_BYTES);
@@ -199,7 +201,7 @@ __global__ void __launch_bounds__(320, 1) prefill_pp_kernel(const __grid_constan
             int n_done[2] = {0, 0};            // tiles issued so far per query tile (for barrier parities)
             auto in_range = [&](int x, int j) { return x == 0 ? (j >= jA0 && j < jA1) : (j >= jB0 && j < jB1); };
             auto qk = [&](int x, int t) {      // S_x = Q_x K_t^T
-                const int s = t & 1;
+                const int s = t % KS;
                 const uint32_t q_addr = ptx::smem_u32(sm + L::Q_OFF + x * L::Q_BYTES);
                 const uint32_t k_addr = ptx::smem_u32(sm + L::K_OFF + s * L::KV_BYTES);
 #pragma unroll
@@ -224,7 +226,7 @@ __global__ void __launch_bounds__(320, 1) prefill_pp_kernel(const __grid_constan
             for (int t = 0; t <= n_tiles && !aborted; t++) {
                 const int j = j0 + t;
                 if (t < n_tiles) {
-                    PP_WAIT(&bars->k_full[t & 1], (uint32_t)((t >> 1) & 1));
+                    PP_WAIT(&bars->k_full[t % KS], (uint32_t)((t / KS) & 1));
                     if (aborted) break;
                     tc_fence_after();
                 }
@@ -247,7 +249,7 @@ __global__ void __launch_bounds__(320, 1) prefill_pp_kernel(const __grid_constan
                     }
                     if (t < n_tiles && in_range(x, j)) { qk(x, t); n_done[x]++; }
                 }
-                if (t < n_tiles) tc_commit(&bars->k_empty[t & 1]);
+                if (t < n_tiles) tc_commit(&bars->k_empty[t % KS]);
             }
         }
     } else {

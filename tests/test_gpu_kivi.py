@@ -171,7 +171,7 @@ def test_g32_decode_step(eng, fb, orc):
     kv.free()
 
 
-@pytest.mark.parametrize("nh,nkv,layers,B,n0", [(32, 8, 2, 2, 1500), (8, 4, 1, 3, 1100), (8, 8, 1, 1, 2000), (4, 2, 3, 2, 1333)])
+@pytest.mark.parametrize("nh,nkv,layers,B,n0", [(32, 8, 2, 2, 1500), (8, 4, 1, 3, 1100), (8, 8, 1, 1, 2000), (4, 2, 3, 2, 1333), (4, 1, 1, 2, 1200)])
 def test_g32_long_context_decode_takes_the_tensor_core_path(eng, fb, orc, nh, nkv, layers, B, n0):
     """From 1024 attended tokens on, equal-length batches at head_dim 64 run the code-tile kernel for the
     quantised prefix plus the general kernel for the newest tokens; results must still match the CPU."""
