@@ -197,32 +197,52 @@ __global__ void __launch_bounds__(128) decode_splitkv_kernel(DecodeParams p) {
         for (int i = 0; i < 8; i++) { q[g][i] = qp[i] * scale_log2; o[g][i] = 0.0f; }
     }
 
-    // the loop bound is the same for every lane of a warp, so the shuffles stay convergent;
-    // a lane group whose slot falls past the end computes on zeros and skips the update.
-    for (int tb = s0 + warp * SPW; tb < s1; tb += 4 * SPW) {
-        const int t = tb + sub;
-        const bool valid = t < s1;
-        float k[8], v[8];
-        if (valid) {
-            Row<DT, false>::load8(s, t, c0, k);
-            Row<DT, true>::load8(s, t, c0, v);
-        } else {
+    // U slots per lane group and iteration: their loads are issued together, and the online softmax is
+    // updated once per block of U (one running-maximum step, U + 1 exponentials) instead of per slot.
+    // The loop bound is the same for every lane of a warp, so the shuffles stay convergent; a lane group
+    // whose slot falls past the end computes on zeros and gets weight 0.
+    constexpr int U = 4;
+    for (int tb = s0 + warp * SPW; tb < s1; tb += 4 * SPW * U) {
+        float k[U][8], v[U][8];
+        bool valid[U];
 #pragma unroll
-            for (int i = 0; i < 8; i++) { k[i] = 0.0f; v[i] = 0.0f; }
+        for (int u = 0; u < U; u++) {
+            const int t = tb + u * 4 * SPW + sub;
+            valid[u] = t < s1;
+            if (valid[u]) {
+                Row<DT, false>::load8(s, t, c0, k[u]);
+                Row<DT, true>::load8(s, t, c0, v[u]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; i++) { k[u][i] = 0.0f; v[u][i] = 0.0f; }
+            }
         }
 #pragma unroll
         for (int g = 0; g < GC; g++) {
-            float d = 0.0f;
+            float d[U], mn = m[g];
 #pragma unroll
-            for (int i = 0; i < 8; i++) d = fmaf(q[g][i], k[i], d);
+            for (int u = 0; u < U; u++) {
+                float acc = 0.0f;
 #pragma unroll
-            for (int off = 1; off < TPS; off <<= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
-            if (valid) {
-                float mn = fmaxf(m[g], d);
-                float a = fast_exp2(m[g] - mn), w = fast_exp2(d - mn);
-                l[g] = l[g] * a + w;
+                for (int i = 0; i < 8; i++) acc = fmaf(q[g][i], k[u][i], acc);
 #pragma unroll
-                for (int i = 0; i < 8; i++) o[g][i] = o[g][i] * a + w * v[i];
+                for (int off = 1; off < TPS; off <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+                d[u] = valid[u] ? acc : -CUDART_INF_F;
+                mn = fmaxf(mn, d[u]);
+            }
+            if (mn != -CUDART_INF_F) {
+                const float a = fast_exp2(m[g] - mn);          // 0 while m is still -inf
+                float w[U], ws = 0.0f;
+#pragma unroll
+                for (int u = 0; u < U; u++) { w[u] = fast_exp2(d[u] - mn); ws += w[u]; }
+                l[g] = l[g] * a + ws;
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    float acc = o[g][i] * a;
+#pragma unroll
+                    for (int u = 0; u < U; u++) acc = fmaf(w[u], v[u][i], acc);
+                    o[g][i] = acc;
+                }
                 m[g] = mn;
             }
         }

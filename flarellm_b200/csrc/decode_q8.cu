@@ -43,6 +43,7 @@ struct Q8Params {
     size_t scale_seq_stride;    // halves between sequences
     int layer_seq0;             // layer * batch: TMA coordinate of sequence 0
     int num_heads, nkv, G, max_seq, n_split, slot_begin, slot_end, want_partial, range_max;
+    int n_q, causal_q, hgroups;   // grid.z = n_q * hgroups: one query and one group of up to 4 of its heads per kv head
     int cluster;             // the n_split CTAs of a sequence form one thread-block cluster and merge through shared memory
     int whole_rows;             // 1: the maps deliver all heads of a tile in one copy; 0: one copy per head
     int* err;
@@ -173,8 +174,11 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
     unsigned char* sbase = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     (void)SCALE_ROW;
 
-    // slot range of this (sequence, split), in whole tiles
-    int lo = 0, hi = p.attend_len[b];
+    // blockIdx.z: which query of the sequence (speculative verify: query i sees n_q-1-i slots fewer) and which
+    // group of up to 4 query heads per KV head; each such chunk streams the cache on its own
+    const int qi = blockIdx.z / p.hgroups, hg = blockIdx.z % p.hgroups;
+    // slot range of this (sequence, query, split), in whole tiles
+    int lo = 0, hi = max(0, p.attend_len[b] - (p.causal_q ? (p.n_q - 1 - qi) : 0));
     if (p.slot_end >= 0) { lo = max(lo, p.slot_begin); hi = min(hi, p.slot_end); }
     int t_first = lo / T, t_last = hi > lo ? (hi + T - 1) / T : t_first;
     const int n_tiles_seq = t_last - t_first;
@@ -233,8 +237,8 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
 
     // ---- q as two int8 limbs per head, laid out as the A operand of m16n8k32 --------------
     const int hq = g & 3;                          // query head of this lane within the group
-    const bool head_ok = hq < p.G;
-    const size_t row = (size_t)b * p.num_heads + kvh * p.G + (head_ok ? hq : 0);
+    const bool head_ok = hq < min(4, p.G - 4 * hg);
+    const size_t row = ((size_t)b * p.n_q + qi) * p.num_heads + kvh * p.G + 4 * hg + (head_ok ? hq : 0);
     uint32_t qa[NB][4];
     float qs;                                       // score = qs * sum_blk ks * (int dot)
     {
@@ -527,13 +531,14 @@ bool flare_decode_q8_supported(const DecodeArgs& a) {
     const int hd = a.kv.head_dim, nkv = a.kv.num_kv_heads;
     // every stage must start on a 1024-byte boundary (swizzle) and the scale tile on 16 bytes
     const size_t stage = (size_t)nkv * 2 * T * hd + 2 * (size_t)T * nkv * (hd / 32) * 2;
-    return a.kv.dtype == FLARE_KV_Q8_0 && (hd == 64 || hd == 128) && a.n_q == 1 && nkv <= 8 &&
-           a.num_heads / nkv <= 4 && a.kmap != nullptr && stage % 1024 == 0;
+    const int chunks = a.n_q * ((a.num_heads / nkv + 3) / 4);
+    return a.kv.dtype == FLARE_KV_Q8_0 && (hd == 64 || hd == 128) && nkv <= 8 && chunks <= 64 && a.window == 0 &&
+           a.kmap != nullptr && stage % 1024 == 0;
 }
 
 int flare_launch_decode_q8(flare_attn_ctx* ctx, const DecodeArgs& a) {
     const int hd = a.kv.head_dim, nkv = a.kv.num_kv_heads;
-    const int rows = a.batch * a.num_heads;
+    const int rows = a.batch * a.n_q * a.num_heads;
     if (rows == 0) return FLARE_OK;
     Q8Params p;
     p.q = a.q; p.out = a.out; p.attend_len = a.attend_len;
@@ -542,6 +547,8 @@ int flare_launch_decode_q8(flare_attn_ctx* ctx, const DecodeArgs& a) {
     p.scale_seq_stride = a.kv.stride[FLARE_PLANE_K_SCALE] / 2;
     p.layer_seq0 = a.layer * a.batch;
     p.num_heads = a.num_heads; p.nkv = nkv; p.G = a.num_heads / nkv; p.max_seq = a.kv.max_seq_len;
+    p.n_q = a.n_q; p.causal_q = a.causal_q; p.hgroups = (p.G + 3) / 4;
+    const int chunks = p.n_q * p.hgroups;
     p.slot_begin = a.slot_begin; p.slot_end = a.slot_end; p.want_partial = a.want_partial;
     p.range_max = a.slot_end >= 0 ? (a.slot_end - a.slot_begin) : a.max_attend;
     if (p.range_max < 0) p.range_max = 0;
@@ -552,7 +559,7 @@ int flare_launch_decode_q8(flare_attn_ctx* ctx, const DecodeArgs& a) {
     const size_t smem = STAGES * stage + 1024;
     const int ctas_per_sm = smem <= 110 * 1024 ? 2 : 1;
     // one wave: as many splits as fit without a second, partly filled wave
-    int n_split = (ctx->sm_count * ctas_per_sm) / a.batch;
+    int n_split = (ctx->sm_count * ctas_per_sm) / (a.batch * chunks);
     const int max_split = (p.range_max + 4 * T - 1) / (4 * T);    // at least 4 tiles per CTA
     if (n_split > max_split) n_split = max_split;
     if (n_split < 1) n_split = 1;
@@ -561,7 +568,7 @@ int flare_launch_decode_q8(flare_attn_ctx* ctx, const DecodeArgs& a) {
     // become one thread-block cluster and merge through distributed shared memory: no second kernel, no
     // round trip of the records through global memory.
     int cluster = 0;
-    if (!a.want_partial && a.slot_end < 0 && n_split >= 2) {
+    if (!a.want_partial && a.slot_end < 0 && n_split >= 2 && chunks == 1) {
         const int c = n_split >= 8 ? 8 : (n_split >= 4 ? 4 : 2);
         if (c * 5 >= n_split * 4) cluster = c;
     }
@@ -617,7 +624,7 @@ int flare_launch_decode_q8(flare_attn_ctx* ctx, const DecodeArgs& a) {
     attr[1].id = cudaLaunchAttributeClusterDimension;
     attr[1].val.clusterDim.x = cluster ? cluster : 1; attr[1].val.clusterDim.y = 1; attr[1].val.clusterDim.z = 1;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(n_split, a.batch);
+    cfg.gridDim = dim3(n_split, a.batch, chunks);
     cfg.blockDim = dim3(32 * nkv);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = ctx->stream;

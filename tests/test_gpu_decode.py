@@ -200,11 +200,13 @@ def test_q8_decode_llama1b_shape(eng, fb, orc, B):
 
 
 @pytest.mark.parametrize("ctx,nh,nkv,hd", [(256, 8, 2, 64), (512, 32, 8, 64), (640, 16, 4, 64), (768, 8, 8, 64),
-                                          (1024, 32, 8, 64), (1280, 8, 2, 128), (1024, 12, 3, 64)])
+                                          (1024, 32, 8, 64), (1280, 8, 2, 128), (1024, 12, 3, 64),
+                                          (1024, 64, 8, 64), (512, 12, 2, 64), (700, 16, 2, 128)])
 def test_q8_split_counts_and_ragged_lengths(eng, fb, orc, ctx, nh, nkv, hd):
     """Contexts that give 2, 4, 5, 6, 8 and 10 slot ranges per sequence: with 2, 4 or 8 the ranges of a
     sequence merge inside the kernel (thread-block cluster), otherwise a second kernel merges.  The
-    sequences of the batch have different lengths, one of them shorter than a tile."""
+    sequences of the batch have different lengths, one of them shorter than a tile.  The last three shapes
+    have 8 and 6 query heads per KV head: two groups of up to 4 heads stream the cache separately."""
     B = 3
     lens = [ctx - 1, ctx // 3, 17]
     kv = eng.kv_alloc(1, B, ctx, nkv, hd, fb.KV_Q8_0)
