@@ -139,11 +139,21 @@ __global__ void merge_q8_kernel(const float* __restrict__ work, int n_split, int
     __syncthreads();
     ll = 0.0f;
     for (int w = 0; w < (nthr + 31) / 32; w++) ll += s_red[w];
-    for (int d = tid; d < hd; d += nthr) {
-        float acc = 0.0f;
-        for (int r = 0; r < n_split; r++) acc = fmaf(base[r * (hd + 2) + 2 + d], s_w[r], acc);
-        if (want_partial) out[(size_t)row * (hd + 2) + 2 + d] = acc;
-        else out[(size_t)row * hd + d] = ll > 0.0f ? acc / ll : 0.0f;
+    // the threads form nthr / hd groups; group k sums the records k, k + groups, ... of channel d, then the
+    // groups are added up through shared memory (a long-context call has hundreds of records per row)
+    __shared__ float s_part[256];
+    const int groups = nthr / hd, grp = tid / hd, d = tid % hd;
+    float acc = 0.0f;
+    if (grp < groups) {
+#pragma unroll 4
+        for (int r = grp; r < n_split; r += groups) acc = fmaf(base[r * (hd + 2) + 2 + d], s_w[r], acc);
+    }
+    s_part[tid] = acc;
+    __syncthreads();
+    if (tid < hd) {
+        for (int k = 1; k < groups; k++) acc += s_part[k * hd + tid];
+        if (want_partial) out[(size_t)row * (hd + 2) + 2 + tid] = acc;
+        else out[(size_t)row * hd + tid] = ll > 0.0f ? acc / ll : 0.0f;
     }
     if (want_partial && tid == 0) {
         out[(size_t)row * (hd + 2)] = mm * 0.6931471805599453f;
@@ -638,7 +648,7 @@ int flare_launch_decode_q8(flare_attn_ctx* ctx, const DecodeArgs& a) {
     if (!cluster && (n_split > 1 || a.want_partial)) {
         cudaLaunchConfig_t mcfg = {};
         mcfg.gridDim = dim3(rows);
-        mcfg.blockDim = dim3(hd < 128 ? hd : 128);
+        mcfg.blockDim = dim3(256);       // a multiple of head_dim: 4 (head_dim 64) or 2 (128) groups of threads per row
         mcfg.stream = ctx->stream;
         mcfg.attrs = attr;
         mcfg.numAttrs = 1;
