@@ -577,6 +577,7 @@ static int decode_common(flare_attn_ctx* ctx, flare_kv* kv, int layer, int num_h
     a.batch = kv->batch; a.n_q = n_q; a.num_heads = num_heads;
     a.slot_begin = slot_begin; a.slot_end = slot_end; a.want_partial = want_partial; a.causal_q = causal_q;
     FLARE_TRY(upload_small(ctx, kv, n_q, attend_len, &a.attend_len, &a.ring, &a.max_attend));
+    a.h_attend = ctx->small_last.size() == (size_t)kv->batch * 3 ? ctx->small_last.data() + 2 * (size_t)kv->batch : nullptr;
     const size_t rows = (size_t)kv->batch * n_q * num_heads;
     const size_t q_bytes = rows * kv->head_dim * 4;
     const size_t o_bytes = rows * (kv->head_dim + (want_partial ? 2 : 0)) * 4;

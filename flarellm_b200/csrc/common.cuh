@@ -130,6 +130,7 @@ struct DecodeArgs {
     const CUtensorMap *kmap, *vmap;   // Q8_0 payload maps (null when the cache has none)
     int whole_rows;                   // maps deliver [head][32 slots][head_dim] in one copy
     const flare_kv* kv_obj;           // the cache itself (tensor maps, ring state)
+    const int* h_attend;              // host copy of attend_len (valid during the call), or null
 };
 int flare_launch_decode(flare_attn_ctx* ctx, const DecodeArgs& a);
 int flare_launch_decode_generic(flare_attn_ctx* ctx, const DecodeArgs& a);

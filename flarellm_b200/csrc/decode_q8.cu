@@ -43,6 +43,8 @@ struct Q8Params {
     size_t scale_seq_stride;    // halves between sequences
     int layer_seq0;             // layer * batch: TMA coordinate of sequence 0
     int num_heads, nkv, G, max_seq, n_split, slot_begin, slot_end, want_partial, range_max;
+    int n_small;             // > 0: attend_small[] holds the lengths (no global load before the first TMA request)
+    int attend_small[64];
     int n_q, causal_q, hgroups;   // grid.z = n_q * hgroups: one query and one group of up to 4 of its heads per kv head
     int cluster;             // the n_split CTAs of a sequence form one thread-block cluster and merge through shared memory
     int whole_rows;             // 1: the maps deliver all heads of a tile in one copy; 0: one copy per head
@@ -188,7 +190,7 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
     // group of up to 4 query heads per KV head; each such chunk streams the cache on its own
     const int qi = blockIdx.z / p.hgroups, hg = blockIdx.z % p.hgroups;
     // slot range of this (sequence, query, split), in whole tiles
-    int lo = 0, hi = max(0, p.attend_len[b] - (p.causal_q ? (p.n_q - 1 - qi) : 0));
+    int lo = 0, hi = max(0, (p.n_small ? p.attend_small[b] : p.attend_len[b]) - (p.causal_q ? (p.n_q - 1 - qi) : 0));
     if (p.slot_end >= 0) { lo = max(lo, p.slot_begin); hi = min(hi, p.slot_end); }
     int t_first = lo / T, t_last = hi > lo ? (hi + T - 1) / T : t_first;
     const int n_tiles_seq = t_last - t_first;
@@ -558,6 +560,11 @@ int flare_launch_decode_q8(flare_attn_ctx* ctx, const DecodeArgs& a) {
     p.layer_seq0 = a.layer * a.batch;
     p.num_heads = a.num_heads; p.nkv = nkv; p.G = a.num_heads / nkv; p.max_seq = a.kv.max_seq_len;
     p.n_q = a.n_q; p.causal_q = a.causal_q; p.hgroups = (p.G + 3) / 4;
+    p.n_small = 0;
+    if (a.h_attend && a.batch <= 64) {
+        p.n_small = a.batch;
+        for (int b = 0; b < a.batch; b++) p.attend_small[b] = a.h_attend[b];
+    }
     const int chunks = p.n_q * p.hgroups;
     p.slot_begin = a.slot_begin; p.slot_end = a.slot_end; p.want_partial = a.want_partial;
     p.range_max = a.slot_end >= 0 ? (a.slot_end - a.slot_begin) : a.max_attend;

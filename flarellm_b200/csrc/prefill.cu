@@ -54,7 +54,7 @@ static int prefill_generic(flare_attn_ctx* ctx, const PrefillArgs& a, const floa
     d.attend_len = (const int*)ctx->d_misc2 + 2 * (size_t)a.batch;
     d.q = q; d.out = out; d.batch = a.batch; d.n_q = a.seq_len; d.num_heads = a.num_heads;
     d.slot_begin = 0; d.slot_end = -1; d.want_partial = 0; d.causal_q = 1; d.max_attend = a.seq_len;
-    d.layer = 0; d.kmap = d.vmap = nullptr; d.whole_rows = 0; d.window = a.window; d.kv_obj = nullptr;
+    d.layer = 0; d.kmap = d.vmap = nullptr; d.whole_rows = 0; d.window = a.window; d.kv_obj = nullptr; d.h_attend = nullptr;
     return flare_launch_decode_generic(ctx, d);
 }
 
