@@ -19,13 +19,25 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 # FLARE_ATTN_LIB selects another build of the same library (e.g. a variant under test)
 LIB_PATH = os.environ.get("FLARE_ATTN_LIB") or os.path.join(_HERE, "libflare_attn.so")
 
-OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_OOM, ERR_CUDA, ERR_TIMEOUT, ERR_STATE = range(7)
+(OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_OOM, ERR_CUDA, ERR_TIMEOUT, ERR_STATE, ERR_NCCL,
+ ERR_BOUNDS) = range(9)
 KV_F32, KV_Q8_0, KV_KIVI_REF, KV_KIVI_G32 = range(4)
 DT_F32, DT_BF16 = 0, 1
 (PLANE_K, PLANE_V, PLANE_K_Q, PLANE_V_Q, PLANE_K_SCALE, PLANE_V_SCALE, PLANE_K_MIN, PLANE_V_MIN,
  PLANE_K_RES, PLANE_V_RES) = range(10)
 
-_STATUS_NAMES = {0: "OK", 1: "INVALID_ARG", 2: "UNSUPPORTED", 3: "OOM", 4: "CUDA", 5: "TIMEOUT", 6: "STATE"}
+_STATUS_NAMES = {0: "OK", 1: "INVALID_ARG", 2: "UNSUPPORTED", 3: "OOM", 4: "CUDA", 5: "TIMEOUT", 6: "STATE", 7: "NCCL",
+                 8: "BOUNDS"}
+OP_NONE, OP_DECODE, OP_PREFILL = range(3)
+
+
+class Stats(C.Structure):
+    """flare_attn_stats of include/flare_attn.h."""
+    _fields_ = [("calls", C.c_uint64), ("last_op", C.c_int32), ("reserved", C.c_int32),
+                ("last_elapsed_us", C.c_double), ("last_bytes", C.c_double), ("last_flops", C.c_double),
+                ("last_gbs", C.c_double), ("last_tflops", C.c_double), ("last_frac_of_peak", C.c_double),
+                ("total_elapsed_us", C.c_double), ("total_bytes", C.c_double), ("total_flops", C.c_double)]
+
 
 # every symbol include/flare_attn.h declares: (name, restype, argtypes)
 _vp, _i, _i64, _f, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_size_t
@@ -40,6 +52,9 @@ SYMBOLS = [
     ("flare_attn_launch_count", C.c_uint64, [_vp]),
     ("flare_attn_backend_name", C.c_char_p, []),
     ("flare_attn_selftest_wait_timeout", _i, [_vp]),
+    ("flare_attn_enable_stats", _i, [_vp, _i]),
+    ("flare_attn_set_peaks", _i, [_vp, C.c_double, C.c_double]),
+    ("flare_attn_get_stats", _i, [_vp, C.POINTER(Stats)]),
     ("flare_kv_alloc", _i, [_vp, _i, _i, _i, _i, _i, _i, C.POINTER(_vp)]),
     ("flare_kv_free", _i, [_vp]),
     ("flare_kv_write_f32", _i, [_vp, _i, _i, _i64, _vp, _vp, _i]),
@@ -57,10 +72,19 @@ SYMBOLS = [
     ("flare_kv_export_q8_0_blocks", _i, [_vp, _i, _i, _i, _i, _vp, _vp, _i]),
     ("flare_kv_export_dequant", _i, [_vp, _i, _i, _vp, _vp, _i]),
     ("flare_decode_attn", _i, [_vp, _vp, _i, _i, _vp, _i, _ip, _f, _vp, _i]),
+    ("flare_decode_step", _i, [_vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _i]),
     ("flare_decode_attn_noalloc", _i, [_vp, _vp, _i, _i, _vp, _i, _ip, _vp]),
     ("flare_decode_attn_noalloc_scratch_bytes", _sz, []),
     ("flare_decode_attn_partial", _i, [_vp, _vp, _i, _i, _vp, _i, _i, _i, _vp, _i]),
     ("flare_merge_partials", _i, [_vp, _vp, _i, _i, _i, _vp, _i]),
+    ("flare_attn_comm_unique_id", _i, [_vp]),
+    ("flare_attn_comm_init", _i, [_vp, _vp, _i, _i]),
+    ("flare_attn_comm_enable_direct", _i, [_vp, _i, _i]),
+    ("flare_attn_comm_set_wait_ms", _i, [_vp, C.c_uint]),
+    ("flare_attn_comm_info", _i, [_vp, _ip, _ip, _ip]),
+    ("flare_attn_comm_destroy", _i, [_vp]),
+    ("flare_decode_attn_splitkv_multi", _i, [_vp, _vp, _i, _i, _vp, _i, _vp, _i]),
+    ("flare_attn_comm_selftest_missing_peer", _i, [_vp]),
     ("flare_gqa_attention_host", _i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _vp]),
     ("flare_prefill_attn", _i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _i, _i]),
     ("flare_backend_init_gpu_kv_cache", _i, [_vp, _i, _i, _i, _i]),
@@ -155,6 +179,18 @@ class Engine:
         ``ERR_TIMEOUT`` when the path works."""
         return int(self.L.flare_attn_selftest_wait_timeout(self.h))
 
+    def enable_stats(self, on=True):
+        self.check(self.L.flare_attn_enable_stats(self.h, int(bool(on))))
+
+    def set_peaks(self, hbm_gbs, tensor_tflops):
+        self.check(self.L.flare_attn_set_peaks(self.h, float(hbm_gbs), float(tensor_tflops)))
+
+    def stats(self) -> Stats:
+        """Measurements of the attention calls made while stats were enabled (waits for the last one)."""
+        st = Stats()
+        self.check(self.L.flare_attn_get_stats(self.h, C.byref(st)))
+        return st
+
     def kv_alloc(self, num_layers, batch, max_seq_len, num_kv_heads, head_dim, dtype=KV_F32) -> "KvCache":
         return KvCache(self, num_layers, batch, max_seq_len, num_kv_heads, head_dim, dtype)
 
@@ -174,6 +210,19 @@ class Engine:
             assert al_arr.size == kv.batch
             al = al_arr.ctypes.data_as(_ip)
         self.check(self.L.flare_decode_attn(self.h, kv.h, layer, num_heads, _ptr(q), n_q, al, softcap, _ptr(out),
+                                            int(on_device)))
+        return out
+
+    def decode_step(self, kv: "KvCache", layer, num_heads, key, value, q, out=None):
+        """flare_decode_step: store the new K/V row of every sequence, then attend.  Host ndarrays
+        (``out`` optional) or device pointers (``out`` required)."""
+        on_device = not isinstance(q, np.ndarray)
+        if not on_device:
+            key, value, q = (a if (a.dtype == np.float32 and a.flags["C_CONTIGUOUS"]) else
+                             np.ascontiguousarray(a, dtype=np.float32) for a in (key, value, q))
+            if out is None:
+                out = np.empty((kv.batch, 1, num_heads, kv.head_dim), dtype=np.float32)
+        self.check(self.L.flare_decode_step(self.h, kv.h, layer, num_heads, _ptr(key), _ptr(value), _ptr(q), _ptr(out),
                                             int(on_device)))
         return out
 
@@ -206,6 +255,42 @@ class Engine:
                 out = np.empty((rows, head_dim), dtype=np.float32)
         self.check(self.L.flare_merge_partials(self.h, _ptr(partials), n_parts, rows, head_dim, _ptr(out),
                                                int(on_device)))
+        return out
+
+    # ---- one sequence over several GPUs ------------------------------------------------------
+    @staticmethod
+    def comm_unique_id() -> bytes:
+        """128 bytes that rank 0 hands to the other ranks (flare_attn_comm_unique_id)."""
+        buf = C.create_string_buffer(128)
+        st = lib().flare_attn_comm_unique_id(buf)
+        if st != OK:
+            raise FlareError(st, "flare_attn_comm_unique_id failed (is libnccl.so.2 loadable?)")
+        return buf.raw
+
+    def comm_init(self, uid, rank: int, world: int):
+        self.check(self.L.flare_attn_comm_init(self.h, C.c_char_p(uid) if uid else None, rank, world))
+
+    def comm_enable_direct(self, max_rows: int, head_dim: int):
+        self.check(self.L.flare_attn_comm_enable_direct(self.h, max_rows, head_dim))
+
+    def comm_set_wait_ms(self, ms: int):
+        self.check(self.L.flare_attn_comm_set_wait_ms(self.h, ms))
+
+    def comm_destroy(self):
+        self.check(self.L.flare_attn_comm_destroy(self.h))
+
+    def comm_selftest_missing_peer(self) -> int:
+        return int(self.L.flare_attn_comm_selftest_missing_peer(self.h))
+
+    def decode_splitkv_multi(self, kv: "KvCache", layer, num_heads, q, n_local_slots, out=None):
+        """flare_decode_attn_splitkv_multi: this rank's slots 0..n_local_slots-1, merged with every other rank's."""
+        on_device = not isinstance(q, np.ndarray)
+        if not on_device:
+            q = np.ascontiguousarray(q, dtype=np.float32)
+            if out is None:
+                out = np.empty((kv.batch, 1, num_heads, kv.head_dim), dtype=np.float32)
+        self.check(self.L.flare_decode_attn_splitkv_multi(self.h, kv.h, layer, num_heads, _ptr(q), n_local_slots,
+                                                          _ptr(out), int(on_device)))
         return out
 
     def gqa_attention_host(self, q, k_cache, v_cache, num_heads, num_kv_heads, head_dim, seq_len, softcap=0.0):

@@ -78,6 +78,53 @@ __global__ void selftest_wait_kernel(int* err, uint32_t limit) {
     }
 }
 
+// ---- per-call measurements -------------------------------------------------------------------
+static int stats_fold(flare_attn_ctx* ctx) {       // bring the last measured call into the totals
+    if (!ctx->stats_pending) return FLARE_OK;
+    FLARE_CUDA_OK(ctx, cudaEventSynchronize(ctx->stats_ev[1]));
+    float ms = 0.0f;
+    FLARE_CUDA_OK(ctx, cudaEventElapsedTime(&ms, ctx->stats_ev[0], ctx->stats_ev[1]));
+    flare_attn_stats& st = ctx->stats;
+    const double us = (double)ms * 1e3, sec = (double)ms * 1e-3;
+    st.calls++;
+    st.last_op = ctx->stats_op;
+    st.last_elapsed_us = us; st.last_bytes = ctx->stats_bytes; st.last_flops = ctx->stats_flops;
+    st.last_gbs = sec > 0.0 ? ctx->stats_bytes / sec / 1e9 : 0.0;
+    st.last_tflops = sec > 0.0 ? ctx->stats_flops / sec / 1e12 : 0.0;
+    st.last_frac_of_peak = ctx->stats_op == FLARE_OP_PREFILL ? st.last_tflops / ctx->peak_tflops : st.last_gbs / ctx->peak_hbm_gbs;
+    st.total_elapsed_us += us; st.total_bytes += ctx->stats_bytes; st.total_flops += ctx->stats_flops;
+    ctx->stats_pending = false;
+    return FLARE_OK;
+}
+static int stats_begin(flare_attn_ctx* ctx) {
+    if (!ctx->stats_on) return FLARE_OK;
+    FLARE_TRY(stats_fold(ctx));
+    ctx->last_launch_overlappable = false;      // a measured call does not start inside its predecessor
+    FLARE_CUDA_OK(ctx, cudaEventRecord(ctx->stats_ev[0], ctx->stream));
+    return FLARE_OK;
+}
+static int stats_end(flare_attn_ctx* ctx, int op, double bytes, double flops) {
+    if (!ctx->stats_on) return FLARE_OK;
+    FLARE_CUDA_OK(ctx, cudaEventRecord(ctx->stats_ev[1], ctx->stream));
+    ctx->stats_op = op; ctx->stats_bytes = bytes; ctx->stats_flops = flops;
+    ctx->stats_pending = true;
+    ctx->last_launch_overlappable = false;      // nor does its successor start inside it
+    return FLARE_OK;
+}
+// K/V bytes that `slots` attended slots of one sequence occupy in the cache's storage format.
+static double kv_bytes_of(const flare_kv* kv, double slots) {
+    const double kvd = kv->kv_dim;
+    switch (kv->dtype) {
+        case FLARE_KV_F32: return slots * 2.0 * kvd * 4.0;
+        case FLARE_KV_Q8_0: return slots * 2.0 * (kvd + kvd / 16.0);
+        case FLARE_KV_KIVI_REF: return slots * (kvd / 2.0 + 8.0);
+        default: {       // group-32 KIVI: the newest 128 tokens are f16 rows, the rest 0.75 bytes per value
+            const double ring = slots < FLARE_G32_RESIDUAL ? slots : FLARE_G32_RESIDUAL;
+            return (slots - ring) * 0.75 * kvd + ring * 2.0 * kvd * 2.0;
+        }
+    }
+}
+
 #define CHECK_CTX(ctx) do { if (!(ctx)) return FLARE_ERR_INVALID_ARG; } while (0)
 #define BIND(ctx) FLARE_CUDA_OK(ctx, cudaSetDevice((ctx)->device))
 
@@ -114,6 +161,7 @@ int flare_attn_destroy(flare_attn_ctx* ctx) {
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     if (ctx->backend_kv) flare_kv_free(ctx->backend_kv);
+    flare_comm_free(ctx);
     cudaFree(ctx->d_err);
     if (ctx->h_err) cudaFreeHost(ctx->h_err);
     cudaFree(ctx->d_misc2); cudaFree(ctx->d_conv);
@@ -122,8 +170,38 @@ int flare_attn_destroy(flare_attn_ctx* ctx) {
     if (ctx->h_rows) cudaFreeHost(ctx->h_rows);
     for (int i = 0; i < FLARE_ROW_SLOTS; i++) if (ctx->rows_events[i]) cudaEventDestroy(ctx->rows_events[i]);
     for (int i = 0; i < FLARE_SMALL_SLOTS; i++) if (ctx->small_events[i]) cudaEventDestroy(ctx->small_events[i]);
+    for (int i = 0; i < 2; i++) if (ctx->stats_ev[i]) cudaEventDestroy(ctx->stats_ev[i]);
     if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
     delete ctx;
+    return FLARE_OK;
+}
+
+int flare_attn_enable_stats(flare_attn_ctx* ctx, int on) {
+    CHECK_CTX(ctx);
+    BIND(ctx);
+    if (on) {
+        for (int i = 0; i < 2; i++)
+            if (!ctx->stats_ev[i]) FLARE_CUDA_OK(ctx, cudaEventCreate(&ctx->stats_ev[i]));
+    } else {
+        FLARE_TRY(stats_fold(ctx));
+    }
+    ctx->stats_on = on != 0;
+    return FLARE_OK;
+}
+
+int flare_attn_set_peaks(flare_attn_ctx* ctx, double hbm_gbs, double tensor_tflops) {
+    CHECK_CTX(ctx);
+    if (!(hbm_gbs > 0.0) || !(tensor_tflops > 0.0)) return flare_set_error(ctx, FLARE_ERR_INVALID_ARG, "peaks must be positive");
+    ctx->peak_hbm_gbs = hbm_gbs; ctx->peak_tflops = tensor_tflops;
+    return FLARE_OK;
+}
+
+int flare_attn_get_stats(flare_attn_ctx* ctx, flare_attn_stats* out) {
+    CHECK_CTX(ctx);
+    if (!out) return flare_set_error(ctx, FLARE_ERR_INVALID_ARG, "flare_attn_get_stats: out is null");
+    BIND(ctx);
+    FLARE_TRY(stats_fold(ctx));
+    *out = ctx->stats;
     return FLARE_OK;
 }
 
@@ -552,9 +630,12 @@ static int upload_small(flare_attn_ctx* ctx, const flare_kv* kv, int n_q, const 
     return FLARE_OK;
 }
 
-static int decode_common(flare_attn_ctx* ctx, flare_kv* kv, int layer, int num_heads, const float* q, int n_q,
-                         const int* attend_len, float softcap, int slot_begin, int slot_end, int want_partial,
-                         int causal_q, float* out, int on_device) {
+// q_staged: when non-null, q is already on the device there although `out` is a host buffer (on_device = 0).
+// multi: the slot range is this rank's share of one sequence; the records of all ranks are exchanged and merged
+// (flare_multi_tail) and `out` receives the attention output over the whole sequence.
+int flare_decode_common(flare_attn_ctx* ctx, flare_kv* kv, int layer, int num_heads, const float* q, int n_q,
+                        const int* attend_len, float softcap, int slot_begin, int slot_end, int want_partial,
+                        int causal_q, float* out, int on_device, const float* q_staged, int multi) {
     CHECK_CTX(ctx);
     if (!kv || kv->ctx != ctx) return flare_set_error(ctx, FLARE_ERR_STATE, "no KV cache bound to this context");
     if (layer < 0 || layer >= kv->num_layers) return flare_set_error(ctx, FLARE_ERR_INVALID_ARG, "layer %d out of range", layer);
@@ -580,13 +661,23 @@ static int decode_common(flare_attn_ctx* ctx, flare_kv* kv, int layer, int num_h
     a.h_attend = ctx->small_last.size() == (size_t)kv->batch * 3 ? ctx->small_last.data() + 2 * (size_t)kv->batch : nullptr;
     const size_t rows = (size_t)kv->batch * n_q * num_heads;
     const size_t q_bytes = rows * kv->head_dim * 4;
-    const size_t o_bytes = rows * (kv->head_dim + (want_partial ? 2 : 0)) * 4;
+    const size_t o_bytes = rows * (kv->head_dim + ((want_partial && !multi) ? 2 : 0)) * 4;
+    const float* work = nullptr;
+    int n_split = 0;
+    if (multi) {
+        if (kv->head_dim != 64 && kv->head_dim != 128)
+            return flare_set_error(ctx, FLARE_ERR_UNSUPPORTED, "the multi-GPU split needs head_dim 64 or 128, got %d", kv->head_dim);
+        a.defer_merge = 1; a.work_out = &work; a.n_split_out = &n_split;
+    }
     bool copy_out = false;
     if (on_device) { a.q = q; a.out = out; }
     else {
-        FLARE_TRY(flare_ensure(ctx, &ctx->d_stage_in, &ctx->stage_in_bytes, q_bytes));
-        FLARE_CUDA_OK(ctx, cudaMemcpyAsync(ctx->d_stage_in, q, q_bytes, cudaMemcpyHostToDevice, ctx->stream));
-        a.q = (const float*)ctx->d_stage_in;
+        if (q_staged) a.q = q_staged;
+        else {
+            FLARE_TRY(flare_ensure(ctx, &ctx->d_stage_in, &ctx->stage_in_bytes, q_bytes));
+            FLARE_CUDA_OK(ctx, cudaMemcpyAsync(ctx->d_stage_in, q, q_bytes, cudaMemcpyHostToDevice, ctx->stream));
+            a.q = (const float*)ctx->d_stage_in;
+        }
         // A page-locked output buffer is written by the kernel itself over the bus (each element once, at the
         // end of the kernel) instead of by a separate device-to-host copy after it.
         cudaPointerAttributes pa;
@@ -599,7 +690,22 @@ static int decode_common(flare_attn_ctx* ctx, flare_kv* kv, int layer, int num_h
             copy_out = true;
         }
     }
+    FLARE_TRY(stats_begin(ctx));
     FLARE_TRY(flare_launch_decode(ctx, a));
+    if (multi) FLARE_TRY(flare_multi_tail(ctx, work, n_split, (int)rows, kv->head_dim, a.out));
+    if (ctx->stats_on) {
+        double bytes = 0.0, pairs = 0.0;
+        for (int b = 0; b < kv->batch && a.h_attend; b++) {
+            for (int i = 0; i < n_q; i++) {
+                int lo = 0, hi = a.h_attend[b] - (causal_q ? (n_q - 1 - i) : 0);
+                if (slot_end >= 0) { lo = slot_begin; if (hi > slot_end) hi = slot_end; }
+                const double n = hi > lo ? hi - lo : 0;
+                pairs += n;
+                if (i == n_q - 1) bytes += kv_bytes_of(kv, n);
+            }
+        }
+        FLARE_TRY(stats_end(ctx, FLARE_OP_DECODE, bytes, 4.0 * num_heads * kv->head_dim * pairs));
+    }
     if (!on_device) {
         if (copy_out) FLARE_CUDA_OK(ctx, cudaMemcpyAsync(out, a.out, o_bytes, cudaMemcpyDeviceToHost, ctx->stream));
         FLARE_TRY(flare_check_device_error(ctx));    // synchronises the stream
@@ -609,7 +715,66 @@ static int decode_common(flare_attn_ctx* ctx, flare_kv* kv, int layer, int num_h
 
 int flare_decode_attn(flare_attn_ctx* ctx, flare_kv* kv, int layer, int num_heads, const float* q, int n_q,
                       const int* attend_len, float softcap, float* out, int on_device) {
-    return decode_common(ctx, kv, layer, num_heads, q, n_q, attend_len, softcap, 0, -1, 0, 1, out, on_device);
+    return flare_decode_common(ctx, kv, layer, num_heads, q, n_q, attend_len, softcap, 0, -1, 0, 1, out, on_device);
+}
+
+static bool is_page_locked(const void* p) {
+    cudaPointerAttributes pa;
+    if (cudaPointerGetAttributes(&pa, p) == cudaSuccess && pa.type == cudaMemoryTypeHost) return true;
+    cudaGetLastError();
+    return false;
+}
+
+int flare_decode_step(flare_attn_ctx* ctx, flare_kv* kv, int layer, int num_heads, const float* key, const float* value,
+                      const float* q, float* out, int on_device) {
+    CHECK_CTX(ctx);
+    if (!kv || kv->ctx != ctx) return flare_set_error(ctx, FLARE_ERR_STATE, "no KV cache bound to this context");
+    if (!key || !value || !q || !out) return flare_set_error(ctx, FLARE_ERR_INVALID_ARG, "flare_decode_step: null buffer");
+    if (layer < 0 || layer >= kv->num_layers) return flare_set_error(ctx, FLARE_ERR_INVALID_ARG, "layer %d out of range", layer);
+    if (num_heads < 1 || num_heads % kv->num_kv_heads)
+        return flare_set_error(ctx, FLARE_ERR_INVALID_ARG, "num_heads %d is not a multiple of %d kv heads", num_heads, kv->num_kv_heads);
+    BIND(ctx);
+    const int* d_att; const int2* d_ring; int mx;
+    FLARE_TRY(upload_small(ctx, kv, 1, nullptr, &d_att, &d_ring, &mx));
+    if (on_device) {
+        FLARE_TRY(flare_launch_kv_write_step(kv, layer, d_ring, key, value));
+        return flare_decode_common(ctx, kv, layer, num_heads, q, 1, nullptr, 0.0f, 0, -1, 0, 1, out, 1);
+    }
+    const size_t row_fl = (size_t)kv->batch * kv->kv_dim, q_fl = (size_t)kv->batch * num_heads * kv->head_dim;
+    const size_t bytes = (2 * row_fl + q_fl) * sizeof(float);
+    FLARE_TRY(flare_ensure(ctx, &ctx->d_stage_in, &ctx->stage_in_bytes, bytes));
+    float* d = (float*)ctx->d_stage_in;
+    const size_t slot_bytes = 1u << 20;
+    if (is_page_locked(key) && is_page_locked(value) && is_page_locked(q)) {
+        // the caller's buffers can be read by the copy engine as they are
+        FLARE_CUDA_OK(ctx, cudaMemcpyAsync(d, key, row_fl * 4, cudaMemcpyHostToDevice, ctx->stream));
+        FLARE_CUDA_OK(ctx, cudaMemcpyAsync(d + row_fl, value, row_fl * 4, cudaMemcpyHostToDevice, ctx->stream));
+        FLARE_CUDA_OK(ctx, cudaMemcpyAsync(d + 2 * row_fl, q, q_fl * 4, cudaMemcpyHostToDevice, ctx->stream));
+    } else if (bytes <= slot_bytes) {
+        // pageable and small: pack the three inputs into one page-locked slot, one transfer
+        if (!ctx->h_rows) {
+            FLARE_CUDA_OK(ctx, cudaMallocHost(&ctx->h_rows, slot_bytes * FLARE_ROW_SLOTS));
+            ctx->rows_slot_bytes = slot_bytes;
+        }
+        const int slot = (int)(ctx->rows_counter++ % FLARE_ROW_SLOTS);
+        if (!ctx->rows_events[slot]) FLARE_CUDA_OK(ctx, cudaEventCreateWithFlags(&ctx->rows_events[slot], cudaEventDisableTiming));
+        else FLARE_CUDA_OK(ctx, cudaEventSynchronize(ctx->rows_events[slot]));
+        float* h = (float*)((char*)ctx->h_rows + (size_t)slot * slot_bytes);
+        memcpy(h, key, row_fl * 4);
+        memcpy(h + row_fl, value, row_fl * 4);
+        memcpy(h + 2 * row_fl, q, q_fl * 4);
+        FLARE_CUDA_OK(ctx, cudaMemcpyAsync(d, h, bytes, cudaMemcpyHostToDevice, ctx->stream));
+        FLARE_CUDA_OK(ctx, cudaEventRecord(ctx->rows_events[slot], ctx->stream));
+    } else {
+        // pageable and large: the call synchronises before it returns, so the buffers stay valid long enough
+        FLARE_CUDA_OK(ctx, cudaMemcpyAsync(d, key, row_fl * 4, cudaMemcpyHostToDevice, ctx->stream));
+        FLARE_CUDA_OK(ctx, cudaMemcpyAsync(d + row_fl, value, row_fl * 4, cudaMemcpyHostToDevice, ctx->stream));
+        FLARE_CUDA_OK(ctx, cudaMemcpyAsync(d + 2 * row_fl, q, q_fl * 4, cudaMemcpyHostToDevice, ctx->stream));
+    }
+    ctx->last_launch_overlappable = false;
+    FLARE_TRY(flare_launch_kv_write_step(kv, layer, d_ring, d, d + row_fl));
+    // attention on the staged q; the output goes to the caller's host buffer; one synchronisation at the end
+    return flare_decode_common(ctx, kv, layer, num_heads, q, 1, nullptr, 0.0f, 0, -1, 0, 1, out, 0, d + 2 * row_fl);
 }
 
 int flare_decode_attn_noalloc(flare_attn_ctx* ctx, flare_kv* kv, int layer, int num_heads, const float* q_dev, int n_q,
@@ -632,7 +797,7 @@ int flare_decode_attn_partial(flare_attn_ctx* ctx, flare_kv* kv, int layer, int 
     if (slot_end < 0) return flare_set_error(ctx, FLARE_ERR_INVALID_ARG, "slot_end must be >= 0");
     // every query reads the whole range: the range itself is the mask
     std::vector<int> att(kv->batch, slot_end > kv->max_seq_len ? kv->max_seq_len : slot_end);
-    return decode_common(ctx, kv, layer, num_heads, q, n_q, att.data(), 0.0f, slot_begin, slot_end, 1, 0, partial, on_device);
+    return flare_decode_common(ctx, kv, layer, num_heads, q, n_q, att.data(), 0.0f, slot_begin, slot_end, 1, 0, partial, on_device);
 }
 
 int flare_merge_partials(flare_attn_ctx* ctx, const float* partials, int n_parts, int rows, int head_dim, float* out,
@@ -705,7 +870,14 @@ int flare_prefill_attn(flare_attn_ctx* ctx, const void* q, const void* k, const 
         FLARE_CUDA_OK(ctx, cudaMemcpyAsync(d + qb + kb, v, kn * esz_in, cudaMemcpyHostToDevice, ctx->stream));
         a.q = d; a.k = d + qb; a.v = d + qb + kb; a.out = ctx->d_stage_out;
     }
+    FLARE_TRY(stats_begin(ctx));
     FLARE_TRY(flare_launch_prefill(ctx, a));
+    if (ctx->stats_on) {
+        double pairs = 0.0;
+        for (int t = 0; t < seq_len; t++) pairs += (window > 0 && t + 1 > window) ? window : t + 1;
+        const double io = ((double)qn * (esz_in + esz_out) + 2.0 * (double)kn * esz_in);
+        FLARE_TRY(stats_end(ctx, FLARE_OP_PREFILL, io, 4.0 * batch * num_heads * head_dim * pairs));
+    }
     if (!on_device) {
         FLARE_CUDA_OK(ctx, cudaMemcpyAsync(out, a.out, qn * esz_out, cudaMemcpyDeviceToHost, ctx->stream));
         FLARE_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));

@@ -24,6 +24,8 @@
 #define FLARE_SMALL_SLOTS 64
 #define FLARE_ROW_SLOTS 8
 
+struct FlareComm;        // collective state of a context (multi.cu)
+
 struct flare_attn_ctx {
     int device = 0;
     cudaStream_t own_stream = nullptr;
@@ -55,6 +57,14 @@ struct flare_attn_ctx {
     int* h_err = nullptr;            // page-locked host copy, so that reading it back costs no synchronous staging
     int sm_count = 148;
     flare_kv* backend_kv = nullptr;  // cache created by flare_backend_init_gpu_kv_cache
+    FlareComm* comm = nullptr;       // set by flare_attn_comm_init
+    // per-call measurements (flare_attn_enable_stats): two events around the kernels of a call
+    bool stats_on = false, stats_pending = false;
+    cudaEvent_t stats_ev[2] = {};
+    int stats_op = 0;
+    double stats_bytes = 0.0, stats_flops = 0.0;
+    double peak_hbm_gbs = 7700.0, peak_tflops = 2250.0;
+    flare_attn_stats stats = {};
 };
 
 struct flare_kv {
@@ -131,6 +141,12 @@ struct DecodeArgs {
     int whole_rows;                   // maps deliver [head][32 slots][head_dim] in one copy
     const flare_kv* kv_obj;           // the cache itself (tensor maps, ring state)
     const int* h_attend;              // host copy of attend_len (valid during the call), or null
+    // defer_merge (with want_partial): the launcher leaves the per-range records unmerged and reports where they
+    // are — [row][n_split][head_dim + 2], maximum in log2 units — so that the caller's own kernel merges them
+    // (the multi-GPU exchange does, together with the records of the other ranks)
+    int defer_merge = 0;
+    const float** work_out = nullptr;
+    int* n_split_out = nullptr;
 };
 int flare_launch_decode(flare_attn_ctx* ctx, const DecodeArgs& a);
 int flare_launch_decode_generic(flare_attn_ctx* ctx, const DecodeArgs& a);
@@ -145,9 +161,20 @@ size_t flare_noalloc_scratch_bytes();
 int flare_launch_merge(flare_attn_ctx* ctx, const float* partials, size_t part_stride_floats, int n_parts,
                        int rows, int head_dim, float* out, int want_partial);
 
+// ---- one sequence split over several GPUs (multi.cu) --------------------------------------------
+void flare_comm_free(flare_attn_ctx* ctx);
+// Called by the decode path after its kernels when the call is a multi-GPU one: exchanges this rank's records
+// with the other ranks and writes the merged attention output.
+int flare_multi_tail(flare_attn_ctx* ctx, const float* work, int n_split, int rows, int head_dim, float* out);
+extern "C" int flare_decode_common(flare_attn_ctx* ctx, flare_kv* kv, int layer, int num_heads, const float* q, int n_q,
+                        const int* attend_len, float softcap, int slot_begin, int slot_end, int want_partial,
+                        int causal_q, float* out, int on_device, const float* q_staged = nullptr, int multi = 0);
+
 struct PrefillArgs {
     const void *q, *k, *v; void* out;   // device
     int in_dtype, out_dtype, batch, seq_len, num_heads, num_kv_heads, head_dim, window;
+    int f16_ops = 0;                    // tensor-core operands are f16 (converted f32 inputs) instead of bf16
+    const float* descale = nullptr;     // device [2]: undoes the conversion's power-of-two scaling (f16_ops only)
 };
 int flare_launch_prefill(flare_attn_ctx* ctx, const PrefillArgs& a);
 int flare_launch_prefill_pp(flare_attn_ctx* ctx, const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm,

@@ -24,6 +24,7 @@
 #include "common.cuh"
 #include "tma.cuh"
 #include <math_constants.h>
+#include <mutex>
 
 namespace {
 
@@ -582,11 +583,15 @@ int flare_launch_decode_g32(flare_attn_ctx* ctx, const DecodeArgs& a, const flar
     FLARE_TRY(flare_ensure(ctx, &ctx->d_work, &ctx->work_bytes, 2 * need));
     ctx->work_phase ^= 1;
     p.work = (float*)((char*)ctx->d_work + (size_t)ctx->work_phase * need);
-    static bool attr_done[64] = {};
-    if (!attr_done[ctx->device & 63]) {
-        FLARE_CUDA_OK(ctx, cudaFuncSetAttribute(decode_g32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                (int)(STAGES * (2 * 8 * T * 16 + NG * 8 * HD * 4 + T * 8 * 2 * 4) + 128)));
-        attr_done[ctx->device & 63] = true;
+    {
+        static std::mutex attr_mutex;          // two contexts on two host threads may get here at once
+        std::lock_guard<std::mutex> lock(attr_mutex);
+        static bool attr_done[64] = {};
+        if (!attr_done[ctx->device & 63]) {
+            FLARE_CUDA_OK(ctx, cudaFuncSetAttribute(decode_g32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                    (int)(STAGES * (2 * 8 * T * 16 + NG * 8 * HD * 4 + T * 8 * 2 * 4) + 128)));
+            attr_done[ctx->device & 63] = true;
+        }
     }
     // Programmatic dependent launch as in the Q8_0 path: after one of this library's own attention kernels
     // (which never write the cache) the next one may start early; both wait before touching q or records.

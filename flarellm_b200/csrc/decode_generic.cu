@@ -10,6 +10,7 @@
 // softmax states that are combined once at the end (shuffles, then shared memory).
 #include "common.cuh"
 #include <math_constants.h>
+#include <mutex>
 
 namespace {
 
@@ -476,6 +477,10 @@ int flare_launch_decode_generic(flare_attn_ctx* ctx, const DecodeArgs& a) {
     }
     if (!ok) return flare_set_error(ctx, FLARE_ERR_UNSUPPORTED, "no decode kernel for dtype %d head_dim %d", a.kv.dtype, hd);
     FLARE_LAUNCH_CHECK(ctx);
+    if (a.defer_merge && a.want_partial) {          // the caller merges: tell it where the records are
+        *a.work_out = p.work; *a.n_split_out = n_split;
+        return FLARE_OK;
+    }
     if (n_split > 1 || a.want_partial) {
         int threads = hd < 128 ? hd : 128;
         merge_partials_kernel<<<rows, threads, 0, ctx->stream>>>(p.work, (size_t)(hd + 2), (size_t)n_split * (hd + 2),
@@ -499,6 +504,9 @@ int flare_launch_decode_generic(flare_attn_ctx* ctx, const DecodeArgs& a) {
 // these bytes until the process exits, which is why the size is modest and fixed.  In host
 // code the array's name is only a handle; the device address is obtained once per device
 // with cudaGetSymbolAddress (while that device is current) and handed to the kernels.
+//
+// The first launch of each kernel instantiation (cache type x head_dim x heads per KV head) can also
+// make the driver load code lazily; that is the driver's business, not an allocation made here.
 //
 // Layout of the array: [0, kSmallBytes) the per-sequence (position, length) records followed
 // by the per-sequence attend lengths; [kSmallBytes, end) the split-KV partials
@@ -531,16 +539,21 @@ int flare_decode_noalloc(flare_attn_ctx* ctx, const flare_kv* kv, int layer, int
     if (ctx->device < 0 || ctx->device >= 64) return flare_set_error(ctx, FLARE_ERR_INVALID_ARG, "device ordinal out of range");
 
     // set-up, once per device, with that device current (the caller has bound it)
-    if (!g_noalloc_ptr[ctx->device]) {
-        void* p = nullptr;
-        cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
-        if (e != cudaSuccess || !p)
-            return flare_set_error(ctx, FLARE_ERR_CUDA, "cudaGetSymbolAddress(g_noalloc_scratch) failed: %s", cudaGetErrorString(e));
-        g_noalloc_ptr[ctx->device] = p;
+    char* scratch;
+    {
+        static std::mutex setup_mutex;     // two contexts on two host threads may make their first call at once
+        std::lock_guard<std::mutex> lock(setup_mutex);
+        if (!g_noalloc_ptr[ctx->device]) {
+            void* p = nullptr;
+            cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+            if (e != cudaSuccess || !p)
+                return flare_set_error(ctx, FLARE_ERR_CUDA, "cudaGetSymbolAddress(g_noalloc_scratch) failed: %s", cudaGetErrorString(e));
+            g_noalloc_ptr[ctx->device] = p;
+        }
+        scratch = (char*)g_noalloc_ptr[ctx->device];
     }
-    char* scratch = (char*)g_noalloc_ptr[ctx->device];
 
-    // small per-sequence records: built on the host stack, copied into the head of the array
+    // small per-sequence records, built on the host stack
     struct { int2 ring[FLARE_NOALLOC_MAX_BATCH]; int att[FLARE_NOALLOC_MAX_BATCH]; } small;
     int max_attend = 0;
     for (int b = 0; b < B; b++) {
@@ -554,9 +567,6 @@ int flare_decode_noalloc(flare_attn_ctx* ctx, const flare_kv* kv, int layer, int
         small.ring[b] = make_int2((int)kv->position[b], (int)kv->length[b]);
     }
     int* d_att = (int*)(scratch + sizeof(small.ring));
-    // pageable source: the runtime has taken its copy of `small` by the time these return
-    FLARE_CUDA_OK(ctx, cudaMemcpyAsync(scratch, small.ring, sizeof(int2) * B, cudaMemcpyHostToDevice, ctx->stream));
-    FLARE_CUDA_OK(ctx, cudaMemcpyAsync(d_att, small.att, sizeof(int) * B, cudaMemcpyHostToDevice, ctx->stream));
 
     const int G = num_heads / nkv;
     const int rows = B * n_q * num_heads;
@@ -575,11 +585,16 @@ int flare_decode_noalloc(flare_attn_ctx* ctx, const flare_kv* kv, int layer, int
     int n_split = want < max_split ? want : max_split;
     if (n_split < 1) n_split = 1;
     if (n_split > 256) n_split = 256;
+    // refuse before anything is put on the stream
     const size_t need = n_split > 1 ? (size_t)rows * n_split * (hd + 2) * sizeof(float) : 0;
     if (need > FLARE_NOALLOC_SCRATCH_BYTES - kSmallBytes)
         return flare_set_error(ctx, FLARE_ERR_INVALID_ARG,
                                "this call needs %zu bytes of split-KV workspace (%d rows x %d splits); the no-allocation "
                                "entry point has %zu", need, rows, n_split, (size_t)FLARE_NOALLOC_SCRATCH_BYTES - kSmallBytes);
+    // The records go into the head of the array.  The source is pageable stack memory: the runtime has taken
+    // its own copy of `small` by the time each of these calls returns.
+    FLARE_CUDA_OK(ctx, cudaMemcpyAsync(scratch, small.ring, sizeof(int2) * B, cudaMemcpyHostToDevice, ctx->stream));
+    FLARE_CUDA_OK(ctx, cudaMemcpyAsync(d_att, small.att, sizeof(int) * B, cudaMemcpyHostToDevice, ctx->stream));
     dim3 grid(n_split, nkv * p.n_chunks, B * n_q);
     bool ok = kv->dtype == FLARE_KV_F32 ? launch_tps<FLARE_KV_F32>(hd, gc, grid, ctx->stream, p)
                                         : launch_tps<FLARE_KV_Q8_0>(hd, gc, grid, ctx->stream, p);

@@ -24,8 +24,12 @@
 #include "common.cuh"
 #include "tma.cuh"
 #include <math_constants.h>
+#include <mutex>
 
 namespace {
+
+// Guards the per-device tables below: two contexts on two host threads may make their first call at once.
+std::mutex g_table_mutex;
 
 constexpr int T = 32;            // slots per tile
 constexpr int STAGES = 3;
@@ -358,9 +362,20 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
                 }
             }
             if (edge_tile) {       // only the first and last tile of a range hold slots outside it
+                // A slot outside the range gets weight exp2(-inf) = 0, but its V scale may be anything: rows past
+                // the end of the plane are never copied, so that part of the stage keeps what an earlier kernel
+                // left in shared memory (possibly Inf or NaN bit patterns, and 0 * NaN = NaN).  Zero it as well.
                 const int slot = slot0 + 8 * j + 2 * tig;
-                if (slot < lo || slot >= hi) s0 = -CUDART_INF_F;
-                if (slot + 1 < lo || slot + 1 >= hi) s1 = -CUDART_INF_F;
+                if (slot < lo || slot >= hi) {
+                    s0 = -CUDART_INF_F;
+#pragma unroll
+                    for (int h = 0; h < NB / 2; h++) vs[h][j][0] = 0.0f;
+                }
+                if (slot + 1 < lo || slot + 1 >= hi) {
+                    s1 = -CUDART_INF_F;
+#pragma unroll
+                    for (int h = 0; h < NB / 2; h++) vs[h][j][1] = 0.0f;
+                }
             }
             sc[j][0] = s0; sc[j][1] = s1;
             tmax = fmaxf(tmax, fmaxf(s0, s1));
@@ -591,6 +606,7 @@ int flare_launch_decode_q8(flare_attn_ctx* ctx, const DecodeArgs& a) {
     }
     if (cluster) {
         // all clusters must be resident at once, or the second wave costs more than the merge kernel did
+        std::lock_guard<std::mutex> lock(g_table_mutex);
         static int max_clusters[64][2][4] = {};            // [device][hd == 128][log2 c]: 0 = not asked yet
         const int lg = cluster == 8 ? 3 : (cluster == 4 ? 2 : 1);
         int& mc = max_clusters[ctx->device & 63][hd == 128][lg];
@@ -624,13 +640,16 @@ int flare_launch_decode_q8(flare_attn_ctx* ctx, const DecodeArgs& a) {
     p.work = (float*)((char*)ctx->d_work + (size_t)ctx->work_phase * need);
 
     // opt in to the large dynamic shared memory once per device
-    static bool attr_done[64][2] = {};
-    bool& done = attr_done[ctx->device & 63][hd == 128];
-    if (!done) {
-        const int max_smem = STAGES * (8 * 2 * T * hd + 2 * T * 8 * (hd / 32) * 2) + 1024;
-        if (hd == 64) FLARE_CUDA_OK(ctx, cudaFuncSetAttribute(decode_q8_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
-        else FLARE_CUDA_OK(ctx, cudaFuncSetAttribute(decode_q8_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
-        done = true;
+    {
+        std::lock_guard<std::mutex> lock(g_table_mutex);
+        static bool attr_done[64][2] = {};
+        bool& done = attr_done[ctx->device & 63][hd == 128];
+        if (!done) {
+            const int max_smem = STAGES * (8 * 2 * T * hd + 2 * T * 8 * (hd / 32) * 2) + 1024;
+            if (hd == 64) FLARE_CUDA_OK(ctx, cudaFuncSetAttribute(decode_q8_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
+            else FLARE_CUDA_OK(ctx, cudaFuncSetAttribute(decode_q8_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
+            done = true;
+        }
     }
     // Programmatic dependent launch: when the previous kernel on this stream is one of this path's
     // own kernels (it never writes the cache), this kernel may start early and request its first
@@ -652,6 +671,10 @@ int flare_launch_decode_q8(flare_attn_ctx* ctx, const DecodeArgs& a) {
     else FLARE_CUDA_OK(ctx, cudaLaunchKernelEx(&cfg, decode_q8_kernel<128>, *a.kmap, *a.vmap, p));
     FLARE_LAUNCH_CHECK(ctx);
     ctx->last_launch_overlappable = true;
+    if (a.defer_merge && a.want_partial) {          // the caller merges: tell it where the records are
+        *a.work_out = p.work; *a.n_split_out = n_split;
+        return FLARE_OK;
+    }
     if (!cluster && (n_split > 1 || a.want_partial)) {
         cudaLaunchConfig_t mcfg = {};
         mcfg.gridDim = dim3(rows);

@@ -37,6 +37,9 @@ struct PPParams {
     void* out;
     int out_dtype, batch, seq_len, num_heads, num_kv_heads, window;
     float scale_log2;
+    // f16 operands only: the power-of-two factors that undo the per-tensor scaling of the conversion,
+    // [0] = 1 / (scale of q * scale of k), [1] = 1 / scale of v (null: both 1)
+    const float* descale;
     int* err;
 };
 
@@ -124,7 +127,9 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
     return d;
 }
 
-template <int HD>
+// F16OPS: the operands (and P) are f16 instead of bf16.  f32 inputs take this form: 11 significant bits instead of 8
+// keep a row that attends a single key within 2^-11 of the f32 result, which bf16 operands would not.
+template <int HD, bool F16OPS>
 // 10 warps are allocated as 12 (granularity 4): 12 x 32 x 168 registers is what one SM holds
 __global__ void __launch_bounds__(320, 1) prefill_pp_kernel(const __grid_constant__ CUtensorMap qmap,
                                                             const __grid_constant__ CUtensorMap kmap,
@@ -196,8 +201,8 @@ __global__ void __launch_bounds__(320, 1) prefill_pp_kernel(const __grid_constan
     } else if (warp == 8) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            const uint32_t idesc_qk = idesc_bf16(BN, false);
-            const uint32_t idesc_pv = idesc_bf16(HD, true);
+            const uint32_t idesc_qk = F16OPS ? idesc_f16(BN, false) : idesc_bf16(BN, false);
+            const uint32_t idesc_pv = F16OPS ? idesc_f16(HD, true) : idesc_bf16(HD, true);
             int n_done[2] = {0, 0};            // tiles issued so far per query tile (for barrier parities)
             auto in_range = [&](int x, int j) { return x == 0 ? (j >= jA0 && j < jA1) : (j >= jB0 && j < jB1); };
             auto qk = [&](int x, int t) {      // S_x = Q_x K_t^T
@@ -263,6 +268,7 @@ __global__ void __launch_bounds__(320, 1) prefill_pp_kernel(const __grid_constan
         const uint32_t tS = tmem + x * 128 + lane_base, tO = tmem + 256 + x * 128 + lane_base;
         const int row_lo = p.window > 0 ? max(0, grow - p.window + 1) : 0;
         float m_ref = -CUDART_INF_F, l_sum = 0.0f;
+        const float scale_log2 = (F16OPS && p.descale) ? p.scale_log2 * __ldg(p.descale) : p.scale_log2;
         for (int j = jx0; j < jx1 && !aborted; j++) {
             const int nd = j - jx0;
             const int c0 = j * BN;
@@ -298,7 +304,7 @@ __global__ void __launch_bounds__(320, 1) prefill_pp_kernel(const __grid_constan
                 for (int c = 0; c < 8; c++) mx[c] = fmaxf(mx[c], __uint_as_float(v[120 + c]));
                 tmax = fmax3(fmax3(mx[0], mx[1], mx[2]), fmax3(mx[3], mx[4], mx[5]), fmaxf(mx[6], mx[7]));
             }
-            tmax *= p.scale_log2;
+            tmax *= scale_log2;
             const bool bump = tmax > m_ref + 8.0f;
             float alpha = 1.0f;
             if (bump) { alpha = fast_exp2(m_ref - tmax); m_ref = tmax; }
@@ -336,13 +342,14 @@ __global__ void __launch_bounds__(320, 1) prefill_pp_kernel(const __grid_constan
 #pragma unroll
                 for (int i = 0; i < 32; i++) {
                     float x0, x1;
-                    ffma2(x0, x1, __uint_as_float(u[2 * i]), __uint_as_float(u[2 * i + 1]), p.scale_log2, neg_m);
+                    ffma2(x0, x1, __uint_as_float(u[2 * i]), __uint_as_float(u[2 * i + 1]), scale_log2, neg_m);
                     float p0, p1;
                     if (POLY_EVERY > 0 && (i % POLY_EVERY) == POLY_EVERY - 1) exp2_poly2(p0, p1, x0, x1);   // one pair in POLY_EVERY on the FMA pipe
                     else { p0 = fast_exp2(x0); p1 = fast_exp2(x1); }
                     fadd2(ls[(2 * i) & 3], ls[(2 * i + 1) & 3], ls[(2 * i) & 3], ls[(2 * i + 1) & 3], p0, p1);
                     uint32_t w;
-                    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(w) : "f"(p1), "f"(p0));
+                    if (F16OPS) asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(w) : "f"(p1), "f"(p0));
+                    else asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(w) : "f"(p1), "f"(p0));
                     u[i] = w;                      // packed in place: slot i was consumed already
                 }
                 // this half's P goes over columns [32 half, 32 half + 32): S columns that pass 2 has already read
@@ -358,7 +365,8 @@ __global__ void __launch_bounds__(320, 1) prefill_pp_kernel(const __grid_constan
         if (!aborted && n_x > 0) PP_WAIT(&bars->o_final[x], 0);
         if (!aborted && n_x > 0) {
             tc_fence_after();
-            const float inv = l_sum > 0.0f ? 1.0f / l_sum : 0.0f;
+            float inv = l_sum > 0.0f ? 1.0f / l_sum : 0.0f;
+            if (F16OPS && p.descale) inv *= __ldg(p.descale + 1);
             const size_t orow = (((size_t)b * S + grow) * p.num_heads + h) * HD;
 #pragma unroll 1
             for (int ch = 0; ch < HD / 32; ch++) {
@@ -406,18 +414,23 @@ int flare_launch_prefill_pp(flare_attn_ctx* ctx, const CUtensorMap& qm, const CU
     p.out = a.out; p.out_dtype = a.out_dtype; p.batch = a.batch; p.seq_len = a.seq_len; p.num_heads = a.num_heads;
     p.num_kv_heads = a.num_kv_heads; p.window = a.window;
     p.scale_log2 = (1.0f / sqrtf((float)a.head_dim)) * 1.4426950408889634f;
+    p.descale = a.descale;
     p.err = ctx->d_err;
     dim3 grid((a.seq_len + 2 * BM - 1) / (2 * BM), a.num_heads, a.batch);
     // one CTA per SM: it owns all 512 tensor-memory columns
+    const int smem128 = SmemPP<128>::TOTAL + 1024;
+    const int smem64 = (SmemPP<64>::TOTAL + 1024) > 120 * 1024 ? (SmemPP<64>::TOTAL + 1024) : 120 * 1024;
+#define PP_LAUNCH(HD_, F16_, SMEM_)                                                                                     \
+    do {                                                                                                                \
+        FLARE_CUDA_OK(ctx, cudaFuncSetAttribute(prefill_pp_kernel<HD_, F16_>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_)); \
+        prefill_pp_kernel<HD_, F16_><<<grid, 320, SMEM_, ctx->stream>>>(qm, km, vm, p);                                  \
+    } while (0)
     if (a.head_dim == 128) {
-        const int smem = SmemPP<128>::TOTAL + 1024;
-        FLARE_CUDA_OK(ctx, cudaFuncSetAttribute(prefill_pp_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        prefill_pp_kernel<128><<<grid, 320, smem, ctx->stream>>>(qm, km, vm, p);
+        if (a.f16_ops) PP_LAUNCH(128, true, smem128); else PP_LAUNCH(128, false, smem128);
     } else {
-        const int smem = (SmemPP<64>::TOTAL + 1024) > 120 * 1024 ? (SmemPP<64>::TOTAL + 1024) : 120 * 1024;
-        FLARE_CUDA_OK(ctx, cudaFuncSetAttribute(prefill_pp_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        prefill_pp_kernel<64><<<grid, 320, smem, ctx->stream>>>(qm, km, vm, p);
+        if (a.f16_ops) PP_LAUNCH(64, true, smem64); else PP_LAUNCH(64, false, smem64);
     }
+#undef PP_LAUNCH
     FLARE_LAUNCH_CHECK(ctx);
     return FLARE_OK;
 }

@@ -67,7 +67,10 @@ __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t saddr, uint32_t panel_
 __device__ __forceinline__ uint32_t idesc_bf16(int n, bool b_mn_major) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(tc5::BM >> 4) << 24);
 }
-
+// The same with f16 A and B (format fields 0).
+__device__ __forceinline__ uint32_t idesc_f16(int n, bool b_mn_major) {
+    return (1u << 4) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(tc5::BM >> 4) << 24);
+}
 
 // D[tmem] (+)= A[tmem] * B[smem desc]: A is M x 16 bf16, row i in lane i, two elements per 32-bit column
 __device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {

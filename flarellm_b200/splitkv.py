@@ -9,6 +9,16 @@ all-gathered (NCCL over NVLink on GPUs) and every rank merges them by log-sum-ex
     m* = max_r m_r,   l = sum_r l_r e^(m_r - m*),   o = sum_r o_r e^(m_r - m*) / l
 
 The only collective is that all-gather of ``num_heads * (head_dim + 2)`` floats per rank.
+
+Two front ends:
+
+* ``CAbiSplitDecoder`` — what a host of the library uses: ``flare_attn_comm_init`` +
+  ``flare_decode_attn_splitkv_multi``; the exchange happens inside the library (records stored straight
+  into the peers' buffers by the merging kernel, or ``ncclAllGather``), ``torch.distributed`` only carries
+  the 128-byte communicator id to the other ranks.
+* ``SplitKvDecoder`` — the same step spelled out on the host with ``torch.distributed`` (any backend),
+  with pluggable partial / merge functions; the CPU tests run it over gloo with a CPU routine standing in
+  for the kernels.
 """
 from __future__ import annotations
 
@@ -44,6 +54,11 @@ class SplitKvDecoder:
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.eng, self.kv, self.num_heads, self.n_local = eng, kv_local, num_heads, n_local
+        if eng is not None and partial_fn is None:
+            # The collective is ordered against torch's current stream only, so the engine's kernels must run
+            # on that stream too: otherwise the all-gather could read the records before they are written.
+            import torch
+            eng.set_stream(torch.cuda.current_stream(torch.device("cuda", eng.device)).cuda_stream)
         self.partial_fn = partial_fn or self._partial_engine
         self.merge_fn = merge_fn or self._merge_engine
         self._bufs = None
@@ -85,3 +100,74 @@ class SplitKvDecoder:
         else:
             self.dist.all_gather(list(gathered.unbind(0)), part.contiguous(), group=self.group)  # gloo (CPU tests)
         return self.merge_fn(gathered)
+
+
+class CAbiSplitDecoder:
+    """Decode attention for one sequence sharded over the ranks of ``dist`` through the library's own
+    multi-GPU entry points (include/flare_attn.h: flare_attn_comm_*, flare_decode_attn_splitkv_multi).
+
+    ``kv_local`` holds this rank's slots ``0 .. n_local-1``.  ``direct=True`` asks for the exchange without
+    a collective (peer stores); if the set-up is refused (no peer access between the GPUs) the NCCL
+    all-gather inside the library is used and ``direct_error`` says why.
+    """
+
+    def __init__(self, eng, kv_local, num_heads: int, n_local: int, dist=None, direct: bool = True, wait_ms: int = 0):
+        import torch
+        self.torch, self.eng, self.kv, self.num_heads, self.n_local, self.dist = torch, eng, kv_local, num_heads, n_local, dist
+        self.world = dist.get_world_size() if dist is not None else 1
+        self.rank = dist.get_rank() if dist is not None else 0
+        self.direct_error = None
+        rows, hd = kv_local.batch * num_heads, kv_local.head_dim
+        if self.world > 1:
+            box = [type(eng).comm_unique_id() if self.rank == 0 else None]
+            dist.broadcast_object_list(box, src=0)
+            eng.comm_init(box[0], self.rank, self.world)
+            self.how = "ncclAllGather issued inside the library + merge kernel"
+            if direct:
+                # the set-up is collective: every rank must attempt it, and all must agree on the outcome
+                try:
+                    eng.comm_enable_direct(rows, hd)
+                    ok = 1
+                except Exception as e:      # FlareError: no peer access / IPC refused
+                    self.direct_error, ok = str(e), 0
+                flag = torch.tensor([ok], device="cuda")
+                dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+                if int(flag.item()) == 1:
+                    self.how = "records stored into the peers' buffers by the merging kernel (peer stores, bounded wait, no collective)"
+                elif ok:
+                    raise RuntimeError("direct exchange set up on this rank but not on every rank")
+            if wait_ms:
+                eng.comm_set_wait_ms(wait_ms)
+        else:
+            eng.comm_init(None, 0, 1)
+            self.how = "one GPU: merge kernel only"
+        dev = torch.device("cuda", eng.device)
+        self.out = torch.empty(rows, hd, device=dev)
+        self.part = torch.empty(rows, hd + 2, device=dev)
+
+    def decode(self, layer, q):
+        self.eng.decode_splitkv_multi(self.kv, layer, self.num_heads, q.data_ptr(), self.n_local, out=self.out.data_ptr())
+        return self.out
+
+    def partial_only(self, layer, q):
+        """This rank's attention kernels alone (no exchange), for timing."""
+        self.eng.decode_partial(self.kv, layer, self.num_heads, q.data_ptr(), 0, self.n_local, out=self.part.data_ptr())
+        return self.part
+
+    def status(self) -> str:
+        """Waits for the queued calls; "ok", or the library's message (e.g. a rank that did not show up in time)."""
+        try:
+            self.eng.sync()
+            return "ok"
+        except Exception as e:
+            return str(e)
+
+    def close(self):
+        self.torch.cuda.synchronize()
+        if self.dist is not None:
+            self.dist.barrier()             # nobody frees a buffer that a peer may still be writing
+        self.eng.comm_destroy()
+
+
+def make_split_decoder(eng, kv_local, num_heads, n_local, dist=None, direct=True):
+    return CAbiSplitDecoder(eng, kv_local, num_heads, n_local, dist, direct)

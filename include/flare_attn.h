@@ -54,7 +54,9 @@ typedef enum {
     FLARE_ERR_OOM = 3,
     FLARE_ERR_CUDA = 4,
     FLARE_ERR_TIMEOUT = 5,
-    FLARE_ERR_STATE = 6          /* e.g. attention before any KV cache exists */
+    FLARE_ERR_STATE = 6,         /* e.g. attention before any KV cache exists */
+    FLARE_ERR_NCCL = 7,          /* the collective library failed or is missing (multi-GPU calls only) */
+    FLARE_ERR_BOUNDS = 8         /* range-checked build only: a kernel computed an index outside its buffer */
 } flare_status;
 
 /* How a cache stores its rows. */
@@ -109,6 +111,28 @@ FLARE_API const char* flare_attn_last_error(const flare_attn_ctx* ctx);
 FLARE_API uint64_t flare_attn_launch_count(const flare_attn_ctx* ctx);
 /* ComputeBackend::name (flare-core/src/model.rs:615-617): "cuda". */
 FLARE_API const char* flare_attn_backend_name(void);
+
+/* Per-call measurements, the counterpart of the reference's PrefillProfile / attention_ms
+ * (flare-core/src/model.rs:1198-1236, 2784-2795), taken on the device instead of with a host clock.
+ * While enabled, every attention call (decode, partial, step, prefill) is bracketed by two CUDA events on
+ * the context's stream and is not overlapped with its predecessor.  flare_attn_get_stats waits for
+ * the last measured call to finish.
+ *   bytes   algorithmic K/V bytes of the attended slots in the cache's storage format
+ *   flops   4 * query rows * head_dim * attended (query, key) pairs
+ *   frac    achieved / peak: bytes per second over the HBM peak for decode, flops per second over the
+ *           tensor peak for prefill; peaks are the caller's (flare_attn_set_peaks), default 7700 GB/s
+ *           and 2250 TFLOP/s (nominal B200). */
+typedef enum { FLARE_OP_NONE = 0, FLARE_OP_DECODE = 1, FLARE_OP_PREFILL = 2 } flare_stat_op;
+typedef struct {
+    uint64_t calls;                /* measured calls so far */
+    int32_t last_op;               /* flare_stat_op */
+    int32_t reserved;
+    double last_elapsed_us, last_bytes, last_flops, last_gbs, last_tflops, last_frac_of_peak;
+    double total_elapsed_us, total_bytes, total_flops;
+} flare_attn_stats;
+FLARE_API int flare_attn_enable_stats(flare_attn_ctx* ctx, int on);
+FLARE_API int flare_attn_set_peaks(flare_attn_ctx* ctx, double hbm_gbs, double tensor_tflops);
+FLARE_API int flare_attn_get_stats(flare_attn_ctx* ctx, flare_attn_stats* out);
 
 /* No counterpart in the reference.  Every wait inside the kernels of this library (on a tile's
  * mbarrier) is bounded: when it runs out the kernel records FLARE_ERR_TIMEOUT in the context's status
@@ -201,6 +225,17 @@ FLARE_API int flare_decode_attn(flare_attn_ctx* ctx, flare_kv* kv, int layer, in
                                 const float* q, int n_q, const int* attend_len, float softcap,
                                 float* out, int on_device);
 
+/* One decode step of one layer for a host that batches sequences: what ComputeBackend::gpu_kv_write
+ * followed by grouped_query_attention_from_gpu_cache (model.rs:2199-2224) collapse to.  Row b of
+ * key/value ([batch][kv_dim], post-RoPE) is stored at sequence b's current ring position exactly as
+ * flare_kv_write_step_f32 does, then q ([batch][1][num_heads][head_dim]) attends min(length + 1,
+ * max_seq_len) slots exactly as flare_decode_attn does.  The ring state is not advanced.  With host
+ * buffers the three inputs cross the bus in one staged transfer (or straight from the caller's
+ * buffers when those are page-locked) and the call synchronises once, when `out` is filled. */
+FLARE_API int flare_decode_step(flare_attn_ctx* ctx, flare_kv* kv, int layer, int num_heads,
+                                const float* key, const float* value, const float* q, float* out,
+                                int on_device);
+
 /* No counterpart in the reference.  flare_decode_attn for callers that must not allocate
  * device memory when they call in: an inference server that gave all GPU memory to its own
  * pool at start-up, a real-time callback that may not wait on the driver's allocator, a host
@@ -210,16 +245,23 @@ FLARE_API int flare_decode_attn(flare_attn_ctx* ctx, flare_kv* kv, int layer, in
  * loads the library carries until the process exits.
  *   - q_dev and out_dev are DEVICE pointers owned by the caller ([batch][n_q][num_heads][head_dim]
  *     f32); attend_len is a host array as in flare_decode_attn (NULL = ring state).
- *   - f32 and Q8_0 caches, head_dim 64 or 128, batch <= 256.  A call whose workspace would not
- *     fit (rows x splits x (head_dim + 2) floats) is refused with FLARE_ERR_INVALID_ARG and a
- *     message that names both sizes.
+ *   - f32 and Q8_0 caches, head_dim 64 or 128, batch <= 256 (more is refused with
+ *     FLARE_ERR_INVALID_ARG).  A call whose partial results (rows x splits x (head_dim + 2)
+ *     floats) would not fit in the array is refused the same way, with a message that names both
+ *     sizes, before anything is put on the stream; with the split rule in use and batch <= 256
+ *     the partials stay below 5 MiB, so that refusal is a guard, not a limit callers meet.
+ *   - it always runs the general CUDA-core split-KV kernel.  For a Q8_0 cache flare_decode_attn
+ *     picks the faster tensor-core kernel instead, so the two entry points agree within the
+ *     output tolerance (2e-3 + 1e-3 |x|), not bit for bit, and this one is the slower of the two.
  *   - the first call on a device is the set-up call: it looks up the array's device address
  *     (cudaGetSymbolAddress), and the driver may load the library's device image, array
- *     included, at that moment.  Make that first call before any stream capture begins.
+ *     included, at that moment.  This first call should come before any stream capture begins.
+ *     The first launch of each kernel variant (cache type x head_dim x heads per KV head) may
+ *     likewise make the driver load code.  The per-sequence lengths travel to the device through
+ *     a copy from the host stack on every call.
  *   - every call on a device shares the one array and leaves its partial results in it; a
  *     call overwrites what it reads, so nothing needs clearing, but two calls that overlap on
- *     the GPU (different streams or contexts) race — serialise them.
- * Results are the same as flare_decode_attn's. */
+ *     the GPU (different streams or contexts) race: serialise them. */
 FLARE_API int flare_decode_attn_noalloc(flare_attn_ctx* ctx, flare_kv* kv, int layer, int num_heads,
                                         const float* q_dev, int n_q, const int* attend_len,
                                         float* out_dev);
@@ -236,6 +278,47 @@ FLARE_API int flare_decode_attn_partial(flare_attn_ctx* ctx, flare_kv* kv, int l
 FLARE_API int flare_merge_partials(flare_attn_ctx* ctx, const float* partials, int n_parts, int rows,
                                    int head_dim, float* out, int on_device);
 
+/* ---------------------------------------------------------------- one sequence over several GPUs
+ * No counterpart in the reference (single device).  One process per GPU; every process creates its context,
+ * then all of them make the same sequence of calls below.  The recurrence merged across GPUs is the block
+ * form of flare-core/src/model.rs:9945-9956.
+ *
+ * flare_attn_comm_unique_id   rank 0 obtains a 128-byte id and hands it to the other ranks over any host
+ *                             channel (the Rust side: whatever already connects its workers).
+ * flare_attn_comm_init        collective: joins the NCCL communicator (libnccl.so.2 is loaded at run time, or
+ *                             the file named by FLARE_NCCL_LIB).  world = 1 needs no id and no NCCL.
+ * flare_attn_comm_enable_direct  collective, optional: sets up the exchange without a collective call — every
+ *                             rank allocates a record buffer for up to max_rows = batch * num_heads rows of
+ *                             head_dim (64 or 128) floats and maps its peers' buffers (CUDA IPC: one process per
+ *                             GPU with peer access).  Afterwards the kernel that finishes a rank's attention
+ *                             stores its records straight into the peers' buffers and merges as soon as theirs
+ *                             have arrived, waiting at most the limit of flare_attn_comm_set_wait_ms (default
+ *                             2000 ms); when the wait runs out the call reports FLARE_ERR_TIMEOUT and the
+ *                             context stays usable.  Without it the records travel by ncclAllGather.
+ * flare_attn_comm_destroy     frees the buffers and the communicator; make sure no rank is still inside a
+ *                             multi-GPU call (a host barrier) before any rank destroys.
+ *
+ * flare_decode_attn_splitkv_multi   `kv` holds this rank's share of the sequence in its slots
+ *                             0 .. n_local_slots-1 (a contiguous range of the whole sequence; which range does
+ *                             not matter to the result).  q [batch][1][num_heads][head_dim] is the same on every
+ *                             rank; every rank receives the attention output over the whole sequence in `out`
+ *                             [batch][1][num_heads][head_dim].  head_dim 64 or 128.  Without a communicator, or in
+ *                             a world of one, it is flare_decode_attn over the slots given.
+ * NCCL failures are reported as FLARE_ERR_NCCL with NCCL's own message in flare_attn_last_error. */
+#define FLARE_COMM_ID_BYTES 128
+FLARE_API int flare_attn_comm_unique_id(void* id_out);
+FLARE_API int flare_attn_comm_init(flare_attn_ctx* ctx, const void* id, int rank, int world);
+FLARE_API int flare_attn_comm_enable_direct(flare_attn_ctx* ctx, int max_rows, int head_dim);
+FLARE_API int flare_attn_comm_set_wait_ms(flare_attn_ctx* ctx, unsigned wait_ms);
+FLARE_API int flare_attn_comm_info(const flare_attn_ctx* ctx, int* rank, int* world, int* direct);
+FLARE_API int flare_attn_comm_destroy(flare_attn_ctx* ctx);
+FLARE_API int flare_decode_attn_splitkv_multi(flare_attn_ctx* ctx, flare_kv* kv, int layer, int num_heads,
+                                              const float* q, int n_local_slots, float* out, int on_device);
+/* Runs the give-up path of the direct exchange on one GPU, without a second rank and without a fault: a
+ * two-rank exchange laid out in this device's own memory in which rank 1 never publishes; the 50 ms wait
+ * runs out.  Expected return value: FLARE_ERR_TIMEOUT; the context stays usable. */
+FLARE_API int flare_attn_comm_selftest_missing_peer(flare_attn_ctx* ctx);
+
 /* Replaces ComputeBackend::grouped_query_attention (model.rs:246-267;
  * flare-gpu/src/backend.rs:4701-4811): K/V given as host f32 [seq_len][kv_dim]. */
 FLARE_API int flare_gqa_attention_host(flare_attn_ctx* ctx, const float* q, const float* k_cache,
@@ -246,8 +329,11 @@ FLARE_API int flare_gqa_attention_host(flare_attn_ctx* ctx, const float* q, cons
  * flare-gpu/src/backend.rs:4981-5022, 2461-2533): causal self-attention of `batch`
  * prompts of seq_len tokens; row t attends rows max(0, t-window+1)..=t (window 0 = all).
  * q [batch][seq_len][num_heads][head_dim]; k, v [batch][seq_len][num_kv_heads][head_dim];
- * in_dtype / out_dtype are flare_dtype.  f32 inputs are rounded to bf16 for the tensor cores,
- * accumulation is f32. */
+ * in_dtype / out_dtype are flare_dtype.  Accumulation is f32.  At head_dim 64 / 128 the products run
+ * on the tensor cores: bf16 inputs as they are; f32 inputs (the trait hook's type) rounded to f16
+ * (11 significant bits; a tensor whose largest magnitude exceeds 2^15 is scaled by a power of two
+ * first, exactly), which keeps the result within 2e-3 + 1e-3 |x| of the f32 CPU loop.  Other
+ * head sizes run in f32 on the general kernel. */
 FLARE_API int flare_prefill_attn(flare_attn_ctx* ctx, const void* q, const void* k, const void* v,
                                  int in_dtype, int batch, int seq_len, int num_heads, int num_kv_heads,
                                  int head_dim, int window, float softcap, void* out, int out_dtype,

@@ -62,6 +62,7 @@ def _declare(L):
     L.orc_dequant_q8_0_block.argtypes = [_u8p, _sz, _f32p]
     L.orc_quantize_q8_0.argtypes = [_f32p, _sz, _u8p]
     L.orc_dequant_q8_0.argtypes = [_u8p, _sz, _f32p]
+    L.orc_dequant_q8_0_mt.argtypes = [_u8p, _sz, _f32p, C.c_int]
     L.orc_q2_quantize_to_packed.argtypes = [_f32p, _sz, _u8p, _f32p, _f32p]
     L.orc_q2_dequant_per_channel.argtypes = [_u8p, _f32p, _f32p, _f32p, _sz]
     L.orc_q2_dequant_per_token.argtypes = [_u8p, C.c_float, C.c_float, _f32p, _sz]
@@ -180,6 +181,15 @@ def dequant_q8_0(blocks) -> np.ndarray:
     assert b.shape[-1] % 34 == 0
     out = np.empty(b.shape[:-1] + (b.shape[-1] // 34 * 32,), dtype=np.float32)
     lib().orc_dequant_q8_0(bp, out.size, out.ctypes.data_as(_f32p))
+    return out
+
+
+def dequant_q8_0_mt(blocks, threads) -> np.ndarray:
+    """dequant_q8_0 spread over host threads (same arithmetic per block)."""
+    b, bp = _u8(blocks)
+    assert b.shape[-1] % 34 == 0
+    out = np.empty(b.shape[:-1] + (b.shape[-1] // 34 * 32,), dtype=np.float32)
+    lib().orc_dequant_q8_0_mt(bp, out.size, out.ctypes.data_as(_f32p), int(threads))
     return out
 
 

@@ -183,6 +183,18 @@ ORC_API void orc_dequant_q8_0(const uint8_t* blocks, size_t n_values, float* out
     for (size_t b = 0; b < n_values / Q8_BLOCK; b++)
         orc_dequant_q8_0_block(blocks + b * Q8_BYTES, Q8_BYTES, out + b * Q8_BLOCK);
 }
+/* The same block by block, spread over host threads in chunks of 4096 blocks (for the timed
+ * all-cores baseline only; the arithmetic per block is orc_dequant_q8_0_block). */
+typedef struct { const uint8_t* blocks; float* out; size_t n_blocks; } orc_dq_args;
+static void orc_dq_task(long c, void* a_) {
+    orc_dq_args* a = (orc_dq_args*)a_;
+    size_t b0 = (size_t)c * 4096, b1 = b0 + 4096 < a->n_blocks ? b0 + 4096 : a->n_blocks;
+    for (size_t b = b0; b < b1; b++) orc_dequant_q8_0_block(a->blocks + b * Q8_BYTES, Q8_BYTES, a->out + b * Q8_BLOCK);
+}
+ORC_API void orc_dequant_q8_0_mt(const uint8_t* blocks, size_t n_values, float* out, int threads) {
+    orc_dq_args a = {blocks, out, n_values / Q8_BLOCK};
+    orc_parallel_for((long)((a.n_blocks + 4095) / 4096), threads, orc_dq_task, &a);
+}
 
 /* ------------------------------------------------------------------------ */
 /* 2-bit pack / unpack                                                      */

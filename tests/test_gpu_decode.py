@@ -322,6 +322,69 @@ def test_q8_head_dim_128_long_context_and_partials(eng, fb, orc):
     kv.free()
 
 
+@pytest.mark.parametrize("ms", [70, 173])
+def test_q8_ring_size_not_a_tile_multiple_after_non_finite_scales(eng, fb, orc, ms):
+    """A ring of 70 or 173 slots is not a multiple of the 32-slot tile and gives a CTA at most three tiles, so
+    every stage is on its first use: the scale rows of the last tile that lie beyond the ring are never copied
+    and that part of shared memory holds what the previous kernel left.  Here the previous kernel streamed a
+    cache whose scales are Inf / NaN bit patterns on every SM; none of it may leak into the result."""
+    nh, nkv, hd = 32, 8, 64
+    poison = eng.kv_alloc(1, 300, 96, nkv, hd, fb.KV_Q8_0)
+    blocks = np.zeros((96, nkv * hd // 32, 34), np.uint8)
+    blocks[:, :, 0:2] = [0x00, 0x7E]                          # f16 NaN scale
+    blocks[::2, :, 0:2] = [0x00, 0x7C]                        # f16 +Inf scale
+    for b in range(300):
+        poison.import_q8_0_blocks(0, b, 0, blocks, blocks)
+    poison.advance(-1, 95)
+    B = 8
+    kv = eng.kv_alloc(1, B, ms, nkv, hd, fb.KV_Q8_0)
+    k, v = normal(141, (B, ms, nkv * hd)), normal(142, (B, ms, nkv * hd))
+    for b in range(B):
+        kv.append(0, b, k[b, :-1], v[b, :-1]); kv.advance(b, ms - 1)
+        kv.write(0, b, ms - 1, k[b, -1], v[b, -1])
+    q = normal(143, (B, 1, nh, hd), 0.4)
+    kd = orc.dequant_q8_0(orc.quantize_q8_0(k))
+    vd = orc.dequant_q8_0(orc.quantize_q8_0(v))
+    want = orc.gqa_decode_batched(q.reshape(B, 1, -1), kd, vd, np.full(B, ms, np.int32), nh, nkv, hd)
+    for attempt in range(2):
+        eng.decode(poison, 0, nh, np.zeros((300, 1, nh, hd), np.float32))     # leaves NaN / Inf scales in every stage
+        got = eng.decode(kv, 0, nh, q)
+        assert_close(got, want, f"ring of {ms} slots, attempt {attempt}")
+    # two local shards as separate partial calls (the shape a rank of a split sequence sees), then the merge
+    eng.decode(poison, 0, nh, np.zeros((300, 1, nh, hd), np.float32))
+    cut = (ms // 2) // 32 * 32 + 32
+    parts = np.stack([eng.decode_partial(kv, 0, nh, q, 0, cut), eng.decode_partial(kv, 0, nh, q, cut, ms)])
+    merged = eng.merge_partials(parts.reshape(2, B * nh, hd + 2), 2, B * nh, hd)
+    assert_close(merged, want, f"ring of {ms} slots, two partials merged")
+    poison.free(); kv.free()
+
+
+def test_stats_report_bytes_flops_and_time(eng, fb, orc):
+    """flare_attn_get_stats: device time by CUDA events, algorithmic bytes and flops of the last call."""
+    nh, nkv, hd, ctx, B = 32, 8, 64, 2048, 4
+    kv = eng.kv_alloc(1, B, ctx, nkv, hd, fb.KV_Q8_0)
+    for b in range(B):
+        kv.append(0, b, normal(151 + b, (ctx - 1, nkv * hd)), normal(161 + b, (ctx - 1, nkv * hd)))
+    kv.advance(-1, ctx - 1)
+    q = normal(171, (B, 1, nh, hd), 0.4)
+    eng.enable_stats(True)
+    eng.set_peaks(6500.0, 1600.0)
+    before = eng.stats().calls
+    eng.decode(kv, 0, nh, q)
+    eng.decode(kv, 0, nh, q, attend_len=[1000, 1, 0, 2048])
+    st = eng.stats()
+    assert st.calls == before + 2 and st.last_op == fb.OP_DECODE
+    assert st.last_bytes == (1000 + 1 + 2048) * 2 * (nkv * hd + nkv * hd // 16)
+    assert st.last_flops == 4.0 * nh * hd * (1000 + 1 + 2048)
+    assert 0.5 < st.last_elapsed_us < 5000.0
+    assert abs(st.last_gbs - st.last_bytes / (st.last_elapsed_us * 1e-6) / 1e9) < 1e-6 * st.last_gbs
+    assert abs(st.last_frac_of_peak - st.last_gbs / 6500.0) < 1e-9
+    eng.enable_stats(False)
+    eng.decode(kv, 0, nh, q)
+    assert eng.stats().calls == before + 2
+    kv.free()
+
+
 def test_bounded_wait_gives_up_and_context_survives(fb, orc):
     """A kernel wait that nothing satisfies runs out, the status reaches the host as ERR_TIMEOUT, and the
     same context then computes a correct attention (nothing hung, nothing poisoned)."""

@@ -64,3 +64,35 @@ def test_two_rank_split_equals_single_device(total):
     mp.spawn(_worker, args=(world, port, 5, total, 8, 2, 32, ret), nprocs=world, join=True)
     assert len(ret) == world
     assert all(err < 2e-6 for err in ret.values()), dict(ret)
+
+
+def _worker_absent(rank, world, port, ret):
+    """Rank 1 never makes the call; rank 0's all-gather ends with an error after the group's short timeout."""
+    import datetime
+    import torch
+    import torch.distributed as dist
+    from flarellm_b200.splitkv import SplitKvDecoder
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=3))
+    nh, hd = 4, 8
+    dec = SplitKvDecoder(num_heads=nh, n_local=0, partial_fn=lambda layer, q: torch.zeros(nh, hd + 2),
+                         merge_fn=lambda g: torch.zeros(nh, hd))
+    dec.decode(0, torch.zeros(nh * hd))            # a first step with every rank present
+    if rank == 1:
+        ret[rank] = "left between steps"
+        return                                      # leaves between steps: nothing of it is in flight
+    try:
+        dec.decode(0, torch.zeros(nh * hd))
+        ret[rank] = "no error"
+    except Exception as e:                          # the collective reports the missing rank; nothing hangs
+        ret[rank] = "error: " + type(e).__name__
+
+
+def test_a_rank_that_skips_the_call_gives_the_others_an_error_not_a_hang():
+    import torch.multiprocessing as mp
+    world, port = 2, _free_port()
+    ret = mp.Manager().dict()
+    mp.spawn(_worker_absent, args=(world, port, ret), nprocs=world, join=True)
+    assert ret[1] == "left between steps"
+    assert ret[0].startswith("error"), dict(ret)

@@ -81,3 +81,28 @@ def test_noalloc_rejects_what_does_not_fit():
     assert e.value.status == fb.ERR_INVALID_ARG and "no-allocation maximum" in str(e.value)
     kv.free()
     eng.close()
+
+
+def test_noalloc_serves_the_largest_batch_it_accepts(orc):
+    """256 sequences x 32 heads is the most rows the entry point takes.  The workspace guard (partials larger
+    than the 8 MiB array are refused) cannot fire below that: the split count falls as the rows grow, and rows x
+    splits x (head_dim + 2) floats stays under 5 MiB.  So the largest batch must simply run, and run right."""
+    import torch
+    import flarellm_b200 as fb
+
+    nh, nkv, hd, B, ctx = 32, 8, 64, 256, 96
+    eng = fb.Engine(0)
+    kv = eng.kv_alloc(1, B, ctx, nkv, hd, fb.KV_F32)
+    k, v = normal(321, (B, ctx, nkv * hd)), normal(322, (B, ctx, nkv * hd))
+    for b in range(B):
+        kv.append(0, b, k[b], v[b])
+    attend = (np.arange(B, dtype=np.int32) % ctx) + 1
+    q = normal(323, (B, 1, nh, hd), 0.4)
+    q_dev = torch.from_numpy(q).cuda()
+    out_dev = torch.full((B, 1, nh, hd), float("nan"), device="cuda")
+    eng.decode_noalloc(kv, 0, nh, q_dev.data_ptr(), out_dev.data_ptr(), attend_len=attend)
+    eng.sync()
+    want = orc.gqa_decode_batched(q.reshape(B, 1, -1), k, v, attend, nh, nkv, hd, threads=8)
+    assert_close(out_dev.cpu().numpy(), want, "no-alloc at batch 256")
+    kv.free()
+    eng.close()
