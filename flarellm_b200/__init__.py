@@ -60,6 +60,9 @@ SYMBOLS = [
     ("flare_kv_write_f32", _i, [_vp, _i, _i, _i64, _vp, _vp, _i]),
     ("flare_kv_append_f32", _i, [_vp, _i, _i, _i, _vp, _vp, _i]),
     ("flare_kv_write_step_f32", _i, [_vp, _i, _vp, _vp, _i]),
+    ("flare_kv_set_rope_table", _i, [_vp, _vp, _vp, _i]),
+    ("flare_kv_write_step_rope_f32", _i, [_vp, _i, _vp, _vp, _i64p, _i]),
+    ("flare_rope_rows_f32", _i, [_vp, _vp, _i, _i, _i64p, _i]),
     ("flare_kv_advance", _i, [_vp, _i, _i]),
     ("flare_kv_get_state", _i, [_vp, _i, _i64p, _i64p]),
     ("flare_kv_set_state", _i, [_vp, _i, _i64, _i64]),
@@ -370,6 +373,35 @@ class KvCache:
             assert key.size == value.size == self.batch * self.kv_dim
         self.eng.check(self.L.flare_kv_write_step_f32(self.h, layer, _ptr(key), _ptr(value), int(on_device)))
 
+    def set_rope_table(self, cos, sin):
+        """The caller's RopeTable: cos, sin [table_len][head_dim // 2] f32."""
+        cos = np.ascontiguousarray(cos, dtype=np.float32)
+        sin = np.ascontiguousarray(sin, dtype=np.float32)
+        assert cos.shape == sin.shape and cos.shape[1] == self.head_dim // 2
+        self.eng.check(self.L.flare_kv_set_rope_table(self.h, _ptr(cos), _ptr(sin), cos.shape[0]))
+
+    def write_step_rope(self, layer, key, value, positions):
+        """write_step on key rows that are still to be rotated for ``positions`` [batch]."""
+        on_device = not isinstance(key, np.ndarray)
+        if not on_device:
+            key = np.ascontiguousarray(key, dtype=np.float32)
+            value = np.ascontiguousarray(value, dtype=np.float32)
+            assert key.size == value.size == self.batch * self.kv_dim
+        pos = np.ascontiguousarray(positions, dtype=np.int64)
+        assert pos.size == self.batch
+        self.eng.check(self.L.flare_kv_write_step_rope_f32(self.h, layer, _ptr(key), _ptr(value),
+                                                           pos.ctypes.data_as(_i64p), int(on_device)))
+
+    def rope_rows(self, rows, num_heads, positions):
+        """Rotate [n_rows][num_heads][head_dim] in place (host ndarray, or a device pointer)."""
+        pos = np.ascontiguousarray(positions, dtype=np.int64)
+        on_device = not isinstance(rows, np.ndarray)
+        if not on_device:
+            assert rows.dtype == np.float32 and rows.flags["C_CONTIGUOUS"] and rows.size == pos.size * num_heads * self.head_dim
+        self.eng.check(self.L.flare_rope_rows_f32(self.h, _ptr(rows), pos.size, num_heads, pos.ctypes.data_as(_i64p),
+                                                  int(on_device)))
+        return rows
+
     def advance(self, seq=-1, n=1):
         self.eng.check(self.L.flare_kv_advance(self.h, seq, n))
 
@@ -477,3 +509,72 @@ class CudaBackend:
         """KvCache::advance for the context-owned cache (the Rust side calls flare_kv_advance on
         flare_backend_kv() where Model advances its CPU cache, flare-core/src/model.rs:2547)."""
         self.eng.check(self.L.flare_kv_advance(self.L.flare_backend_kv(self.eng.h), 0, n))
+
+
+# ---------------------------------------------------------------------------------------------
+# Speculative verify, the host-side loop (flare-core/src/generate.rs:244-306, 314-405).
+#
+# `model` is whatever runs the layers around attention for the caller; it provides
+#   num_layers, num_heads
+#   embed(tokens) -> x [n][d]              qkv(layer, x) -> (q [n][nh*hd], k [n][kv_dim], v [n][kv_dim])  (post-RoPE)
+#   post(layer, x, attn [n][nh*hd]) -> x   greedy(x) -> n token ids
+# The cache holds one sequence (the reference's Generator is single-sequence).
+# ---------------------------------------------------------------------------------------------
+def forward_token(eng: Engine, kv: KvCache, model, token: int) -> int:
+    """One decode step the way Model::forward orders it (flare-core/src/model.rs:2186-2247, 2547): per layer
+    write the token's K/V row at the current position, attend over length + 1 slots; then advance.  Returns the
+    greedy next token (forward_greedy)."""
+    pos = kv.len(0)
+    x = np.asarray(model.embed([token]), dtype=np.float32)
+    for layer in range(model.num_layers):
+        q, k, v = model.qkv(layer, x)
+        kv.write(layer, 0, pos, k[0], v[0])
+        attn = eng.decode(kv, layer, model.num_heads, np.ascontiguousarray(q, dtype=np.float32).reshape(1, 1, model.num_heads, kv.head_dim))
+        x = model.post(layer, x, attn.reshape(1, -1))
+    kv.advance(0, 1)
+    return int(model.greedy(x)[0])
+
+
+def verify_drafts_sequential(eng: Engine, kv: KvCache, model, last_token: int, drafts) -> list:
+    """The reference's loop as it stands (generate.rs:258-303): one full forward per draft token, accept while the
+    verified token equals the draft, accept the correcting token at the first mismatch and stop."""
+    accepted, last = [], last_token
+    for draft in drafts:
+        verified = forward_token(eng, kv, model, last)
+        accepted.append(verified)
+        last = verified
+        if verified != draft:
+            break
+    return accepted
+
+
+def verify_drafts(eng: Engine, kv: KvCache, model, last_token: int, drafts) -> list:
+    """The same verification with ONE attention call per layer: the K/V rows of all n forward inputs (the last
+    accepted token and the first n - 1 drafts) are written at the next n positions, a single n-query call attends
+    them causally (query i sees length + i + 1 slots), the matching prefix plus the correcting token is accepted
+    and the cache is rolled back to what the sequential loop would have kept (Model::truncate_kv_cache,
+    flare-core/src/model.rs:4835-4840)."""
+    drafts = list(drafts)
+    n = len(drafts)
+    if n == 0:
+        return []
+    base = kv.len(0)
+    if base + n > kv.max_seq_len:
+        raise ValueError("the drafts do not fit in the ring: verify them one by one")
+    x = np.asarray(model.embed([last_token] + drafts[:-1]), dtype=np.float32)
+    for layer in range(model.num_layers):
+        q, k, v = model.qkv(layer, x)
+        for i in range(n):
+            kv.write(layer, 0, base + i, k[i], v[i])
+        attn = eng.decode(kv, layer, model.num_heads,
+                          np.ascontiguousarray(q, dtype=np.float32).reshape(1, n, model.num_heads, kv.head_dim), n_q=n)
+        x = model.post(layer, x, attn.reshape(n, -1))
+    verified = [int(t) for t in model.greedy(x)]
+    accepted = []
+    for i in range(n):
+        accepted.append(verified[i])
+        if verified[i] != drafts[i]:
+            break
+    kv.advance(0, n)
+    kv.truncate(0, base + len(accepted))
+    return accepted

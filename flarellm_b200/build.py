@@ -33,7 +33,13 @@ def _stale(target, deps):
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
+def build(force: bool = False, verbose: bool = False, flags=(), suffix: str = "") -> str:
+    """flags / suffix: a variant of the library (extra nvcc flags, e.g. -DFLARE_DEBUG_BOUNDS) built beside the
+    product as libflare_attn<suffix>.so from its own object directory."""
+    global OBJ, SO
+    if suffix:
+        OBJ = os.path.join(HERE, "build" + suffix)
+        SO = os.path.join(HERE, "libflare_attn" + suffix + ".so")
     os.makedirs(OBJ, exist_ok=True)
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h", ".hpp"))]
     headers.append(os.path.join(os.path.dirname(HERE), "include", "flare_attn.h"))
@@ -44,7 +50,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         o = os.path.join(OBJ, src[:-3] + ".o")
         objs.append(o)
         if force or _stale(o, [s] + headers):
-            cmd = [NVCC, *ARCH, *CFLAGS, "-c", s, "-o", o]
+            cmd = [NVCC, *ARCH, *CFLAGS, *flags, "-c", s, "-o", o]
             if verbose:
                 cmd.insert(1, "-Xptxas=-v")
             jobs.append(cmd)
@@ -64,4 +70,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    # python -m flarellm_b200.build [--force] [-v] [--variant SUFFIX -DFLAG ...]
+    argv = sys.argv[1:]
+    suffix = argv[argv.index("--variant") + 1] if "--variant" in argv else ""
+    print(build(force="--force" in argv, verbose="-v" in argv, flags=[a for a in argv if a.startswith("-D")], suffix=suffix))

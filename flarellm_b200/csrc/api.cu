@@ -56,14 +56,15 @@ int flare_launch_decode(flare_attn_ctx* ctx, const DecodeArgs& a) {
     return flare_launch_decode_generic(ctx, a);
 }
 
-// A kernel whose bounded wait gave up leaves a status in ctx->d_err; read and clear it.
+// A kernel whose bounded wait gave up leaves a status in the context's status word (mapped host memory);
+// wait for the stream, read and clear it.
 int flare_check_device_error(flare_attn_ctx* ctx) {
-    FLARE_CUDA_OK(ctx, cudaMemcpyAsync(ctx->h_err, ctx->d_err, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
     FLARE_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
-    const int h = *ctx->h_err;
+    const int h = *reinterpret_cast<volatile int*>(ctx->h_err);
     if (h != 0) {
-        FLARE_CUDA_OK(ctx, cudaMemsetAsync(ctx->d_err, 0, sizeof(int), ctx->stream));
-        return flare_set_error(ctx, h, "a kernel gave up waiting for its own memory copies (status %d)", h);
+        *reinterpret_cast<volatile int*>(ctx->h_err) = 0;      // nothing is running on the stream
+        return flare_set_error(ctx, h, h == FLARE_ERR_TIMEOUT ? "a kernel gave up waiting (for its own memory copies, or for a peer rank's records): status %d"
+                                                              : "a kernel reported status %d", h);
     }
     return FLARE_OK;
 }
@@ -74,7 +75,7 @@ __global__ void selftest_wait_kernel(int* err, uint32_t limit) {
     if (threadIdx.x == 0) {
         ptx::mbar_init(&bar, 1);
         ptx::fence_barrier_init();
-        if (!ptx::mbar_wait(&bar, 0, limit)) atomicExch(err, FLARE_ERR_TIMEOUT);
+        if (!ptx::mbar_wait(&bar, 0, limit)) flare_report(err, FLARE_ERR_TIMEOUT);
     }
 }
 
@@ -125,6 +126,15 @@ static double kv_bytes_of(const flare_kv* kv, double slots) {
     }
 }
 
+// The device's address of a page-locked host buffer, or null when the buffer is pageable.
+static const float* device_view_of_host(const void* p) {
+    cudaPointerAttributes pa;
+    if (cudaPointerGetAttributes(&pa, p) == cudaSuccess && pa.type == cudaMemoryTypeHost && pa.devicePointer)
+        return (const float*)pa.devicePointer;
+    cudaGetLastError();
+    return nullptr;
+}
+
 #define CHECK_CTX(ctx) do { if (!(ctx)) return FLARE_ERR_INVALID_ARG; } while (0)
 #define BIND(ctx) FLARE_CUDA_OK(ctx, cudaSetDevice((ctx)->device))
 
@@ -145,13 +155,15 @@ int flare_attn_create(int device, flare_attn_ctx** out_ctx) {
         return FLARE_ERR_CUDA;
     }
     ctx->stream = ctx->own_stream;
-    if (cudaMalloc(&ctx->d_err, sizeof(int)) != cudaSuccess || cudaMemset(ctx->d_err, 0, sizeof(int)) != cudaSuccess ||
-        cudaMallocHost(&ctx->h_err, sizeof(int)) != cudaSuccess) {
+    if (cudaHostAlloc((void**)&ctx->h_err, 64, cudaHostAllocMapped) != cudaSuccess ||
+        cudaHostGetDevicePointer((void**)&ctx->d_err, ctx->h_err, 0) != cudaSuccess) {
+        if (ctx->h_err) cudaFreeHost(ctx->h_err);
         cudaStreamDestroy(ctx->own_stream);
         delete ctx;
         return FLARE_ERR_CUDA;
     }
     cudaDeviceGetAttribute(&ctx->sm_count, cudaDevAttrMultiProcessorCount, device);
+    *ctx->h_err = 0;
     *out_ctx = ctx;
     return FLARE_OK;
 }
@@ -162,7 +174,6 @@ int flare_attn_destroy(flare_attn_ctx* ctx) {
     cudaStreamSynchronize(ctx->stream);
     if (ctx->backend_kv) flare_kv_free(ctx->backend_kv);
     flare_comm_free(ctx);
-    cudaFree(ctx->d_err);
     if (ctx->h_err) cudaFreeHost(ctx->h_err);
     cudaFree(ctx->d_misc2); cudaFree(ctx->d_conv);
     cudaFree(ctx->d_work); cudaFree(ctx->d_stage_in); cudaFree(ctx->d_stage_out); cudaFree(ctx->d_misc);
@@ -337,6 +348,7 @@ int flare_kv_free(flare_kv* kv) {
     cudaSetDevice(kv->ctx->device);
     cudaStreamSynchronize(kv->ctx->stream);
     for (int i = 0; i < FLARE_PLANE_COUNT; i++) if (kv->plane[i]) cudaFree(kv->plane[i]);
+    cudaFree(kv->rope_cos); cudaFree(kv->rope_sin);
     if (kv->ctx->backend_kv == kv) kv->ctx->backend_kv = nullptr;
     delete kv;
     return FLARE_OK;
@@ -437,6 +449,87 @@ int flare_kv_write_step_f32(flare_kv* kv, int layer, const float* key, const flo
     FLARE_TRY(stage_rows(ctx, key, value, (size_t)kv->batch * kv->kv_dim, on_device, &dk, &dv, &must_sync));
     FLARE_TRY(flare_launch_kv_write_step(kv, layer, d_ring, dk, dv));
     if (must_sync) FLARE_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
+    return FLARE_OK;
+}
+
+int flare_kv_set_rope_table(flare_kv* kv, const float* cos, const float* sin, int table_len) {
+    if (!kv) return FLARE_ERR_INVALID_ARG;
+    flare_attn_ctx* ctx = kv->ctx;
+    if (!cos || !sin || table_len < 1 || kv->head_dim % 2)
+        return flare_set_error(ctx, FLARE_ERR_INVALID_ARG, "flare_kv_set_rope_table: null table, no rows, or an odd head_dim");
+    BIND(ctx);
+    FLARE_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
+    cudaFree(kv->rope_cos); cudaFree(kv->rope_sin);
+    kv->rope_cos = kv->rope_sin = nullptr; kv->rope_len = 0;
+    const size_t bytes = (size_t)table_len * (kv->head_dim / 2) * sizeof(float);
+    FLARE_CUDA_OK(ctx, cudaMalloc(&kv->rope_cos, bytes));
+    FLARE_CUDA_OK(ctx, cudaMalloc(&kv->rope_sin, bytes));
+    FLARE_CUDA_OK(ctx, cudaMemcpyAsync(kv->rope_cos, cos, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    FLARE_CUDA_OK(ctx, cudaMemcpyAsync(kv->rope_sin, sin, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    FLARE_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
+    kv->rope_len = table_len;
+    return FLARE_OK;
+}
+
+// positions of a step on the device (checked against the table on the host first)
+static int upload_positions(flare_kv* kv, const int64_t* positions, int n, const long long** d_pos) {
+    flare_attn_ctx* ctx = kv->ctx;
+    if (!kv->rope_cos) return flare_set_error(ctx, FLARE_ERR_STATE, "no rotary table: call flare_kv_set_rope_table first");
+    if (!positions) return flare_set_error(ctx, FLARE_ERR_INVALID_ARG, "positions is null");
+    for (int i = 0; i < n; i++)
+        if (positions[i] < 0 || positions[i] >= kv->rope_len)
+            return flare_set_error(ctx, FLARE_ERR_INVALID_ARG, "positions[%d] = %lld is outside the rotary table of %d rows", i,
+                                   (long long)positions[i], kv->rope_len);
+    FLARE_TRY(flare_ensure(ctx, &ctx->d_misc2, &ctx->misc2_bytes, (size_t)n * sizeof(long long)));
+    // pageable source: the runtime has taken its own copy by the time this returns
+    FLARE_CUDA_OK(ctx, cudaMemcpyAsync(ctx->d_misc2, positions, (size_t)n * sizeof(long long), cudaMemcpyHostToDevice, ctx->stream));
+    ctx->last_launch_overlappable = false;
+    *d_pos = (const long long*)ctx->d_misc2;
+    return FLARE_OK;
+}
+
+int flare_kv_write_step_rope_f32(flare_kv* kv, int layer, const float* key, const float* value, const int64_t* positions,
+                                 int on_device) {
+    FLARE_TRY(check_layer_seq(kv, layer, 0));
+    flare_attn_ctx* ctx = kv->ctx;
+    if (!key || !value) return flare_set_error(ctx, FLARE_ERR_INVALID_ARG, "flare_kv_write_step_rope_f32: null rows");
+    BIND(ctx);
+    const long long* d_pos = nullptr;
+    FLARE_TRY(upload_positions(kv, positions, kv->batch, &d_pos));
+    const int* d_att; const int2* d_ring; int mx;
+    FLARE_TRY(upload_small(ctx, kv, 1, nullptr, &d_att, &d_ring, &mx));
+    const float *dk, *dv;
+    bool must_sync;
+    FLARE_TRY(stage_rows(ctx, key, value, (size_t)kv->batch * kv->kv_dim, on_device, &dk, &dv, &must_sync));
+    if (kv->dtype == FLARE_KV_KIVI_REF || kv->dtype == FLARE_KV_KIVI_G32) {
+        // the 2-bit caches take one sequence at a time through the general row writer: rotate a copy of the rows first
+        const size_t bytes = (size_t)kv->batch * kv->kv_dim * sizeof(float);
+        FLARE_TRY(flare_ensure(ctx, &ctx->d_conv, &ctx->conv_bytes, bytes));
+        FLARE_CUDA_OK(ctx, cudaMemcpyAsync(ctx->d_conv, dk, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+        FLARE_TRY(flare_launch_rope_rows(kv, (float*)ctx->d_conv, kv->batch, kv->num_kv_heads, d_pos));
+        FLARE_TRY(flare_launch_kv_write_step(kv, layer, d_ring, (const float*)ctx->d_conv, dv));
+    } else {
+        FLARE_TRY(flare_launch_kv_write_step(kv, layer, d_ring, dk, dv, d_pos));
+    }
+    if (must_sync) FLARE_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
+    return FLARE_OK;
+}
+
+int flare_rope_rows_f32(flare_kv* kv, float* rows, int n_rows, int num_heads, const int64_t* positions, int on_device) {
+    if (!kv) return FLARE_ERR_INVALID_ARG;
+    flare_attn_ctx* ctx = kv->ctx;
+    if (!rows || n_rows < 0 || num_heads < 1) return flare_set_error(ctx, FLARE_ERR_INVALID_ARG, "flare_rope_rows_f32: bad argument");
+    if (n_rows == 0) return FLARE_OK;
+    BIND(ctx);
+    const long long* d_pos = nullptr;
+    FLARE_TRY(upload_positions(kv, positions, n_rows, &d_pos));
+    if (on_device) return flare_launch_rope_rows(kv, rows, n_rows, num_heads, d_pos);
+    const size_t bytes = (size_t)n_rows * num_heads * kv->head_dim * sizeof(float);
+    FLARE_TRY(flare_ensure(ctx, &ctx->d_stage_in, &ctx->stage_in_bytes, bytes));
+    FLARE_CUDA_OK(ctx, cudaMemcpyAsync(ctx->d_stage_in, rows, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    FLARE_TRY(flare_launch_rope_rows(kv, (float*)ctx->d_stage_in, n_rows, num_heads, d_pos));
+    FLARE_CUDA_OK(ctx, cudaMemcpyAsync(rows, ctx->d_stage_in, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    FLARE_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
     return FLARE_OK;
 }
 
@@ -673,6 +766,7 @@ int flare_decode_common(flare_attn_ctx* ctx, flare_kv* kv, int layer, int num_he
     if (on_device) { a.q = q; a.out = out; }
     else {
         if (q_staged) a.q = q_staged;
+        else if (const float* qv = device_view_of_host(q)) a.q = qv;       // page-locked: the kernel reads it over the bus
         else {
             FLARE_TRY(flare_ensure(ctx, &ctx->d_stage_in, &ctx->stage_in_bytes, q_bytes));
             FLARE_CUDA_OK(ctx, cudaMemcpyAsync(ctx->d_stage_in, q, q_bytes, cudaMemcpyHostToDevice, ctx->stream));
@@ -718,12 +812,6 @@ int flare_decode_attn(flare_attn_ctx* ctx, flare_kv* kv, int layer, int num_head
     return flare_decode_common(ctx, kv, layer, num_heads, q, n_q, attend_len, softcap, 0, -1, 0, 1, out, on_device);
 }
 
-static bool is_page_locked(const void* p) {
-    cudaPointerAttributes pa;
-    if (cudaPointerGetAttributes(&pa, p) == cudaSuccess && pa.type == cudaMemoryTypeHost) return true;
-    cudaGetLastError();
-    return false;
-}
 
 int flare_decode_step(flare_attn_ctx* ctx, flare_kv* kv, int layer, int num_heads, const float* key, const float* value,
                       const float* q, float* out, int on_device) {
@@ -742,39 +830,41 @@ int flare_decode_step(flare_attn_ctx* ctx, flare_kv* kv, int layer, int num_head
     }
     const size_t row_fl = (size_t)kv->batch * kv->kv_dim, q_fl = (size_t)kv->batch * num_heads * kv->head_dim;
     const size_t bytes = (2 * row_fl + q_fl) * sizeof(float);
-    FLARE_TRY(flare_ensure(ctx, &ctx->d_stage_in, &ctx->stage_in_bytes, bytes));
-    float* d = (float*)ctx->d_stage_in;
-    const size_t slot_bytes = 1u << 20;
-    if (is_page_locked(key) && is_page_locked(value) && is_page_locked(q)) {
-        // the caller's buffers can be read by the copy engine as they are
-        FLARE_CUDA_OK(ctx, cudaMemcpyAsync(d, key, row_fl * 4, cudaMemcpyHostToDevice, ctx->stream));
-        FLARE_CUDA_OK(ctx, cudaMemcpyAsync(d + row_fl, value, row_fl * 4, cudaMemcpyHostToDevice, ctx->stream));
-        FLARE_CUDA_OK(ctx, cudaMemcpyAsync(d + 2 * row_fl, q, q_fl * 4, cudaMemcpyHostToDevice, ctx->stream));
-    } else if (bytes <= slot_bytes) {
-        // pageable and small: pack the three inputs into one page-locked slot, one transfer
-        if (!ctx->h_rows) {
-            FLARE_CUDA_OK(ctx, cudaMallocHost(&ctx->h_rows, slot_bytes * FLARE_ROW_SLOTS));
-            ctx->rows_slot_bytes = slot_bytes;
-        }
-        const int slot = (int)(ctx->rows_counter++ % FLARE_ROW_SLOTS);
-        if (!ctx->rows_events[slot]) FLARE_CUDA_OK(ctx, cudaEventCreateWithFlags(&ctx->rows_events[slot], cudaEventDisableTiming));
-        else FLARE_CUDA_OK(ctx, cudaEventSynchronize(ctx->rows_events[slot]));
-        float* h = (float*)((char*)ctx->h_rows + (size_t)slot * slot_bytes);
-        memcpy(h, key, row_fl * 4);
-        memcpy(h + row_fl, value, row_fl * 4);
-        memcpy(h + 2 * row_fl, q, q_fl * 4);
-        FLARE_CUDA_OK(ctx, cudaMemcpyAsync(d, h, bytes, cudaMemcpyHostToDevice, ctx->stream));
-        FLARE_CUDA_OK(ctx, cudaEventRecord(ctx->rows_events[slot], ctx->stream));
+    const float *dk = device_view_of_host(key), *dv = device_view_of_host(value), *dq = device_view_of_host(q);
+    if (dk && dv && dq) {
+        // Page-locked inputs: the kernels read them where they are, over the bus, each element once (the store
+        // kernel the K/V rows, the attention kernel q) — no copy to queue, nothing to stage.
     } else {
-        // pageable and large: the call synchronises before it returns, so the buffers stay valid long enough
-        FLARE_CUDA_OK(ctx, cudaMemcpyAsync(d, key, row_fl * 4, cudaMemcpyHostToDevice, ctx->stream));
-        FLARE_CUDA_OK(ctx, cudaMemcpyAsync(d + row_fl, value, row_fl * 4, cudaMemcpyHostToDevice, ctx->stream));
-        FLARE_CUDA_OK(ctx, cudaMemcpyAsync(d + 2 * row_fl, q, q_fl * 4, cudaMemcpyHostToDevice, ctx->stream));
+        FLARE_TRY(flare_ensure(ctx, &ctx->d_stage_in, &ctx->stage_in_bytes, bytes));
+        float* d = (float*)ctx->d_stage_in;
+        const size_t slot_bytes = 1u << 20;
+        if (bytes <= slot_bytes) {
+            // pageable and small: pack the three inputs into one page-locked slot, one transfer
+            if (!ctx->h_rows) {
+                FLARE_CUDA_OK(ctx, cudaMallocHost(&ctx->h_rows, slot_bytes * FLARE_ROW_SLOTS));
+                ctx->rows_slot_bytes = slot_bytes;
+            }
+            const int slot = (int)(ctx->rows_counter++ % FLARE_ROW_SLOTS);
+            if (!ctx->rows_events[slot]) FLARE_CUDA_OK(ctx, cudaEventCreateWithFlags(&ctx->rows_events[slot], cudaEventDisableTiming));
+            else FLARE_CUDA_OK(ctx, cudaEventSynchronize(ctx->rows_events[slot]));
+            float* h = (float*)((char*)ctx->h_rows + (size_t)slot * slot_bytes);
+            memcpy(h, key, row_fl * 4);
+            memcpy(h + row_fl, value, row_fl * 4);
+            memcpy(h + 2 * row_fl, q, q_fl * 4);
+            FLARE_CUDA_OK(ctx, cudaMemcpyAsync(d, h, bytes, cudaMemcpyHostToDevice, ctx->stream));
+            FLARE_CUDA_OK(ctx, cudaEventRecord(ctx->rows_events[slot], ctx->stream));
+        } else {
+            // pageable and large: the call synchronises before it returns, so the buffers stay valid long enough
+            FLARE_CUDA_OK(ctx, cudaMemcpyAsync(d, key, row_fl * 4, cudaMemcpyHostToDevice, ctx->stream));
+            FLARE_CUDA_OK(ctx, cudaMemcpyAsync(d + row_fl, value, row_fl * 4, cudaMemcpyHostToDevice, ctx->stream));
+            FLARE_CUDA_OK(ctx, cudaMemcpyAsync(d + 2 * row_fl, q, q_fl * 4, cudaMemcpyHostToDevice, ctx->stream));
+        }
+        dk = d; dv = d + row_fl; dq = d + 2 * row_fl;
     }
     ctx->last_launch_overlappable = false;
-    FLARE_TRY(flare_launch_kv_write_step(kv, layer, d_ring, d, d + row_fl));
-    // attention on the staged q; the output goes to the caller's host buffer; one synchronisation at the end
-    return flare_decode_common(ctx, kv, layer, num_heads, q, 1, nullptr, 0.0f, 0, -1, 0, 1, out, 0, d + 2 * row_fl);
+    FLARE_TRY(flare_launch_kv_write_step(kv, layer, d_ring, dk, dv));
+    // attention on q where it is; the output goes to the caller's host buffer; one synchronisation at the end
+    return flare_decode_common(ctx, kv, layer, num_heads, q, 1, nullptr, 0.0f, 0, -1, 0, 1, out, 0, dq);
 }
 
 int flare_decode_attn_noalloc(flare_attn_ctx* ctx, flare_kv* kv, int layer, int num_heads, const float* q_dev, int n_q,

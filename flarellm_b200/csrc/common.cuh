@@ -53,8 +53,8 @@ struct flare_attn_ctx {
     // true while the last kernel put on the stream is one that never writes a cache or q, so that the
     // next decode kernel may overlap its prologue with it (programmatic dependent launch)
     bool last_launch_overlappable = false;
-    int* d_err = nullptr;            // device word a kernel sets when a bounded wait gives up
-    int* h_err = nullptr;            // page-locked host copy, so that reading it back costs no synchronous staging
+    int* h_err = nullptr;            // status word in page-locked, device-mapped host memory: a kernel whose bounded wait gives up stores a code here
+    int* d_err = nullptr;            // the device's address of the same word (what kernels are given)
     int sm_count = 148;
     flare_kv* backend_kv = nullptr;  // cache created by flare_backend_init_gpu_kv_cache
     FlareComm* comm = nullptr;       // set by flare_attn_comm_init
@@ -81,6 +81,10 @@ struct flare_kv {
     // TMA maps of the group-32 KIVI code planes: (16 bytes = 64 codes of one head, slot, kv head, layer*batch + seq)
     CUtensorMap g32_kmap, g32_vmap;
     bool has_g32_maps = false;
+    // rotary table of the caller (RopeTable, flare-core/src/model.rs:7184-7213): cos and sin, [rope_len][head_dim / 2]
+    float* rope_cos = nullptr;
+    float* rope_sin = nullptr;
+    int rope_len = 0;
     inline char* plane_ptr(int p, int layer, int seq) const {
         return (char*)plane[p] + ((size_t)layer * batch + seq) * plane_bytes[p];
     }
@@ -166,6 +170,11 @@ void flare_comm_free(flare_attn_ctx* ctx);
 // Called by the decode path after its kernels when the call is a multi-GPU one: exchanges this rank's records
 // with the other ranks and writes the merged attention output.
 int flare_multi_tail(flare_attn_ctx* ctx, const float* work, int n_split, int rows, int head_dim, float* out);
+// Log-sum-exp merge of per-row slot-range records [row][n_split][head_dim + 2] (maximum in log2 units, n_split <= 256,
+// head_dim a multiple of 32) into the attention output [row][head_dim], or (want_partial) into one record per row
+// with the maximum in natural units.  Launched with programmatic stream serialisation: it waits for its predecessor.
+int flare_launch_merge_splits(flare_attn_ctx* ctx, const float* work, int n_split, int rows, int head_dim, float* out,
+                              int want_partial);
 extern "C" int flare_decode_common(flare_attn_ctx* ctx, flare_kv* kv, int layer, int num_heads, const float* q, int n_q,
                         const int* attend_len, float softcap, int slot_begin, int slot_end, int want_partial,
                         int causal_q, float* out, int on_device, const float* q_staged = nullptr, int multi = 0);
@@ -182,7 +191,11 @@ int flare_launch_prefill_pp(flare_attn_ctx* ctx, const CUtensorMap& qm, const CU
 
 int flare_launch_kv_write(flare_kv* kv, int layer, int seq, int64_t first_abs_position, int64_t length_before,
                           int n_rows, const float* d_key, const float* d_value);
-int flare_launch_kv_write_step(flare_kv* kv, int layer, const int2* d_ring, const float* d_key, const float* d_value);
+// d_positions (with the cache's rotary table): the key rows are rotated for these absolute positions on their way
+// into the cache; null = stored as given
+int flare_launch_kv_write_step(flare_kv* kv, int layer, const int2* d_ring, const float* d_key, const float* d_value,
+                               const long long* d_positions = nullptr);
+int flare_launch_rope_rows(flare_kv* kv, float* d_rows, int n_rows, int num_heads, const long long* d_positions);
 int flare_launch_kv_export_dequant(flare_kv* kv, int layer, int seq, float* d_k, float* d_v);
 int flare_launch_q8_blocks(flare_kv* kv, int layer, int seq, int first_slot, int n_slots, void* d_kb, void* d_vb,
                            int to_blocks);
@@ -196,6 +209,12 @@ __device__ __forceinline__ float q2_code(const uint8_t* packed, int i) {
 // code * scale + min as a separate multiply and add, never fused.
 __device__ __forceinline__ float q2_dequant(float code, float scale, float mn) {
     return __fadd_rn(__fmul_rn(code, scale), mn);
+}
+// A kernel reports a status (FLARE_ERR_TIMEOUT ...) by storing it into the context's status word, which lives in
+// page-locked host memory mapped into the device: the host reads it after synchronising, with no copy.  A plain
+// store: the word only ever goes from 0 to a code, and every writer writes the same kind of code.
+__device__ __forceinline__ void flare_report(int* status_word, int code) {
+    *reinterpret_cast<volatile int*>(status_word) = code;
 }
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;

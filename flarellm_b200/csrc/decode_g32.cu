@@ -12,14 +12,17 @@
 // Dequantisation never happens per element, and both products run "transposed" so that the codes are
 // the 16-row A operand and the 8 columns carry the (at most 4) query heads.  With c the 2-bit code:
 //   scores  S[t, h] = sum_ch c[t,ch] (q s)[ch,h]  +  sum_ch z[ch] q[ch,h]
-//           A = codes of 16 slots (exact f16 after one mask-or and one fma per pair; lane tig works on
-//           word tig of a slot's 16 code bytes, i.e. channels 16 tig .. 16 tig + 15),
+//           A = codes of 16 slots, used as they are: a code masked out at bit 2k of a 16-bit half IS the f16
+//           subnormal c 4^k 2^-24 (one AND per pair of codes, nothing else), the factor 4^-k goes into B and 2^24
+//           into the f32 result; lane tig works on word tig of a slot's 16 code bytes, i.e. channels
+//           16 tig .. 16 tig + 15,
 //           B = q*s rebuilt per key group with packed f16 arithmetic as an exact hi + lo pair
 //           (column 2h = hi, 2h+1 = lo; q is pre-scaled by a power of two so q*s cannot overflow);
 //           the zero-point term is one more MMA whose A holds z in row 0 and whose B is q itself.
 //   output  O[ch, (h, blk)] = sum_t c[t,ch] (p[t,h] s_v[t,blk])  +  sum_t p[t,h] z_v[t,blk]
-//           A = V codes transposed by ldmatrix.trans (16-bit units hold 8 codes of a slot) and made exact
-//           f16 the same way, B = the f16 weights p*s_v moved into operand layout by movmatrix; column
+//           A = V codes transposed by ldmatrix.trans (16-bit units hold 8 codes of a slot), masked the same
+//           way (here 4^k 2^-24 is a factor of the output ROW and is removed once, at the end),
+//           B = the f16 weights p*s_v moved into operand layout by movmatrix; column
 //           2h+blk serves channel block blk; the zero-point term is one f32 scalar per (head, block).
 #include "common.cuh"
 #include "tma.cuh"
@@ -33,7 +36,6 @@ constexpr int NG = T / 32;
 constexpr int STAGES = FLARE_G32_TILE == 64 ? 3 : 4;
 constexpr int HD = 64;
 constexpr float kLog2e = 1.4426950408889634f;
-constexpr uint32_t kMagic = 0x64006400u;      // half2 (1024, 1024): a code OR-ed into the mantissa is 1024 + code * 2^bit
 
 struct G32Params {
     const float* q;
@@ -48,9 +50,7 @@ struct G32Params {
     const int2* ring;
     int layer_seq0, num_heads, nkv, G, n_split;
     int* err;
-    // 0x64006400 and 0x00030003, passed as arguments so that they live in registers: a logic instruction takes
-    // one immediate only, and with both known at compile time every mask-or would become two instructions
-    uint32_t magic, mask3;
+    uint32_t mask3;         // 0x00030003: a 2-bit code at bit 0 of both 16-bit halves
 };
 
 __device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -84,23 +84,16 @@ __device__ __forceinline__ uint32_t hmul2(uint32_t a, uint32_t b) {
 __device__ __forceinline__ uint32_t hfma2(uint32_t a, uint32_t b, uint32_t c) {
     uint32_t d; asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c)); return d;
 }
-// (a & b) | c in one logic instruction
-__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
-    uint32_t d; asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c)); return d;
-}
 __device__ __forceinline__ uint32_t hneg2(uint32_t a) {
     uint32_t d; asm("neg.f16x2 %0, %1;" : "=r"(d) : "r"(a)); return d;
 }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-// A 2-bit code c masked out at bit 2k of an f16 mantissa and OR-ed with 0x6400 reads 1024 + 4^k c;
-// fma(x, code_mul(k), code_sub(k)) = x / 4^k - 1024 / 4^k = c exactly (half2 constants, k = 0..4).
+// half2 (4^-k, 4^-k), k = 0..4: the factor that a code masked out at bit 2k of a 16-bit half carries too much
+// (the half then reads as the f16 subnormal code * 4^k * 2^-24).
 __device__ __forceinline__ constexpr uint32_t code_mul(int k) {
     return k == 0 ? 0x3c003c00u : k == 1 ? 0x34003400u : k == 2 ? 0x2c002c00u : k == 3 ? 0x24002400u : 0x1c001c00u;
-}
-__device__ __forceinline__ constexpr uint32_t code_sub(int k) {
-    return k == 0 ? 0xe400e400u : k == 1 ? 0xdc00dc00u : k == 2 ? 0xd400d400u : k == 3 ? 0xcc00cc00u : 0xc400c400u;
 }
 
 // Scratch of one warp for its share of the newest tokens, kept until the end of the kernel.
@@ -327,7 +320,7 @@ __global__ void __launch_bounds__(256, 2) decode_g32_kernel(const __grid_constan
     const int hB = g >> 1;
     const bool lo_col = g & 1;
     uint32_t qx[4][2], qhz[4][2];          // qx: this column's part of q (hi or lo); qhz: hi part in lo columns, else 0
-    float unscale;                         // 2^e that undoes the power-of-two pre-scaling of head `tig`
+    float unscale, unscale24;              // 2^e that undoes the power-of-two pre-scaling of head `tig`; 2^(e + 24)
     {
         const bool ok = hB < p.G;
         const float* qrow = p.q + ((size_t)b * p.num_heads + kvh * p.G + (ok ? hB : 0)) * HD + 16 * tig;
@@ -346,6 +339,7 @@ __global__ void __launch_bounds__(256, 2) decode_g32_kernel(const __grid_constan
         const float down = exp2f((float)-e);
         const float up = exp2f((float)e);
         unscale = __shfl_sync(0xffffffffu, up, 8 * tig);          // lane with g = 2 tig holds head tig
+        unscale24 = unscale * 16777216.0f;                        // and the 2^24 of the subnormal codes
 #pragma unroll
         for (int ks = 0; ks < 4; ks++)
 #pragma unroll
@@ -358,7 +352,6 @@ __global__ void __launch_bounds__(256, 2) decode_g32_kernel(const __grid_constan
                 qhz[ks][bb] = lo_col ? h : 0u;
             }
     }
-    const uint32_t magic = p.magic;
     uint32_t cmask[5];                                             // a code at bit 0, 2, 4, 6, 8 of both halves
 #pragma unroll
     for (int k = 0; k < 5; k++) cmask[k] = p.mask3 << (2 * k);
@@ -397,7 +390,8 @@ __global__ void __launch_bounds__(256, 2) decode_g32_kernel(const __grid_constan
                 for (int ks = 0; ks < 4; ks++) {
 #pragma unroll
                     for (int bb = 0; bb < 2; bb++) {
-                        const uint32_t sv = s2[ks + 4 * bb];
+                        // the scale of the pair, times the 4^-ks that the masked codes of k-step ks carry too much
+                        const uint32_t sv = ks == 0 ? s2[4 * bb] : hmul2(s2[ks + 4 * bb], code_mul(ks));
                         const uint32_t ph = hmul2(qhz[ks][bb], sv);                  // lo columns: rounded hi product
                         const uint32_t er = hfma2(qhz[ks][bb], sv, hneg2(ph));       //             its exact rounding error
                         bq[ks][bb] = hfma2(qx[ks][bb], sv, er);                      // hi columns: round(q_hi s); lo: q_lo s + error
@@ -405,7 +399,7 @@ __global__ void __launch_bounds__(256, 2) decode_g32_kernel(const __grid_constan
                     mma_f16(dz, z2[ks], 0u, z2[ks + 4], 0u, qx[ks][0], qx[ks][1]);
                 }
             }
-            const float zd = __shfl_sync(0xffffffffu, dz[0] + dz[1], tig);           // row 0 lives in lanes g = 0
+            const float zdu = __shfl_sync(0xffffffffu, dz[0] + dz[1], tig) * unscale;   // row 0 lives in lanes g = 0
 
             // ---- scores of slots 32 gi + 16 mt + g and + 8 for head tig -----------------------------------
 #pragma unroll
@@ -416,16 +410,11 @@ __global__ void __launch_bounds__(256, 2) decode_g32_kernel(const __grid_constan
                 float d[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
                 for (int ks = 0; ks < 4; ks++) {
-                    // a code at bit 2 ks of a half becomes 1024 + 4^ks code; one fma scales and removes the bias exactly
-                    const uint32_t mul = code_mul(ks), sub = code_sub(ks);
-                    const uint32_t a0 = hfma2(and_or(wa, cmask[ks], magic), mul, sub);
-                    const uint32_t a1 = hfma2(and_or(wb, cmask[ks], magic), mul, sub);
-                    const uint32_t a2 = hfma2(and_or(wa8, cmask[ks], magic), mul, sub);
-                    const uint32_t a3 = hfma2(and_or(wb8, cmask[ks], magic), mul, sub);
-                    mma_f16(d, a0, a1, a2, a3, bq[ks][0], bq[ks][1]);
+                    // a code at bit 2 ks of a half, alone in the word, reads as the subnormal code * 4^ks * 2^-24
+                    mma_f16(d, wa & cmask[ks], wb & cmask[ks], wa8 & cmask[ks], wb8 & cmask[ks], bq[ks][0], bq[ks][1]);
                 }
-                sc[4 * gi + 2 * mt] = (d[0] + d[1] + zd) * unscale;
-                sc[4 * gi + 2 * mt + 1] = (d[2] + d[3] + zd) * unscale;
+                sc[4 * gi + 2 * mt] = fmaf(d[0] + d[1], unscale24, zdu);
+                sc[4 * gi + 2 * mt + 1] = fmaf(d[2] + d[3], unscale24, zdu);
             }
         }
         float tmax = sc[0];
@@ -471,10 +460,10 @@ __global__ void __launch_bounds__(256, 2) decode_g32_kernel(const __grid_constan
                     // channel 8g + c: its code sits at bit 2c of the 16-bit unit, or at bit 2c - 6 after the shift
                     const int c0 = 2 * j, c1 = 2 * j + 1;
                     const int k0 = c0 <= 4 ? c0 : c0 - 3, k1 = c1 <= 4 ? c1 : c1 - 3;
-                    const uint32_t a0 = hfma2(and_or(c0 <= 4 ? r0 : r0s, cmask[k0], magic), code_mul(k0), code_sub(k0));
-                    const uint32_t a1 = hfma2(and_or(c1 <= 4 ? r0 : r0s, cmask[k1], magic), code_mul(k1), code_sub(k1));
-                    const uint32_t a2 = hfma2(and_or(c0 <= 4 ? r1 : r1s, cmask[k0], magic), code_mul(k0), code_sub(k0));
-                    const uint32_t a3 = hfma2(and_or(c1 <= 4 ? r1 : r1s, cmask[k1], magic), code_mul(k1), code_sub(k1));
+                    const uint32_t a0 = (c0 <= 4 ? r0 : r0s) & cmask[k0];
+                    const uint32_t a1 = (c1 <= 4 ? r0 : r0s) & cmask[k1];
+                    const uint32_t a2 = (c0 <= 4 ? r1 : r1s) & cmask[k0];
+                    const uint32_t a3 = (c1 <= 4 ? r1 : r1s) & cmask[k1];
                     mma_f16(acc[j], a0, a1, a2, a3, b0, b1);
                 }
             }
@@ -491,7 +480,7 @@ __global__ void __launch_bounds__(256, 2) decode_g32_kernel(const __grid_constan
     }
     pdl_trigger();
     if (failed) {
-        if (lane == 0) atomicExch(p.err, FLARE_ERR_TIMEOUT);
+        if (lane == 0) flare_report(p.err, FLARE_ERR_TIMEOUT);
         return;
     }
 #pragma unroll
@@ -508,8 +497,11 @@ __global__ void __launch_bounds__(256, 2) decode_g32_kernel(const __grid_constan
     float o8[8];
 #pragma unroll
     for (int j = 0; j < 4; j++) {
-        o8[2 * j] = (blk ? acc[j][1] : acc[j][0]) + zp;
-        o8[2 * j + 1] = (blk ? acc[j][3] : acc[j][2]) + zp;
+        // rows g / g + 8 of m-tile j used the codes at position k0 / k1: remove 4^k 2^-24
+        const int c0 = 2 * j, c1 = 2 * j + 1;
+        const int k0 = c0 <= 4 ? c0 : c0 - 3, k1 = c1 <= 4 ? c1 : c1 - 3;
+        o8[2 * j] = fmaf(blk ? acc[j][1] : acc[j][0], 16777216.0f / (float)(1 << (2 * k0)), zp);
+        o8[2 * j + 1] = fmaf(blk ? acc[j][3] : acc[j][2], 16777216.0f / (float)(1 << (2 * k1)), zp);
     }
 #pragma unroll
     for (int k = 0; k < 8; k++) wrec[2 + 8 * g + k] = o8[k];
@@ -568,7 +560,7 @@ int flare_launch_decode_g32(flare_attn_ctx* ctx, const DecodeArgs& a, const flar
     p.layer_seq0 = a.layer * a.batch;
     p.num_heads = a.num_heads; p.nkv = nkv; p.G = a.num_heads / nkv;
     p.err = ctx->d_err;
-    p.magic = kMagic; p.mask3 = 0x00030003u;
+    p.mask3 = 0x00030003u;
     const size_t stage = 2 * (size_t)nkv * T * 16 + (size_t)NG * nkv * HD * 4 + (size_t)T * nkv * 2 * 4;
     size_t smem = STAGES * stage + 128;
     if (smem < (size_t)nkv * sizeof(NewestScratch) + 128) smem = (size_t)nkv * sizeof(NewestScratch) + 128;

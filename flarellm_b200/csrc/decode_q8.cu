@@ -26,6 +26,25 @@
 #include <math_constants.h>
 #include <mutex>
 
+#ifdef FLARE_TIMELINE
+// Tuning aid (not part of the product build): thread 0 of every CTA stamps the global timer at eight points of
+// the kernel into a device array that flare_debug_timeline copies out.
+__device__ unsigned long long g_timeline[8192 * 8];
+#define TL_STAMP(k)                                                                                              \
+    do {                                                                                                         \
+        if (threadIdx.x == 0) {                                                                                  \
+            unsigned long long _t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t));                        \
+            const unsigned _c = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;                  \
+            if (_c < 8192) g_timeline[_c * 8 + (k)] = _t;                                                        \
+        }                                                                                                        \
+    } while (0)
+extern "C" __attribute__((visibility("default"))) int flare_debug_timeline(void* dst, size_t bytes) {
+    return (int)cudaMemcpyFromSymbol(dst, g_timeline, bytes < sizeof(g_timeline) ? bytes : sizeof(g_timeline));
+}
+#else
+#define TL_STAMP(k) do { } while (0)
+#endif
+
 namespace {
 
 // Guards the per-device tables below: two contexts on two host threads may make their first call at once.
@@ -51,6 +70,7 @@ struct Q8Params {
     int attend_small[64];
     int n_q, causal_q, hgroups;   // grid.z = n_q * hgroups: one query and one group of up to 4 of its heads per kv head
     int cluster;             // the n_split CTAs of a sequence form one thread-block cluster and merge through shared memory
+    int rec_overlap;         // the cluster's record area reuses the stage buffers (no room behind them)
     int whole_rows;             // 1: the maps deliver all heads of a tile in one copy; 0: one copy per head
     int* err;
 };
@@ -105,66 +125,11 @@ __device__ __forceinline__ void cluster_sync_all() {
 __device__ __forceinline__ uint32_t cluster_map(uint32_t smem_addr, uint32_t cta_rank) {
     uint32_t r; asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(cta_rank)); return r;
 }
-__device__ __forceinline__ float cluster_ld(uint32_t addr) {
-    float v; asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory"); return v;
+__device__ __forceinline__ void cluster_st(uint32_t addr, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
-
-// Log-sum-exp merge of the split partials of this path ([row][split][HD + 2], reference max in
-// log2 units); one CTA per (sequence, head) row.  The per-split weights are computed once, in
-// parallel over the splits, so that a long-context call with more than a hundred splits does not
-// serialise on dependent loads.
-__global__ void merge_q8_kernel(const float* __restrict__ work, int n_split, int hd, float* __restrict__ out,
-                                int want_partial) {
-    __shared__ float s_w[256];          // weight of each split (n_split <= 256)
-    __shared__ float s_red[8];
-    pdl_trigger();          // the next layer's kernel may begin its prologue
-    pdl_wait();             // the decode kernel has written every partial
-    const int row = blockIdx.x, tid = threadIdx.x, nthr = blockDim.x;
-    const float* base = work + (size_t)row * n_split * (hd + 2);
-    // reference max over the non-empty splits
-    float mm = -CUDART_INF_F;
-    for (int r = tid; r < n_split; r += nthr)
-        if (base[r * (hd + 2) + 1] > 0.0f) mm = fmaxf(mm, base[r * (hd + 2)]);
-#pragma unroll
-    for (int off = 16; off; off >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, off));
-    if ((tid & 31) == 0) s_red[tid >> 5] = mm;
-    __syncthreads();
-    mm = s_red[0];
-    for (int w = 1; w < (nthr + 31) / 32; w++) mm = fmaxf(mm, s_red[w]);
-    __syncthreads();
-    float ll = 0.0f;
-    for (int r = tid; r < n_split; r += nthr) {
-        const float l_r = base[r * (hd + 2) + 1];
-        const float w = l_r > 0.0f ? fast_exp2(base[r * (hd + 2)] - mm) : 0.0f;
-        s_w[r] = w;
-        ll += l_r * w;
-    }
-#pragma unroll
-    for (int off = 16; off; off >>= 1) ll += __shfl_xor_sync(0xffffffffu, ll, off);
-    if ((tid & 31) == 0) s_red[tid >> 5] = ll;
-    __syncthreads();
-    ll = 0.0f;
-    for (int w = 0; w < (nthr + 31) / 32; w++) ll += s_red[w];
-    // the threads form nthr / hd groups; group k sums the records k, k + groups, ... of channel d, then the
-    // groups are added up through shared memory (a long-context call has hundreds of records per row)
-    __shared__ float s_part[256];
-    const int groups = nthr / hd, grp = tid / hd, d = tid % hd;
-    float acc = 0.0f;
-    if (grp < groups) {
-#pragma unroll 4
-        for (int r = grp; r < n_split; r += groups) acc = fmaf(base[r * (hd + 2) + 2 + d], s_w[r], acc);
-    }
-    s_part[tid] = acc;
-    __syncthreads();
-    if (tid < hd) {
-        for (int k = 1; k < groups; k++) acc += s_part[k * hd + tid];
-        if (want_partial) out[(size_t)row * (hd + 2) + 2 + tid] = acc;
-        else out[(size_t)row * hd + tid] = ll > 0.0f ? acc / ll : 0.0f;
-    }
-    if (want_partial && tid == 0) {
-        out[(size_t)row * (hd + 2)] = mm * 0.6931471805599453f;
-        out[(size_t)row * (hd + 2) + 1] = ll;
-    }
+__device__ __forceinline__ void cluster_st4(uint32_t addr, float a, float b, float c, float d) {
+    asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
 template <int HD>
@@ -178,6 +143,7 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
     __shared__ uint64_t full_bar[STAGES];
     __shared__ int done_cnt[STAGES];        // warps that have finished with the stage's current tile
 
+    TL_STAMP(0);            // CTA started
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, tig = lane & 3;
     const int split = blockIdx.x, b = blockIdx.y;
@@ -246,10 +212,12 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
         for (int i = STAGES; i < STAGES + L2_AHEAD && i < n_tiles; i++) prefetch(i);
     }
     __syncthreads();
+    TL_STAMP(1);            // first tiles requested
 
     // The K/V tiles requested above do not depend on the previous kernel in the stream (the previous
     // layer's attention); q does.
     pdl_wait();
+    TL_STAMP(2);            // predecessor complete
 
     // ---- q as two int8 limbs per head, laid out as the A operand of m16n8k32 --------------
     const int hq = g & 3;                          // query head of this lane within the group
@@ -328,10 +296,12 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
     const uint32_t vsoff = ksoff + scale_tile + lane_blk * 2;
 
     bool failed = false;
+    TL_STAMP(3);            // q ready
     for (int i = 0; i < n_tiles; i++) {
         const int s = i % STAGES;
         const int slot0 = (t_begin + i) * T;
         if (!ptx::mbar_wait(&full_bar[s], (uint32_t)((i / STAGES) & 1))) { failed = true; break; }
+        if (i == 0) TL_STAMP(4);        // first tile arrived
         const unsigned char* kt = sbase + (size_t)s * stage_bytes;
         const uint32_t vt = ptx::smem_u32(kt);
 
@@ -461,9 +431,10 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
             }
         }
     }
+    TL_STAMP(5);            // warp 0 done with its tiles
     pdl_trigger();          // the next kernel in the stream may be scheduled; it waits for this grid to finish
     if (failed) {
-        if (lane == 0) atomicExch(p.err, FLARE_ERR_TIMEOUT);
+        if (lane == 0) flare_report(p.err, FLARE_ERR_TIMEOUT);
         if (!p.cluster) return;     // in a cluster every CTA still has to reach the barriers
     }
 
@@ -476,53 +447,54 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
         lb[mt] += __shfl_xor_sync(0xffffffffu, lb[mt], 2);
     }
     if (p.cluster) {
-        // The splits of this sequence are the CTAs of one cluster: every CTA leaves its (m, l, o) records
-        // in its own shared memory, then each merges a share of the rows by reading its peers' records.
-        __syncthreads();                                    // all warps are done with the stage buffers
-        float* rec = reinterpret_cast<float*>(sbase);       // [num_heads][HD + 2]
+        // The splits of this sequence are the CTAs of one cluster.  Row r of the sequence (a query head) is merged
+        // by CTA r % n: every CTA stores its (o, m, l) record of the row straight into that CTA's shared memory
+        // (distributed shared memory, slot [r / n][own rank]), one cluster barrier makes the stores visible, and
+        // each CTA merges the rows it owns out of its own shared memory.  The record area lies behind the stage
+        // buffers, so that a fast CTA may deliver while the owner is still streaming; where shared memory has no
+        // room for that (head_dim 128) it reuses the stage buffers after one more barrier.  After the last barrier
+        // nobody touches another CTA's memory, so a CTA may leave as soon as it has written its rows.
+        constexpr int RS = HD + 4;                          // floats per record: o[HD], m, l, padding (16-byte rows)
+        const uint32_t rank = cluster_ctarank(), n = (uint32_t)p.n_split;
+        float* rec = reinterpret_cast<float*>(sbase + (p.rec_overlap ? 0 : (size_t)STAGES * stage_bytes));   // [rows owned][n][RS]
+        if (p.rec_overlap) cluster_sync_all();              // no room behind the stages: wait until every CTA has finished streaming
         if (head_ok) {
-            float* r = rec + (kvh * p.G + hq) * (HD + 2);
+            const uint32_t r = (uint32_t)(kvh * p.G + hq), owner = r % n, k = r / n;
+            const uint32_t dst = cluster_map(ptx::smem_u32(rec) + ((k * n + rank) * RS) * 4, owner);
 #pragma unroll
             for (int mt = 0; mt < MT; mt++) {
                 const float bias = 1152.0f * lb[mt];
 #pragma unroll
                 for (int lc = 0; lc < 2; lc++) {
                     const int d0 = 64 * mt + 16 * (2 * lane_blk + lc) + 4 * tig;
-                    r[2 + d0] = (lane_blk ? acc[mt][2 + lc][0][0] : acc[mt][lc][0][0]) - bias;
-                    r[2 + d0 + 1] = (lane_blk ? acc[mt][2 + lc][1][0] : acc[mt][lc][1][0]) - bias;
-                    r[2 + d0 + 2] = (lane_blk ? acc[mt][2 + lc][0][1] : acc[mt][lc][0][1]) - bias;
-                    r[2 + d0 + 3] = (lane_blk ? acc[mt][2 + lc][1][1] : acc[mt][lc][1][1]) - bias;
+                    cluster_st4(dst + d0 * 4,
+                                (lane_blk ? acc[mt][2 + lc][0][0] : acc[mt][lc][0][0]) - bias,
+                                (lane_blk ? acc[mt][2 + lc][1][0] : acc[mt][lc][1][0]) - bias,
+                                (lane_blk ? acc[mt][2 + lc][0][1] : acc[mt][lc][0][1]) - bias,
+                                (lane_blk ? acc[mt][2 + lc][1][1] : acc[mt][lc][1][1]) - bias);
                 }
             }
-            if (g < 4 && tig == 0) { r[0] = m_run; r[1] = failed ? 0.0f : l_run; }
+            if (g < 4 && tig == 0) { cluster_st(dst + HD * 4, m_run); cluster_st(dst + (HD + 1) * 4, failed ? 0.0f : l_run); }
         }
         cluster_sync_all();
-        const uint32_t rank = cluster_ctarank(), n = (uint32_t)p.n_split;
-        const uint32_t rec0 = ptx::smem_u32(rec);
-        for (int item = threadIdx.x;; item += blockDim.x) {
-            const int r = (int)rank + (item / HD) * (int)n, d = item % HD;
-            if (r >= p.num_heads) break;
-            float mv[8], lv[8], ov[8];
-#pragma unroll
-            for (uint32_t s2 = 0; s2 < 8; s2++) {
-                if (s2 < n) {
-                    const uint32_t a = cluster_map(rec0 + (uint32_t)r * (HD + 2) * 4, s2);
-                    mv[s2] = cluster_ld(a); lv[s2] = cluster_ld(a + 4); ov[s2] = cluster_ld(a + (2 + d) * 4);
-                } else { mv[s2] = 0.0f; lv[s2] = 0.0f; ov[s2] = 0.0f; }
-            }
+        TL_STAMP(6);        // every CTA of the cluster has delivered its records
+        const int owned = ((int)p.num_heads - (int)rank + (int)n - 1) / (int)n;        // rows rank, rank + n, ...
+        for (int item = threadIdx.x; item < owned * HD; item += blockDim.x) {
+            const int k = item / HD, d = item % HD;
+            const float* rk = rec + (size_t)k * n * RS;
             float mm = -CUDART_INF_F;
-#pragma unroll
-            for (int s2 = 0; s2 < 8; s2++) if (lv[s2] > 0.0f) mm = fmaxf(mm, mv[s2]);
+            for (uint32_t s2 = 0; s2 < n; s2++)
+                if (rk[s2 * RS + HD + 1] > 0.0f) mm = fmaxf(mm, rk[s2 * RS + HD]);
             float ll = 0.0f, o = 0.0f;
-#pragma unroll
-            for (int s2 = 0; s2 < 8; s2++) {
-                const float w = lv[s2] > 0.0f ? fast_exp2(mv[s2] - mm) : 0.0f;
-                ll = fmaf(lv[s2], w, ll);
-                o = fmaf(ov[s2], w, o);
+            for (uint32_t s2 = 0; s2 < n; s2++) {
+                const float l2 = rk[s2 * RS + HD + 1];
+                const float w = l2 > 0.0f ? fast_exp2(rk[s2 * RS + HD] - mm) : 0.0f;
+                ll = fmaf(l2, w, ll);
+                o = fmaf(rk[s2 * RS + d], w, o);
             }
-            p.out[((size_t)b * p.num_heads + r) * HD + d] = ll > 0.0f ? o / ll : 0.0f;
+            p.out[((size_t)b * p.num_heads + rank + (size_t)k * n) * HD + d] = ll > 0.0f ? o / ll : 0.0f;
         }
-        cluster_sync_all();                                 // nobody leaves while a peer still reads its records
+        TL_STAMP(7);
         return;
     }
     if (!head_ok) return;
@@ -596,40 +568,72 @@ int flare_launch_decode_q8(flare_attn_ctx* ctx, const DecodeArgs& a) {
     if (n_split > max_split) n_split = max_split;
     if (n_split < 1) n_split = 1;
     if (n_split > 256) n_split = 256;
-    // Cluster mode: when about 8 (4, 2) splits per sequence fill the GPU anyway, the splits of a sequence
-    // become one thread-block cluster and merge through distributed shared memory: no second kernel, no
-    // round trip of the records through global memory.
+    // Cluster mode: when a handful of splits per sequence fill the GPU anyway, the splits of a sequence become one
+    // thread-block cluster (2 .. 16 CTAs; more than 8 is the non-portable size the kernel opts in to) and merge
+    // through distributed shared memory: no second kernel, no round trip of the records through global memory.
+    // The size is the largest one for which every sequence's cluster is resident at once: with 32 sequences
+    // 9 CTAs each put two CTAs on (nearly) every SM, where 8 leave 40 of the 296 places empty and the SMs
+    // unevenly loaded.
     int cluster = 0;
+    p.rec_overlap = 0;
+    size_t rec_bytes = 0;          // record area of a cluster CTA: [rows it owns][cluster size][head_dim + 4] floats
     if (!a.want_partial && a.slot_end < 0 && n_split >= 2 && chunks == 1) {
-        const int c = n_split >= 8 ? 8 : (n_split >= 4 ? 4 : 2);
-        if (c * 5 >= n_split * 4) cluster = c;
-    }
-    if (cluster) {
-        // all clusters must be resident at once, or the second wave costs more than the merge kernel did
         std::lock_guard<std::mutex> lock(g_table_mutex);
-        static int max_clusters[64][2][4] = {};            // [device][hd == 128][log2 c]: 0 = not asked yet
-        const int lg = cluster == 8 ? 3 : (cluster == 4 ? 2 : 1);
-        int& mc = max_clusters[ctx->device & 63][hd == 128][lg];
-        if (mc == 0) {
-            // the opt-in to large dynamic shared memory has to precede the occupancy query
-            const int max_smem = STAGES * (8 * 2 * T * hd + 2 * T * 8 * (hd / 32) * 2) + 1024;
-            if (hd == 64) cudaFuncSetAttribute(decode_q8_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
-            else cudaFuncSetAttribute(decode_q8_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
-            cudaLaunchAttribute ca[1];
-            ca[0].id = cudaLaunchAttributeClusterDimension;
-            ca[0].val.clusterDim.x = cluster; ca[0].val.clusterDim.y = 1; ca[0].val.clusterDim.z = 1;
-            cudaLaunchConfig_t qc = {};
-            qc.gridDim = dim3(cluster, 1); qc.blockDim = dim3(32 * 8); qc.dynamicSmemBytes = STAGES * (8 * 2 * T * hd + 2 * T * 8 * (hd / 32) * 2) + 1024;
-            qc.attrs = ca; qc.numAttrs = 1;
-            int n = 0;
-            cudaError_t e = hd == 64 ? cudaOccupancyMaxActiveClusters(&n, decode_q8_kernel<64>, &qc)
-                                     : cudaOccupancyMaxActiveClusters(&n, decode_q8_kernel<128>, &qc);
-            if (e != cudaSuccess) { cudaGetLastError(); n = 0; }
-            mc = n > 0 ? n : -1;
+        // [device][hd == 128][size]: 0 = not asked yet.  Asked with the shapes of the first call (number of heads,
+        // kv heads); other shapes of the same head size have smaller or equal footprints in practice
+        static int max_clusters[64][2][17][2] = {};        // last index: record area behind the stages / over them
+        static bool attr_set[64][2] = {};
+        bool& as = attr_set[ctx->device & 63][hd == 128];
+        if (!as) {
+            // the opt-ins have to precede the occupancy queries
+            int max_smem = STAGES * (8 * 2 * T * hd + 2 * T * 8 * (hd / 32) * 2) + 1024 + (32 + 16) * (hd + 4) * 4;
+            if (max_smem > 225 * 1024) max_smem = 225 * 1024;      // a CTA can opt in to 227 KB, static shared memory included
+            if (hd == 64) {
+                cudaFuncSetAttribute(decode_q8_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+                cudaFuncSetAttribute(decode_q8_kernel<64>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+            } else {
+                cudaFuncSetAttribute(decode_q8_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+                cudaFuncSetAttribute(decode_q8_kernel<128>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+            }
+            cudaGetLastError();
+            as = true;
         }
-        if (mc < a.batch) cluster = 0;
+        int c_first = n_split > 16 ? 16 : n_split;
+        bool forced = false;
+#ifdef FLARE_TUNE
+        if (const char* e = getenv("FLARE_Q8_CLUSTER")) { c_first = atoi(e); forced = true; }     // 0 or 1: no cluster
+#endif
+        for (int c = c_first; c >= 2 && !cluster; c--) {
+            if (c * 5 < n_split * 4 && !forced) break;            // far fewer CTAs than places: the merge kernel is cheaper
+            const size_t rb = (size_t)((a.num_heads + c - 1) / c) * c * (hd + 4) * sizeof(float);
+            for (int ov = 0; ov < 2 && !cluster; ov++) {
+                int& mc = max_clusters[ctx->device & 63][hd == 128][c][ov];
+                if (mc == 0) {
+                    cudaLaunchAttribute ca[1];
+                    ca[0].id = cudaLaunchAttributeClusterDimension;
+                    ca[0].val.clusterDim.x = c; ca[0].val.clusterDim.y = 1; ca[0].val.clusterDim.z = 1;
+                    cudaLaunchConfig_t qc = {};
+                    qc.gridDim = dim3(c, 1); qc.blockDim = dim3(32 * nkv);
+                    qc.dynamicSmemBytes = smem + (ov ? 0 : rb);
+                    qc.attrs = ca; qc.numAttrs = 1;
+                    int n = 0;
+                    cudaError_t e = hd == 64 ? cudaOccupancyMaxActiveClusters(&n, decode_q8_kernel<64>, &qc)
+                                             : cudaOccupancyMaxActiveClusters(&n, decode_q8_kernel<128>, &qc);
+                    if (e != cudaSuccess) { cudaGetLastError(); n = 0; }
+                    mc = n > 0 ? n : -1;
+#ifdef FLARE_TUNE
+                    fprintf(stderr, "[flare tune] cluster size %d (records %s the stages): %d clusters resident (hd %d, %d kv heads)\n",
+                            c, ov ? "over" : "behind", n, hd, nkv);
+#endif
+                }
+                if (mc >= a.batch) { cluster = c; rec_bytes = ov ? 0 : rb; p.rec_overlap = ov; }
+            }
+        }
     }
     if (cluster) n_split = cluster;
+#ifdef FLARE_TUNE
+    if (const char* e = getenv("FLARE_Q8_NSPLIT")) if (!cluster) n_split = atoi(e);
+#endif
     p.n_split = n_split;
     p.cluster = cluster;
     // two workspaces used alternately: the merge of one call may still be reading while the next
@@ -645,7 +649,8 @@ int flare_launch_decode_q8(flare_attn_ctx* ctx, const DecodeArgs& a) {
         static bool attr_done[64][2] = {};
         bool& done = attr_done[ctx->device & 63][hd == 128];
         if (!done) {
-            const int max_smem = STAGES * (8 * 2 * T * hd + 2 * T * 8 * (hd / 32) * 2) + 1024;
+            int max_smem = STAGES * (8 * 2 * T * hd + 2 * T * 8 * (hd / 32) * 2) + 1024 + (32 + 16) * (hd + 4) * 4;
+            if (max_smem > 225 * 1024) max_smem = 225 * 1024;      // a CTA can opt in to 227 KB, static shared memory included
             if (hd == 64) FLARE_CUDA_OK(ctx, cudaFuncSetAttribute(decode_q8_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
             else FLARE_CUDA_OK(ctx, cudaFuncSetAttribute(decode_q8_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
             done = true;
@@ -662,7 +667,7 @@ int flare_launch_decode_q8(flare_attn_ctx* ctx, const DecodeArgs& a) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(n_split, a.batch, chunks);
     cfg.blockDim = dim3(32 * nkv);
-    cfg.dynamicSmemBytes = smem;
+    cfg.dynamicSmemBytes = smem + rec_bytes;
     cfg.stream = ctx->stream;
     // the attributes in use are a contiguous run of attr[]: [PDL][cluster]
     cfg.attrs = ctx->last_launch_overlappable ? attr : attr + 1;
@@ -676,14 +681,8 @@ int flare_launch_decode_q8(flare_attn_ctx* ctx, const DecodeArgs& a) {
         return FLARE_OK;
     }
     if (!cluster && (n_split > 1 || a.want_partial)) {
-        cudaLaunchConfig_t mcfg = {};
-        mcfg.gridDim = dim3(rows);
-        mcfg.blockDim = dim3(256);       // a multiple of head_dim: 4 (head_dim 64) or 2 (128) groups of threads per row
-        mcfg.stream = ctx->stream;
-        mcfg.attrs = attr;
-        mcfg.numAttrs = 1;
-        FLARE_CUDA_OK(ctx, cudaLaunchKernelEx(&mcfg, merge_q8_kernel, (const float*)p.work, n_split, hd, a.out, a.want_partial));
-        FLARE_LAUNCH_CHECK(ctx);
+        // log-sum-exp merge of the slot ranges, chained with programmatic dependent launch (multi.cu)
+        FLARE_TRY(flare_launch_merge_splits(ctx, p.work, n_split, rows, hd, a.out, a.want_partial));
         ctx->last_launch_overlappable = true;
     }
     return FLARE_OK;

@@ -55,22 +55,59 @@ __global__ void write_q8_kernel(int8_t* __restrict__ Kq, __half* __restrict__ Ks
     }
 }
 
+// ------------------------------------------------------------------ rotary position embedding
+// apply_rope_with_table (flare-core/src/model.rs:7256-7292, the branch compiled on x86_64): element i of a head
+// pairs with element i + head_dim/2; (x0, x1) -> (x0 c - x1 s, x0 s + x1 c) with c, s from the caller's table row
+// of the token's position; two multiplies and a subtract / an add, never fused, so that the rotated row is the
+// CPU's bit for bit.
+struct RopeArgs {
+    const float* cos;            // null: no rotation
+    const float* sin;
+    const long long* positions;  // per row: absolute token position = row of the table
+    int head_dim;
+};
+// Channel c of the rotated key row `row` (kv_dim values) of a token at table row `pos`.
+__device__ __forceinline__ float rope_channel(const float* __restrict__ row, int c, const RopeArgs& r, long long pos) {
+    const int half = r.head_dim >> 1, e = c % r.head_dim, head0 = c - e;
+    const float* cr = r.cos + (size_t)pos * half;
+    const float* sr = r.sin + (size_t)pos * half;
+    if (e < half) return __fsub_rn(__fmul_rn(row[head0 + e], cr[e]), __fmul_rn(row[head0 + e + half], sr[e]));
+    const int i = e - half;
+    return __fadd_rn(__fmul_rn(row[head0 + i], sr[i]), __fmul_rn(row[head0 + e], cr[i]));
+}
+// In-place rotation of [n_rows][num_heads][head_dim] (used for q, and for the key rows of the 2-bit caches).
+__global__ void rope_rows_kernel(float* __restrict__ rows, int n_rows, int num_heads, RopeArgs r) {
+    const int half = r.head_dim >> 1;
+    const size_t total = (size_t)n_rows * num_heads * half;
+    for (size_t t = blockIdx.x * (size_t)blockDim.x + threadIdx.x; t < total; t += (size_t)gridDim.x * blockDim.x) {
+        const int i = (int)(t % half);
+        const size_t rh = t / half;                   // (row, head)
+        const int row = (int)(rh / num_heads);
+        const long long pos = r.positions[row];
+        float* x = rows + rh * r.head_dim;
+        const float c = r.cos[(size_t)pos * half + i], s = r.sin[(size_t)pos * half + i];
+        const float x0 = x[i], x1 = x[i + half];
+        x[i] = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
+        x[i + half] = __fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c));
+    }
+}
+
 // One new token per sequence (a decode step of the whole batch): row b -> ring slot position[b].
 __global__ void write_step_f32_kernel(float* __restrict__ K, float* __restrict__ V, size_t seq_stride_floats,
                                       const float* __restrict__ key, const float* __restrict__ value,
-                                      const int2* __restrict__ ring, int batch, int kv_dim) {
+                                      const int2* __restrict__ ring, int batch, int kv_dim, RopeArgs rope) {
     size_t total = (size_t)batch * kv_dim;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         int b = (int)(i / kv_dim), c = (int)(i % kv_dim);
         size_t dst = (size_t)b * seq_stride_floats + (size_t)ring[b].x * kv_dim + c;
-        K[dst] = key[i];
+        K[dst] = rope.cos ? rope_channel(key + (size_t)b * kv_dim, c, rope, rope.positions[b]) : key[i];
         V[dst] = value[i];
     }
 }
 __global__ void write_step_q8_kernel(int8_t* __restrict__ Kq, __half* __restrict__ Ks, int8_t* __restrict__ Vq,
                                      __half* __restrict__ Vs, size_t q_stride, size_t s_stride,
                                      const float* __restrict__ key, const float* __restrict__ value,
-                                     const int2* __restrict__ ring, int batch, int kv_dim) {
+                                     const int2* __restrict__ ring, int batch, int kv_dim, RopeArgs rope) {
     const int lane = threadIdx.x & 31;
     const int bpr = kv_dim / 32;
     const size_t n_blocks = (size_t)batch * bpr * 2;
@@ -78,7 +115,9 @@ __global__ void write_step_q8_kernel(int8_t* __restrict__ Kq, __half* __restrict
         const bool is_v = w >= n_blocks / 2;
         const size_t bi = is_v ? w - n_blocks / 2 : w;
         const int b = (int)(bi / bpr), blk = (int)(bi % bpr);
-        const float x = (is_v ? value : key)[(size_t)b * kv_dim + blk * 32 + lane];
+        // the key is rotated (when a table is given) before it is quantised, as the model does (model.rs:2168-2206)
+        const float x = (!is_v && rope.cos) ? rope_channel(key + (size_t)b * kv_dim, blk * 32 + lane, rope, rope.positions[b])
+                                            : (is_v ? value : key)[(size_t)b * kv_dim + blk * 32 + lane];
         float amax = fabsf(x);
 #pragma unroll
         for (int off = 16; off; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
@@ -411,25 +450,36 @@ int flare_launch_kv_write(flare_kv* kv, int layer, int seq, int64_t first_pos, i
     return FLARE_OK;
 }
 
-int flare_launch_kv_write_step(flare_kv* kv, int layer, const int2* d_ring, const float* d_key, const float* d_value) {
+int flare_launch_rope_rows(flare_kv* kv, float* d_rows, int n_rows, int num_heads, const long long* d_positions) {
+    flare_attn_ctx* ctx = kv->ctx;
+    if (n_rows <= 0) return FLARE_OK;
+    RopeArgs r = {kv->rope_cos, kv->rope_sin, d_positions, kv->head_dim};
+    rope_rows_kernel<<<grid_for((size_t)n_rows * num_heads * (kv->head_dim / 2), 256), 256, 0, ctx->stream>>>(d_rows, n_rows, num_heads, r);
+    FLARE_LAUNCH_CHECK(ctx);
+    return FLARE_OK;
+}
+
+int flare_launch_kv_write_step(flare_kv* kv, int layer, const int2* d_ring, const float* d_key, const float* d_value,
+                               const long long* d_positions) {
     flare_attn_ctx* ctx = kv->ctx;
     const int kvd = kv->kv_dim, B = kv->batch;
+    RopeArgs rope = {d_positions ? kv->rope_cos : nullptr, kv->rope_sin, d_positions, kv->head_dim};
     switch (kv->dtype) {
         case FLARE_KV_F32:
             write_step_f32_kernel<<<grid_for((size_t)B * kvd, 256), 256, 0, ctx->stream>>>(
                 (float*)kv->plane_ptr(FLARE_PLANE_K, layer, 0), (float*)kv->plane_ptr(FLARE_PLANE_V, layer, 0),
-                kv->plane_bytes[FLARE_PLANE_K] / 4, d_key, d_value, d_ring, B, kvd);
+                kv->plane_bytes[FLARE_PLANE_K] / 4, d_key, d_value, d_ring, B, kvd, rope);
             FLARE_LAUNCH_CHECK(ctx);
             return FLARE_OK;
         case FLARE_KV_Q8_0:
             write_step_q8_kernel<<<grid_for((size_t)B * kvd * 2, 256), 256, 0, ctx->stream>>>(
                 (int8_t*)kv->plane_ptr(FLARE_PLANE_K_Q, layer, 0), (__half*)kv->plane_ptr(FLARE_PLANE_K_SCALE, layer, 0),
                 (int8_t*)kv->plane_ptr(FLARE_PLANE_V_Q, layer, 0), (__half*)kv->plane_ptr(FLARE_PLANE_V_SCALE, layer, 0),
-                kv->plane_bytes[FLARE_PLANE_K_Q], kv->plane_bytes[FLARE_PLANE_K_SCALE] / 2, d_key, d_value, d_ring, B, kvd);
+                kv->plane_bytes[FLARE_PLANE_K_Q], kv->plane_bytes[FLARE_PLANE_K_SCALE] / 2, d_key, d_value, d_ring, B, kvd, rope);
             FLARE_LAUNCH_CHECK(ctx);
             return FLARE_OK;
         default:
-            // the 2-bit caches keep per-sequence running state: one sequence at a time
+            // the 2-bit caches keep per-sequence running state: one sequence at a time (the caller has rotated the rows)
             for (int b = 0; b < B; b++) {
                 int64_t abs_pos = kv->length[b] < kv->max_seq_len ? kv->length[b] : kv->max_seq_len + kv->position[b];
                 FLARE_TRY(flare_launch_kv_write(kv, layer, b, abs_pos, kv->length[b], 1, d_key + (size_t)b * kvd,

@@ -10,9 +10,10 @@
 //            flare_attn_comm_init.  NCCL is loaded at run time (libnccl.so.2); the library does not link it.
 //   direct   after flare_attn_comm_enable_direct every rank owns a record buffer that its peers have mapped
 //            (CUDA IPC).  The kernel that merges a rank's slot ranges STORES the rank's record into slot `rank`
-//            of every peer's buffer, publishes a sequence number per (rank, row) with a system-scope release
-//            store, waits — with a time limit — until the numbers of all ranks have arrived in its OWN buffer,
-//            and merges.  Peer memory is only ever written, never read, and no bulk or multicast copy touches it.
+//            of every peer's buffer as 8-byte words {value, sequence number of the call}: an aligned 8-byte store
+//            arrives whole, so a word whose number matches carries its value — no fence, no separate flag.  It
+//            then polls the words of all ranks in its OWN buffer, with a time limit, and merges.  Peer memory is
+//            only ever written with plain stores, never read, and no bulk copy touches it.
 //            One kernel instead of a kernel, a collective and another kernel.
 // Every rank makes the same sequence of multi-GPU calls; a rank that does not show up makes the others' wait run
 // out: they report FLARE_ERR_TIMEOUT and stay usable.
@@ -21,6 +22,23 @@
 #include <math_constants.h>
 #include <mutex>
 #include <nccl.h>
+
+#ifdef FLARE_TIMELINE
+// Tuning aid (not part of the product build): thread 0 of every CTA of the exchange kernel stamps the global timer.
+__device__ unsigned long long g_timeline_x[1024 * 8];
+#define TLX_STAMP(k)                                                                                             \
+    do {                                                                                                         \
+        if (threadIdx.x == 0 && blockIdx.x < 1024) {                                                             \
+            unsigned long long _t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t));                        \
+            g_timeline_x[blockIdx.x * 8 + (k)] = _t;                                                             \
+        }                                                                                                        \
+    } while (0)
+extern "C" __attribute__((visibility("default"))) int flare_debug_timeline_x(void* dst, size_t bytes) {
+    return (int)cudaMemcpyFromSymbol(dst, g_timeline_x, bytes < sizeof(g_timeline_x) ? bytes : sizeof(g_timeline_x));
+}
+#else
+#define TLX_STAMP(k) do { } while (0)
+#endif
 
 namespace {
 
@@ -80,8 +98,8 @@ struct FlareComm {
     // direct exchange
     bool direct = false;
     int rows_max = 0, hd_max = 0;
-    char* local_buf = nullptr;            // [2 phases][world][rows_max][hd_max + 2] f32, then flags [world][rows_max] u32
-    size_t flags_off = 0, buf_bytes = 0;
+    char* local_buf = nullptr;            // [2 phases][world][rows_max][hd_max / 32][34] words of {f32 value, u32 call number}
+    size_t buf_bytes = 0;
     void* peer_buf[kMaxWorld] = {};       // the same buffer of every rank as mapped here; [rank] = local_buf
     uint32_t seq = 0;
     unsigned wait_ms = 2000;
@@ -102,135 +120,150 @@ __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.lau
 __device__ __forceinline__ unsigned long long global_ns() {
     unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t;
 }
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-    uint32_t v; asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory"); return v;
-}
+constexpr int CW = 32;               // channels per CTA of the merge kernel
+constexpr int WORDS = CW + 2;        // 8-byte words of one (row, channel chunk) record: o[32], m, l
 
 struct ExchangeParams {
-    float* rec[kMaxWorld];          // record buffer of rank r (as mapped in this process)
-    uint32_t* flags[kMaxWorld];     // flag array of rank r
-    int rank, world, rows_max, rec_stride;   // rec_stride: floats per record slot (hd_max + 2)
+    uint2* rec[kMaxWorld];          // record buffer of rank r (as mapped in this process): [2][world][rows_max][chunks][WORDS]
+    int rank, world, rows_max, chunks_max;
     int phase;                      // which half of the record buffers this call uses
     uint32_t seq;                   // this call's sequence number
     unsigned long long wait_ns;
     int* err;
 };
 
+__device__ __forceinline__ void st_word(uint2* p, float v, uint32_t seq) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(seq) : "memory");
+}
+__device__ __forceinline__ uint2 ld_word(const uint2* p) {
+    uint2 v; asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory"); return v;
+}
+
 enum { MODE_FINAL = 0, MODE_RECORD = 1, MODE_EXCHANGE = 2 };
 
-// One CTA per (sequence, query, head) row.  Merges the row's n_split slot-range records (maximum in log2
-// units) into one record, then
+// One CTA per (row, chunk of 32 channels); a row is one (sequence, query, head).  Merges the row's n_split
+// slot-range records (maximum in log2 units, n_split <= 256) into one record for its channels, then
 //   MODE_FINAL     writes the normalised output (a world of one rank)
 //   MODE_RECORD    writes the record with the maximum in natural units to `out` [row][hd + 2] (NCCL exchange)
-//   MODE_EXCHANGE  stores the record into every rank's buffer, publishes, waits for all ranks' records in its own
-//                  buffer and writes the normalised output over all ranks
+//   MODE_EXCHANGE  stores the record into every rank's buffer, waits for all ranks' records in its own buffer and
+//                  writes the normalised output over all ranks
+// The split records of a long-context call are a few MB spread over L2: many small CTAs with several loads in
+// flight per thread fetch them far faster than one CTA per row.
 template <int MODE>
 __global__ void __launch_bounds__(256) merge_exchange_kernel(const float* __restrict__ work, int n_split, int hd,
                                                              ExchangeParams mp, float* __restrict__ out) {
-    __shared__ float s_w[256];          // weight of each slot range (n_split <= 256)
+    __shared__ float s_w[256];          // weight of each slot range
     __shared__ float s_red[8];
-    __shared__ float s_part[256];
-    __shared__ float s_rec[258];        // this rank's record of the row
+    __shared__ float s_part[16][CW];
+    __shared__ float s_send[WORDS];
+    __shared__ float s_recv[kMaxWorld][WORDS];
     __shared__ int s_fail;
+    TLX_STAMP(0);
     pdl_trigger();          // the next call's attention kernel may begin its prologue (it never writes what is read here)
     pdl_wait();             // the attention kernel has written every slot-range record
-    const int row = blockIdx.x, tid = threadIdx.x, nthr = blockDim.x;
-    const float* base = work + (size_t)row * n_split * (hd + 2);
-    float mm = -CUDART_INF_F;
-    for (int r = tid; r < n_split; r += nthr)
-        if (base[r * (hd + 2) + 1] > 0.0f) mm = fmaxf(mm, base[r * (hd + 2)]);
+    TLX_STAMP(1);
+    const int row = blockIdx.x, chunk = blockIdx.y, tid = threadIdx.x;
+    const int rs = hd + 2;
+    const float* base = work + (size_t)row * n_split * rs;
+    // ---- weights of the slot ranges: one range per thread ------------------------------------------------
+    float m_r = -CUDART_INF_F, l_r = 0.0f;
+    if (tid < n_split) { l_r = base[tid * rs + 1]; if (l_r > 0.0f) m_r = base[tid * rs]; }
+    float mm = m_r;
 #pragma unroll
     for (int off = 16; off; off >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, off));
     if ((tid & 31) == 0) s_red[tid >> 5] = mm;
     if (tid == 0) s_fail = 0;
     __syncthreads();
     mm = s_red[0];
-    for (int w = 1; w < (nthr + 31) / 32; w++) mm = fmaxf(mm, s_red[w]);
+#pragma unroll
+    for (int w = 1; w < 8; w++) mm = fmaxf(mm, s_red[w]);
     __syncthreads();
-    float ll = 0.0f;
-    for (int r = tid; r < n_split; r += nthr) {
-        const float l_r = base[r * (hd + 2) + 1];
-        const float w = l_r > 0.0f ? fast_exp2(base[r * (hd + 2)] - mm) : 0.0f;
-        s_w[r] = w;
-        ll += l_r * w;
-    }
+    const float w_r = l_r > 0.0f ? fast_exp2(m_r - mm) : 0.0f;
+    s_w[tid] = w_r;
+    float ll = l_r * w_r;
 #pragma unroll
     for (int off = 16; off; off >>= 1) ll += __shfl_xor_sync(0xffffffffu, ll, off);
     if ((tid & 31) == 0) s_red[tid >> 5] = ll;
     __syncthreads();
     ll = 0.0f;
-    for (int w = 0; w < (nthr + 31) / 32; w++) ll += s_red[w];
-    const int groups = nthr / hd, grp = tid / hd, d = tid % hd;
-    float acc = 0.0f;
-    if (grp < groups) {
+#pragma unroll
+    for (int w = 0; w < 8; w++) ll += s_red[w];
+    // ---- weighted sum of the ranges' outputs: 16 groups of 16 threads, a thread owns 2 channels ------------
+    {
+        const int grp = tid >> 4, c2 = (tid & 15) * 2;
+        const float* src = base + 2 + chunk * CW + c2;
+        float a0 = 0.0f, a1 = 0.0f;
 #pragma unroll 4
-        for (int r = grp; r < n_split; r += groups) acc = fmaf(base[r * (hd + 2) + 2 + d], s_w[r], acc);
-    }
-    s_part[tid] = acc;
-    __syncthreads();
-    if (tid < hd) {
-        for (int k = 1; k < groups; k++) acc += s_part[k * hd + tid];
-        if (MODE == MODE_FINAL) out[(size_t)row * hd + tid] = ll > 0.0f ? acc / ll : 0.0f;
-        else if (MODE == MODE_RECORD) out[(size_t)row * (hd + 2) + 2 + tid] = acc;
-        else s_rec[2 + tid] = acc;
-    }
-    if (MODE == MODE_FINAL) return;
-    if (MODE == MODE_RECORD) {
-        if (tid == 0) {
-            out[(size_t)row * (hd + 2)] = ll > 0.0f ? mm * kLn2 : 0.0f;
-            out[(size_t)row * (hd + 2) + 1] = ll;
+        for (int r = grp; r < n_split; r += 16) {
+            const float2 v = *reinterpret_cast<const float2*>(src + (size_t)r * rs);
+            const float w = s_w[r];
+            a0 = fmaf(v.x, w, a0); a1 = fmaf(v.y, w, a1);
         }
+        s_part[grp][c2] = a0; s_part[grp][c2 + 1] = a1;
+    }
+    __syncthreads();
+    float val = 0.0f;
+    if (tid < CW) {
+#pragma unroll
+        for (int k = 0; k < 16; k++) val += s_part[k][tid];
+    }
+    TLX_STAMP(2);
+    const int d = chunk * CW + tid;         // channel of thread tid < CW
+    if (MODE == MODE_FINAL) {
+        if (tid < CW) out[(size_t)row * hd + d] = ll > 0.0f ? val / ll : 0.0f;
         return;
     }
-    if (tid == 0) { s_rec[0] = ll > 0.0f ? mm : 0.0f; s_rec[1] = ll; }
-    __syncthreads();
-
-    // ---- this rank's record into slot `rank` of every rank's buffer (plain stores; the own buffer included) ----
-    const size_t slot_off = ((size_t)(mp.phase * mp.world + mp.rank) * mp.rows_max + row) * mp.rec_stride;
-    for (int r = 0; r < mp.world; r++) {
-        float* dst = mp.rec[r] + slot_off;
-        for (int i = tid; i < hd + 2; i += nthr) dst[i] = s_rec[i];
+    if (MODE == MODE_RECORD) {
+        if (tid < CW) out[(size_t)row * rs + 2 + d] = val;
+        if (chunk == 0 && tid == 0) { out[(size_t)row * rs] = ll > 0.0f ? mm * kLn2 : 0.0f; out[(size_t)row * rs + 1] = ll; }
+        return;
     }
-    __threadfence_system();             // each thread's stores are ordered before what follows, system-wide
+    if (tid < CW) s_send[tid] = val;
+    if (tid == 0) { s_send[CW] = ll > 0.0f ? mm : 0.0f; s_send[CW + 1] = ll; }
     __syncthreads();
-    if (tid < mp.world) st_release_sys(mp.flags[tid] + (size_t)mp.rank * mp.rows_max + row, mp.seq);
-    // ---- wait until every rank's record of this row has arrived here (own memory, bounded) -----------------
-    if (tid < mp.world) {
-        const uint32_t* f = mp.flags[mp.rank] + (size_t)tid * mp.rows_max + row;
-        const unsigned long long t0 = global_ns();
+    // ---- this rank's record into slot `rank` of every rank's buffer: {value, call number} words ------------
+    const size_t slot_words = (size_t)WORDS;
+    const size_t my_slot = ((((size_t)mp.phase * mp.world + mp.rank) * mp.rows_max + row) * mp.chunks_max + chunk) * slot_words;
+    for (int t = tid; t < WORDS * mp.world; t += blockDim.x) {
+        const int r = t / WORDS, i = t % WORDS;
+        st_word(mp.rec[r] + my_slot + i, s_send[i], mp.seq);
+    }
+    TLX_STAMP(3);
+    // ---- every rank's record of this (row, chunk) out of the own buffer: a word is there when its number matches
+    const unsigned long long t0 = global_ns();
+    for (int t = tid; t < WORDS * mp.world; t += blockDim.x) {
+        const int r = t / WORDS, i = t % WORDS;
+        const uint2* src = mp.rec[mp.rank] + ((((size_t)mp.phase * mp.world + r) * mp.rows_max + row) * mp.chunks_max + chunk) * slot_words + i;
         bool ok = false;
         for (;;) {
-            if (ld_acquire_sys(f) == mp.seq) { ok = true; break; }
+            const uint2 v = ld_word(src);
+            if (v.y == mp.seq) { s_recv[r][i] = __uint_as_float(v.x); ok = true; break; }
             if (global_ns() - t0 > mp.wait_ns) break;
-            __nanosleep(100);
+            __nanosleep(40);
         }
         if (!ok) s_fail = 1;
     }
     __syncthreads();
+    TLX_STAMP(5);
     if (s_fail) {       // a rank did not show up in time: report, leave zeros, return (the context stays usable)
-        if (tid == 0) atomicExch(mp.err, FLARE_ERR_TIMEOUT);
-        if (tid < hd) out[(size_t)row * hd + tid] = 0.0f;
+        if (tid == 0) flare_report(mp.err, FLARE_ERR_TIMEOUT);
+        if (tid < CW) out[(size_t)row * hd + d] = 0.0f;
         return;
     }
-    // ---- merge the ranks' records (read past L1: they were written by other GPUs) ---------------------------
-    if (tid < hd) {
-        const float* mine = mp.rec[mp.rank] + ((size_t)(mp.phase * mp.world) * mp.rows_max + row) * mp.rec_stride;
-        const size_t rank_stride = (size_t)mp.rows_max * mp.rec_stride;
+    if (tid < CW) {
         float gm = -CUDART_INF_F;
         for (int r = 0; r < mp.world; r++)
-            if (__ldcg(mine + r * rank_stride + 1) > 0.0f) gm = fmaxf(gm, __ldcg(mine + r * rank_stride));
+            if (s_recv[r][CW + 1] > 0.0f) gm = fmaxf(gm, s_recv[r][CW]);
         float gl = 0.0f, go = 0.0f;
         for (int r = 0; r < mp.world; r++) {
-            const float l_r = __ldcg(mine + r * rank_stride + 1);
-            const float w = l_r > 0.0f ? fast_exp2(__ldcg(mine + r * rank_stride) - gm) : 0.0f;
-            gl = fmaf(l_r, w, gl);
-            go = fmaf(__ldcg(mine + r * rank_stride + 2 + tid), w, go);
+            const float l2 = s_recv[r][CW + 1];
+            const float w = l2 > 0.0f ? fast_exp2(s_recv[r][CW] - gm) : 0.0f;
+            gl = fmaf(l2, w, gl);
+            go = fmaf(s_recv[r][tid], w, go);
         }
-        out[(size_t)row * hd + tid] = gl > 0.0f ? go / gl : 0.0f;
+        out[(size_t)row * hd + d] = gl > 0.0f ? go / gl : 0.0f;
     }
+    TLX_STAMP(6);
 }
 
 template <int MODE>
@@ -240,8 +273,8 @@ int launch_merge_exchange(flare_attn_ctx* ctx, const float* work, int n_split, i
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(rows);
-    cfg.blockDim = dim3(256);           // a multiple of head_dim 64 / 128
+    cfg.gridDim = dim3(rows, hd / CW);
+    cfg.blockDim = dim3(256);
     cfg.stream = ctx->stream;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
@@ -263,11 +296,8 @@ int ensure_nccl_buffers(flare_attn_ctx* ctx, FlareComm* c, size_t part_floats) {
 
 void fill_exchange_params(const FlareComm* c, ExchangeParams* mp, int* err) {
     memset(mp, 0, sizeof(*mp));
-    for (int r = 0; r < c->world; r++) {
-        mp->rec[r] = reinterpret_cast<float*>(c->peer_buf[r]);
-        mp->flags[r] = reinterpret_cast<uint32_t*>(reinterpret_cast<char*>(c->peer_buf[r]) + c->flags_off);
-    }
-    mp->rank = c->rank; mp->world = c->world; mp->rows_max = c->rows_max; mp->rec_stride = c->hd_max + 2;
+    for (int r = 0; r < c->world; r++) mp->rec[r] = reinterpret_cast<uint2*>(c->peer_buf[r]);
+    mp->rank = c->rank; mp->world = c->world; mp->rows_max = c->rows_max; mp->chunks_max = c->hd_max / CW;
     mp->wait_ns = (unsigned long long)c->wait_ms * 1000000ull;
     mp->err = err;
 }
@@ -287,6 +317,14 @@ void flare_comm_free(flare_attn_ctx* ctx) {
     if (c->comm && api) api->CommDestroy(c->comm);
     delete c;
     ctx->comm = nullptr;
+}
+
+int flare_launch_merge_splits(flare_attn_ctx* ctx, const float* work, int n_split, int rows, int head_dim, float* out,
+                              int want_partial) {
+    ExchangeParams mp;
+    memset(&mp, 0, sizeof(mp));
+    return want_partial ? launch_merge_exchange<MODE_RECORD>(ctx, work, n_split, rows, head_dim, mp, out)
+                        : launch_merge_exchange<MODE_FINAL>(ctx, work, n_split, rows, head_dim, mp, out);
 }
 
 int flare_multi_tail(flare_attn_ctx* ctx, const float* work, int n_split, int rows, int head_dim, float* out) {
@@ -379,9 +417,7 @@ int flare_attn_comm_enable_direct(flare_attn_ctx* ctx, int max_rows, int head_di
     NcclApi* api = nccl_api();
     if (!api) return flare_set_error(ctx, FLARE_ERR_NCCL, "NCCL is not loaded");
     FLARE_CUDA_OK(ctx, cudaSetDevice(ctx->device));
-    const size_t rec_bytes = (size_t)2 * c->world * max_rows * (head_dim + 2) * sizeof(float);
-    c->flags_off = (rec_bytes + 255) / 256 * 256;
-    c->buf_bytes = c->flags_off + (size_t)c->world * max_rows * sizeof(uint32_t);
+    c->buf_bytes = (size_t)2 * c->world * max_rows * (head_dim / CW) * WORDS * sizeof(uint2);
     FLARE_CUDA_OK(ctx, cudaMalloc(&c->local_buf, c->buf_bytes));
     FLARE_CUDA_OK(ctx, cudaMemsetAsync(c->local_buf, 0, c->buf_bytes, ctx->stream));
     // every rank's IPC handle to every rank (an all-gather of 64 bytes through device memory)
@@ -452,22 +488,17 @@ int flare_attn_comm_selftest_missing_peer(flare_attn_ctx* ctx) {
     if (!ctx) return FLARE_ERR_INVALID_ARG;
     FLARE_CUDA_OK(ctx, cudaSetDevice(ctx->device));
     const int hd = 64, rows = 2, world = 2;
-    const size_t rec_floats = (size_t)2 * world * rows * (hd + 2);
-    const size_t flags_off = (rec_floats * 4 + 255) / 256 * 256;
-    const size_t buf_bytes = flags_off + world * rows * 4;
+    const size_t buf_bytes = ((size_t)2 * world * rows * (hd / CW) * WORDS * sizeof(uint2) + 255) / 256 * 256;
     char* bufs = nullptr;
     float* work = nullptr;
-    FLARE_CUDA_OK(ctx, cudaMalloc(&bufs, 2 * buf_bytes + 256));
+    FLARE_CUDA_OK(ctx, cudaMalloc(&bufs, 2 * buf_bytes));
     if (cudaMalloc(&work, (size_t)rows * (hd + 2) * 4 + rows * hd * 4) != cudaSuccess) { cudaFree(bufs); cudaGetLastError(); return FLARE_ERR_OOM; }
-    cudaMemsetAsync(bufs, 0, 2 * buf_bytes + 256, ctx->stream);
+    cudaMemsetAsync(bufs, 0, 2 * buf_bytes, ctx->stream);
     cudaMemsetAsync(work, 0, (size_t)rows * (hd + 2) * 4 + rows * hd * 4, ctx->stream);
     ExchangeParams mp;
     memset(&mp, 0, sizeof(mp));
-    for (int r = 0; r < world; r++) {
-        mp.rec[r] = reinterpret_cast<float*>(bufs + r * ((buf_bytes + 255) / 256 * 256));
-        mp.flags[r] = reinterpret_cast<uint32_t*>(reinterpret_cast<char*>(mp.rec[r]) + flags_off);
-    }
-    mp.rank = 0; mp.world = world; mp.rows_max = rows; mp.rec_stride = hd + 2; mp.phase = 1; mp.seq = 1;
+    for (int r = 0; r < world; r++) mp.rec[r] = reinterpret_cast<uint2*>(bufs + r * buf_bytes);
+    mp.rank = 0; mp.world = world; mp.rows_max = rows; mp.chunks_max = hd / CW; mp.phase = 1; mp.seq = 1;
     mp.wait_ns = 50ull * 1000000ull;
     mp.err = ctx->d_err;
     ctx->last_launch_overlappable = false;

@@ -399,7 +399,7 @@ __global__ void __launch_bounds__(320, 1) prefill_pp_kernel(const __grid_constan
     }
     tc_fence_before();
     __syncthreads();
-    if (threadIdx.x == 0 && bars->abort_flag) atomicExch(p.err, FLARE_ERR_TIMEOUT);
+    if (threadIdx.x == 0 && bars->abort_flag) flare_report(p.err, FLARE_ERR_TIMEOUT);
     if (warp == 8) {
         tc_fence_after();
         tmem_dealloc(tmem, 512);

@@ -174,6 +174,26 @@ FLARE_API int flare_kv_append_f32(flare_kv* kv, int layer, int seq, int n_rows,
 FLARE_API int flare_kv_write_step_f32(flare_kv* kv, int layer, const float* key, const float* value,
                                       int on_device);
 
+/* Rotary position embedding fused into the step write (the reference rotates on the CPU right before the
+ * write: apply_rope_with_table at flare-core/src/model.rs:2168-2183, then gpu_kv_write at 2199-2206).
+ *
+ * flare_kv_set_rope_table   the caller's RopeTable (model.rs:7184-7213): cos and sin, each
+ *                           [table_len][head_dim / 2] f32, copied to the device.  The library never evaluates
+ *                           sin / cos itself, so the rotation uses the caller's values bit for bit; a caller with
+ *                           positions beyond the reference's 8192-row cap passes a longer table (every entry is
+ *                           the expression the reference's inline fallback, model.rs:7299-7332, evaluates).
+ * flare_kv_write_step_rope_f32   flare_kv_write_step_f32 on key rows that have NOT been rotated yet: row b is
+ *                           rotated for absolute position positions[b] (half-split pairs, model.rs:7280-7289:
+ *                           two multiplies and a subtract / an add, not fused) and quantised / stored in the same
+ *                           kernel (f32 and Q8_0 caches; the 2-bit caches rotate in a kernel of their own first).
+ *                           Values are stored as given.  positions is a host array of `batch` entries.
+ * flare_rope_rows_f32       the same rotation in place on [n_rows][num_heads][head_dim] rows (for q). */
+FLARE_API int flare_kv_set_rope_table(flare_kv* kv, const float* cos, const float* sin, int table_len);
+FLARE_API int flare_kv_write_step_rope_f32(flare_kv* kv, int layer, const float* key, const float* value,
+                                           const int64_t* positions, int on_device);
+FLARE_API int flare_rope_rows_f32(flare_kv* kv, float* rows, int n_rows, int num_heads, const int64_t* positions,
+                                  int on_device);
+
 /* KvCache::advance (kv_cache.rs:484-489) applied n times; seq < 0 = every sequence. */
 FLARE_API int flare_kv_advance(flare_kv* kv, int seq, int n);
 /* KvCache::len / position (kv_cache.rs:502-513). */

@@ -291,6 +291,40 @@ def merge_partials(partials, nh, hd) -> np.ndarray:
     return out
 
 
+# ---------------------------------------------------------------- rotary position embedding
+ROPE_TABLE_MAX_SEQ_LEN = 8192      # flare-core/src/model.rs:7171
+
+
+def rope_table(head_dim, max_seq_len, theta, cap=ROPE_TABLE_MAX_SEQ_LEN):
+    """RopeTable::new: (cos, sin), each [min(max_seq_len, cap)][head_dim // 2]."""
+    n, half = min(max_seq_len, cap), head_dim // 2
+    cos, sin = np.empty((n, half), np.float32), np.empty((n, half), np.float32)
+    L = lib()
+    L.orc_rope_table.restype = _sz
+    L.orc_rope_table.argtypes = [_sz, _sz, C.c_float, _sz, _f32p, _f32p]
+    got = L.orc_rope_table(head_dim, max_seq_len, theta, cap, cos.ctypes.data_as(_f32p), sin.ctypes.data_as(_f32p))
+    assert got == n
+    return cos, sin
+
+
+def apply_rope(data, num_heads, head_dim, pos, theta) -> np.ndarray:
+    d = np.array(data, dtype=np.float32).reshape(-1).copy()
+    L = lib()
+    L.orc_apply_rope.argtypes = [_f32p, _sz, _sz, _sz, C.c_float]
+    L.orc_apply_rope(d.ctypes.data_as(_f32p), num_heads, head_dim, pos, theta)
+    return d
+
+
+def apply_rope_with_table(data, num_heads, head_dim, pos, theta, cos, sin) -> np.ndarray:
+    d = np.array(data, dtype=np.float32).reshape(-1).copy()
+    cos, cp = _f(cos)
+    sin, sp = _f(sin)
+    L = lib()
+    L.orc_apply_rope_with_table.argtypes = [_f32p, _sz, _sz, _sz, C.c_float, _f32p, _f32p, _sz, _sz]
+    L.orc_apply_rope_with_table(d.ctypes.data_as(_f32p), num_heads, head_dim, pos, theta, cp, sp, cos.shape[0], cos.shape[1] * 2)
+    return d
+
+
 # ---------------------------------------------------------------- caches
 class KvCache:
     """flare-core/src/kv_cache.rs:431-546."""

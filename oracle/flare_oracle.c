@@ -874,6 +874,71 @@ ORC_API const uint16_t* orc_g32_res_k(const orc_g32_cache* c) { return c->res_k;
 ORC_API const uint16_t* orc_g32_res_v(const orc_g32_cache* c) { return c->res_v; }
 ORC_API size_t orc_g32_written(const orc_g32_cache* c) { return c->written; }
 
+/* ------------------------------------------------------------------------ */
+/* rotary position embedding (the step before the KV write)                 */
+/* ------------------------------------------------------------------------ */
+
+/* flare-core/src/model.rs:7171 (ROPE_TABLE_MAX_SEQ_LEN) and 7190-7213 (RopeTable::new):
+ * cos/sin of pos * freq for every (pos, d), d < head_dim / 2, flattened [positions][head_dim / 2];
+ * freq = 1 / theta^(2 d / head_dim), everything in f32.  The number of positions is capped at
+ * `cap` (the reference's constant is 8192; a caller that wants exact rows for later positions
+ * passes a larger cap — the expression per entry is the one the inline fallback evaluates).
+ * Returns the number of positions written. */
+ORC_API size_t orc_rope_table(size_t head_dim, size_t max_seq_len, float rope_theta, size_t cap,
+                              float* cos_out, float* sin_out) {
+    size_t capped = max_seq_len < cap ? max_seq_len : cap;
+    size_t half = head_dim / 2;
+    for (size_t pos = 0; pos < capped; pos++) {
+        for (size_t d = 0; d < half; d++) {
+            float freq = 1.0f / powf(rope_theta, 2.0f * (float)d / (float)head_dim);
+            float angle = (float)pos * freq;
+            cos_out[pos * half + d] = cosf(angle);
+            sin_out[pos * half + d] = sinf(angle);
+        }
+    }
+    return capped;
+}
+
+/* model.rs:7280-7289 (the branch compiled on x86_64): half-split pairs (i, i + half) of every head,
+ * two multiplies and a subtract / an add per element, no fused multiply-add. */
+static void rope_rotate(float* data, size_t num_heads, size_t head_dim, const float* cos_row, const float* sin_row) {
+    size_t half = head_dim / 2;
+    for (size_t h = 0; h < num_heads; h++) {
+        size_t offset = h * head_dim;
+        for (size_t i = 0; i < half; i++) {
+            float c = cos_row[i], s = sin_row[i];
+            float x0 = data[offset + i], x1 = data[offset + i + half];
+            data[offset + i] = x0 * c - x1 * s;
+            data[offset + i + half] = x0 * s + x1 * c;
+        }
+    }
+}
+
+/* model.rs:7299-7332 (apply_rope): cos/sin computed inline for one position. */
+ORC_API void orc_apply_rope(float* data, size_t num_heads, size_t head_dim, size_t pos, float theta) {
+    size_t half = head_dim / 2;
+    float* cs = (float*)malloc(2 * half * sizeof(float) + 8);
+    for (size_t i = 0; i < half; i++) {
+        float freq = 1.0f / powf(theta, 2.0f * (float)i / (float)head_dim);
+        float angle = (float)pos * freq;
+        cs[half + i] = sinf(angle);
+        cs[i] = cosf(angle);
+    }
+    rope_rotate(data, num_heads, head_dim, cs, cs + half);
+    free(cs);
+}
+
+/* model.rs:7256-7292 (apply_rope_with_table): table rows for positions inside the table and a
+ * matching head size, the inline computation otherwise. */
+ORC_API void orc_apply_rope_with_table(float* data, size_t num_heads, size_t head_dim, size_t pos, float theta,
+                                       const float* cos_tab, const float* sin_tab, size_t table_len,
+                                       size_t table_head_dim) {
+    if (pos >= table_len || head_dim != table_head_dim) { orc_apply_rope(data, num_heads, head_dim, pos, theta); return; }
+    size_t half = head_dim / 2;
+    rope_rotate(data, num_heads, head_dim, cos_tab + pos * half, sin_tab + pos * half);
+}
+
+
 ORC_API int orc_max_threads(void) {
     long n = sysconf(_SC_NPROCESSORS_ONLN);
     return n > 0 ? (int)n : 1;

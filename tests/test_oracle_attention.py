@@ -342,3 +342,33 @@ def test_g32_short_context_is_all_residual(orc):
     r16 = orc.f16_to_f32(orc.f32_to_f16(rows))
     assert np.array_equal(k[:100], r16) and np.array_equal(v[:100], -r16)
     assert not k[100:].any()
+
+
+# ------------------------------------------------------------------ rotary position embedding
+def test_rope_reference_properties(orc):
+    """flare-core/src/model.rs:10354-10364, 10934-11028 restated: magnitude is preserved, position 0 is the
+    identity, the table path equals the inline path (bit for bit here: the same expression per entry), positions
+    beyond the table fall back to the inline computation, the table is capped."""
+    d = orc.apply_rope([1.0, 0.0, 0.0, 1.0], 1, 4, 5, 10000.0)
+    assert abs(float(np.sum(d * d)) - 2.0) < 1e-4
+    orig = np.arange(1, 9, dtype=np.float32)
+    assert np.max(np.abs(orc.apply_rope(orig, 2, 4, 0, 10000.0) - orig)) < 1e-6
+    cos, sin = orc.rope_table(8, 128, 10000.0)
+    for pos in (0, 1, 5, 42, 127):
+        orig = (np.arange(1, 25, dtype=np.float32) * np.float32(0.3))
+        a = orc.apply_rope(orig, 3, 8, pos, 10000.0)
+        b = orc.apply_rope_with_table(orig, 3, 8, pos, 10000.0, cos, sin)
+        assert np.max(np.abs(a - b)) < 1e-6 and np.array_equal(a, b)
+    cos16, sin16 = orc.rope_table(4, 16, 10000.0)
+    orig = np.array([1, 2, 3, 4], np.float32)
+    assert np.array_equal(orc.apply_rope(orig, 1, 4, 20, 10000.0), orc.apply_rope_with_table(orig, 1, 4, 20, 10000.0, cos16, sin16))
+    capped, _ = orc.rope_table(4, 1_000_000, 10000.0)
+    assert capped.shape[0] <= orc.ROPE_TABLE_MAX_SEQ_LEN
+    cos64, sin64 = orc.rope_table(4, 64, 10000.0)
+    d = orc.apply_rope_with_table([1.0, 0.0, 0.0, 1.0], 1, 4, 5, 10000.0, cos64, sin64)
+    assert abs(float(np.sum(d * d)) - 2.0) < 1e-4
+    # the half-split pairing and the sign convention, on numbers that can be checked by hand:
+    # head_dim 2, position 1, theta anything: angle = 1 -> (x0 cos 1 - x1 sin 1, x0 sin 1 + x1 cos 1)
+    d = orc.apply_rope([1.0, 2.0], 1, 2, 1, 10000.0)
+    c, s = np.float32(np.cos(np.float32(1.0))), np.float32(np.sin(np.float32(1.0)))
+    assert abs(d[0] - (c - 2 * s)) < 1e-6 and abs(d[1] - (s + 2 * c)) < 1e-6
