@@ -29,11 +29,12 @@ DT_F32, DT_BF16 = 0, 1
 _STATUS_NAMES = {0: "OK", 1: "INVALID_ARG", 2: "UNSUPPORTED", 3: "OOM", 4: "CUDA", 5: "TIMEOUT", 6: "STATE", 7: "NCCL",
                  8: "BOUNDS"}
 OP_NONE, OP_DECODE, OP_PREFILL = range(3)
+PATH_NONE, PATH_GENERAL, PATH_Q8_TENSOR, PATH_KIVI_TENSOR, PATH_PREFILL_TENSOR = range(5)
 
 
 class Stats(C.Structure):
     """flare_attn_stats of include/flare_attn.h."""
-    _fields_ = [("calls", C.c_uint64), ("last_op", C.c_int32), ("reserved", C.c_int32),
+    _fields_ = [("calls", C.c_uint64), ("last_op", C.c_int32), ("last_path", C.c_int32),
                 ("last_elapsed_us", C.c_double), ("last_bytes", C.c_double), ("last_flops", C.c_double),
                 ("last_gbs", C.c_double), ("last_tflops", C.c_double), ("last_frac_of_peak", C.c_double),
                 ("total_elapsed_us", C.c_double), ("total_bytes", C.c_double), ("total_flops", C.c_double)]
@@ -80,6 +81,9 @@ SYMBOLS = [
     ("flare_decode_attn_noalloc_scratch_bytes", _sz, []),
     ("flare_decode_attn_partial", _i, [_vp, _vp, _i, _i, _vp, _i, _i, _i, _vp, _i]),
     ("flare_merge_partials", _i, [_vp, _vp, _i, _i, _i, _vp, _i]),
+    ("flare_weight_upload_q8_0", _i, [_vp, _vp, _i, _i, C.POINTER(_vp)]),
+    ("flare_weight_free", _i, [_vp]),
+    ("flare_matvec_q8_0", _i, [_vp, _vp, _vp, _i, _vp, _i]),
     ("flare_attn_comm_unique_id", _i, [_vp]),
     ("flare_attn_comm_init", _i, [_vp, _vp, _i, _i]),
     ("flare_attn_comm_enable_direct", _i, [_vp, _i, _i]),
@@ -194,6 +198,10 @@ class Engine:
         self.check(self.L.flare_attn_get_stats(self.h, C.byref(st)))
         return st
 
+    def last_path(self) -> int:
+        """Which kernel family served the most recent attention call (PATH_*)."""
+        return int(self.stats().last_path)
+
     def kv_alloc(self, num_layers, batch, max_seq_len, num_kv_heads, head_dim, dtype=KV_F32) -> "KvCache":
         return KvCache(self, num_layers, batch, max_seq_len, num_kv_heads, head_dim, dtype)
 
@@ -260,6 +268,25 @@ class Engine:
                                                int(on_device)))
         return out
 
+    # ---- Q8_0-weight projections -----------------------------------------------------------------
+    def weight_upload_q8_0(self, blocks, rows: int, cols: int) -> "Q8Weight":
+        return Q8Weight(self, blocks, rows, cols)
+
+    def matvec_q8_0(self, w: "Q8Weight", x, out=None):
+        """out[b][r] = row r of w . x[b], bit-identical to flare-core's matvec_q8_0_preq_into.  x: host ndarray
+        [batch][cols] or a device pointer (then `batch` is taken from ``out`` = (pointer, batch))."""
+        on_device = not isinstance(x, np.ndarray)
+        if on_device:
+            out_ptr, batch = out
+        else:
+            x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1, w.cols)
+            batch = x.shape[0]
+            if out is None:
+                out = np.empty((batch, w.rows), dtype=np.float32)
+            out_ptr = _ptr(out)
+        self.check(self.L.flare_matvec_q8_0(self.h, w.h, _ptr(x), batch, out_ptr, int(on_device)))
+        return out
+
     # ---- one sequence over several GPUs ------------------------------------------------------
     @staticmethod
     def comm_unique_id() -> bytes:
@@ -319,6 +346,29 @@ class Engine:
                                              num_kv_heads, head_dim, window, softcap, _ptr(out), out_dtype,
                                              int(on_device)))
         return out
+
+
+class Q8Weight:
+    """A Q8_0 weight matrix on the device (flare_weight)."""
+
+    def __init__(self, eng: Engine, blocks, rows: int, cols: int):
+        blocks = np.ascontiguousarray(blocks, dtype=np.uint8)
+        assert blocks.size == rows * (cols // 32) * 34
+        self.eng, self.L, self.rows, self.cols = eng, eng.L, rows, cols
+        h = _vp()
+        eng.check(self.L.flare_weight_upload_q8_0(eng.h, _ptr(blocks), rows, cols, C.byref(h)))
+        self.h = h
+
+    def free(self):
+        if getattr(self, "h", None) and getattr(self.eng, "h", None):
+            self.L.flare_weight_free(self.h)
+        self.h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
 
 
 class KvCache:

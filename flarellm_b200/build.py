@@ -36,10 +36,8 @@ def _stale(target, deps):
 def build(force: bool = False, verbose: bool = False, flags=(), suffix: str = "") -> str:
     """flags / suffix: a variant of the library (extra nvcc flags, e.g. -DFLARE_DEBUG_BOUNDS) built beside the
     product as libflare_attn<suffix>.so from its own object directory."""
-    global OBJ, SO
-    if suffix:
-        OBJ = os.path.join(HERE, "build" + suffix)
-        SO = os.path.join(HERE, "libflare_attn" + suffix + ".so")
+    OBJ = os.path.join(HERE, "build" + suffix)
+    SO = os.path.join(HERE, "libflare_attn" + suffix + ".so")
     os.makedirs(OBJ, exist_ok=True)
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h", ".hpp"))]
     headers.append(os.path.join(os.path.dirname(HERE), "include", "flare_attn.h"))

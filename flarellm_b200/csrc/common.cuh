@@ -62,6 +62,7 @@ struct flare_attn_ctx {
     bool stats_on = false, stats_pending = false;
     cudaEvent_t stats_ev[2] = {};
     int stats_op = 0;
+    int last_path = 0;               // flare_kernel_path of the most recent attention call
     double stats_bytes = 0.0, stats_flops = 0.0;
     double peak_hbm_gbs = 7700.0, peak_tflops = 2250.0;
     flare_attn_stats stats = {};
@@ -216,6 +217,21 @@ __device__ __forceinline__ float q2_dequant(float code, float scale, float mn) {
 __device__ __forceinline__ void flare_report(int* status_word, int code) {
     *reinterpret_cast<volatile int*>(status_word) = code;
 }
+// Range-checked build (-DFLARE_DEBUG_BOUNDS, `python -m flarellm_b200.build --variant _dbg -DFLARE_DEBUG_BOUNDS`):
+// the kernels that compute shared-memory offsets by hand (swizzled tiles, ldmatrix rows, stage rings) and the
+// records they write to global memory verify every such offset against the extent of its buffer.  A violation
+// stores FLARE_ERR_BOUNDS in the context's status word and the access is redirected to offset 0 — nothing traps,
+// nothing is read or written out of range — so the next host call that reads results reports it.  In the
+// product build the macro is the identity and costs nothing.
+#ifdef FLARE_DEBUG_BOUNDS
+__device__ __forceinline__ uint32_t flare_checked(uint32_t off, uint32_t bytes, uint32_t limit, int* status_word) {
+    if (off + bytes > limit || off + bytes < off) { flare_report(status_word, FLARE_ERR_BOUNDS); return 0u; }
+    return off;
+}
+#define FLARE_CK(off, bytes, limit, err) flare_checked((uint32_t)(off), (uint32_t)(bytes), (uint32_t)(limit), (err))
+#else
+#define FLARE_CK(off, bytes, limit, err) (off)
+#endif
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

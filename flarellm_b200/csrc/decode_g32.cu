@@ -48,7 +48,7 @@ struct G32Params {
     const unsigned char *k_codes, *v_codes, *k_res, *v_res;
     size_t codes_seq_stride, res_seq_stride;       // bytes
     const int2* ring;
-    int layer_seq0, num_heads, nkv, G, n_split;
+    int layer_seq0, num_heads, nkv, G, n_split, max_seq;
     int* err;
     uint32_t mask3;         // 0x00030003: a 2-bit code at bit 0 of both 16-bit halves
 };
@@ -233,19 +233,20 @@ __device__ __forceinline__ void g32_newest_chunk(const G32Params& p, int b, int 
     }
 }
 
-// The newest tokens [t0, t1) of a sequence — 2-bit codes for the few that are older than the residual
-// ring and that the group-aligned tile loop does not cover, then the f16 ring for the last 128.  One warp
-// per KV head on CUDA cores, 32 slots at a time with an online softmax.  Leaves (m, l, o) per head in `ws`.
-__device__ __noinline__ void g32_newest_tokens(const G32Params& p, int b, int kvh, int lane, int t0, int t1, NewestScratch* ws) {
-    const int newest = p.ring[b].x;  // ring not wrapped: slot index = token index
+// The slots of a sequence that the group-aligned tile loop does not cover: up to two runs of 2-bit codes
+// [a0, a1) and [b0, b1) (physical slots: tokens that have left the residual ring but share a tile with ring
+// tokens) and the run [r0, r1) served by the f16 ring (slot indices that are only ever used modulo 128, so a
+// run that crosses the end of a wrapped ring needs no special case).  One warp per KV head on CUDA cores, 32
+// slots at a time with an online softmax.  Leaves (m, l, o) per head in `ws`.
+__device__ __noinline__ void g32_newest_tokens(const G32Params& p, int b, int kvh, int lane, int a0, int a1, int b0, int b1,
+                                               int r0, int r1, NewestScratch* ws) {
     NewestState st;
 #pragma unroll
     for (int h = 0; h < 4; h++) { st.m[h] = -CUDART_INF_F; st.l[h] = 0.0f; st.acc[h][0] = st.acc[h][1] = 0.0f; }
-    int t_ring = newest - (FLARE_G32_RESIDUAL - 1);          // first slot that the ring serves
-    t_ring = t_ring < t0 ? t0 : (t_ring > t1 ? t1 : t_ring);
     bool have_q = false;
-    for (int c0 = t0; c0 < t_ring; c0 += 32) g32_newest_chunk<false>(p, b, kvh, lane, c0, min(32, t_ring - c0), have_q, ws, st);
-    for (int c0 = t_ring; c0 < t1; c0 += 32) g32_newest_chunk<true>(p, b, kvh, lane, c0, min(32, t1 - c0), have_q, ws, st);
+    for (int c0 = a0; c0 < a1; c0 += 32) g32_newest_chunk<false>(p, b, kvh, lane, c0, min(32, a1 - c0), have_q, ws, st);
+    for (int c0 = b0; c0 < b1; c0 += 32) g32_newest_chunk<false>(p, b, kvh, lane, c0, min(32, b1 - c0), have_q, ws, st);
+    for (int c0 = r0; c0 < r1; c0 += 32) g32_newest_chunk<true>(p, b, kvh, lane, c0, min(32, r1 - c0), have_q, ws, st);
     __syncwarp();                                       // q is dead: its place takes the outputs
 #pragma unroll
     for (int h = 0; h < 4; h++) {
@@ -255,6 +256,9 @@ __device__ __noinline__ void g32_newest_tokens(const G32Params& p, int b, int kv
     __syncwarp();
 }
 
+// WRAP: some sequence of the batch has a wrapped ring (the instantiation without it carries no ring arithmetic
+// through the tile loop).
+template <bool WRAP>
 __global__ void __launch_bounds__(256, 2) decode_g32_kernel(const __grid_constant__ CUtensorMap kmap,
                                                             const __grid_constant__ CUtensorMap vmap, G32Params p) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -272,13 +276,40 @@ __global__ void __launch_bounds__(256, 2) decode_g32_kernel(const __grid_constan
     const int stage_bytes = 2 * codes + kmeta_bytes + vmeta_bytes;
     unsigned char* sbase = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
 
-    // quantised slots of this sequence: everything older than the newest 128 tokens, in whole groups
+    // Which slots go through the tile loop (2-bit codes only, whole tiles) and which through the newest-token
+    // routine.  Ring not wrapped: slot = token index; tiles 0 .. (n - 128) / T - 1 are all codes, the rest of the
+    // n attended slots ends with the <= 128 tokens that the f16 ring serves.  Ring wrapped (every slot holds a
+    // token, the newest one in slot ring.x): the 128 ring tokens are the slots ring.x - 127 .. ring.x cyclically;
+    // the two or three tiles they touch go to the newest-token routine — ring tokens, the older codes before them
+    // in their first tile, and the OLDEST codes after ring.x in its tile — and the tile loop walks the remaining
+    // tiles starting behind that window.
     const int n = p.attend_len[b];
-    const int lim_tiles = n > 128 ? (n - 128) / T : 0;
+    const int2 ring = p.ring[b];
+    const int TT = p.max_seq / T;
+    const bool wrapped = WRAP && ring.y >= p.max_seq;
+    int lim_tiles, tile0;              // tiles of the tile loop; the first one of them (physical)
+    if (!wrapped) {
+        lim_tiles = n > 128 ? (n - 128) / T : 0;
+        tile0 = 0;
+    } else {
+        const int w0 = (ring.x - (FLARE_G32_RESIDUAL - 1) + p.max_seq) % p.max_seq;
+        const int tile_sn = ring.x / T;
+        lim_tiles = TT - (((tile_sn - w0 / T + TT) % TT) + 1);  // all but the tiles touched by the ring window
+        tile0 = (tile_sn + 1) % TT;
+    }
     if (split == p.n_split) {            // the CTA of the newest tokens: one more record per row
+        int ca0, ca1, cb0, cb1, rr0, rr1;
+        if (!wrapped) {
+            int t_ring = ring.x - (FLARE_G32_RESIDUAL - 1);          // first slot that the ring serves
+            t_ring = t_ring < lim_tiles * T ? lim_tiles * T : (t_ring > n ? n : t_ring);
+            ca0 = lim_tiles * T; ca1 = t_ring; cb0 = cb1 = 0; rr0 = t_ring; rr1 = n;
+        } else {
+            const int s_n = ring.x, w0 = (s_n - (FLARE_G32_RESIDUAL - 1) + p.max_seq) % p.max_seq;
+            ca0 = (w0 / T) * T; ca1 = w0; cb0 = s_n + 1; cb1 = (s_n / T + 1) * T; rr0 = w0; rr1 = w0 + FLARE_G32_RESIDUAL;
+        }
         pdl_wait();
         NewestScratch* ws = reinterpret_cast<NewestScratch*>(sbase) + warp;
-        g32_newest_tokens(p, b, kvh, lane, lim_tiles * T, n, ws);
+        g32_newest_tokens(p, b, kvh, lane, ca0, ca1, cb0, cb1, rr0, rr1, ws);
         pdl_trigger();
         for (int h = 0; h < p.G; h++) {
             const size_t row = (size_t)b * p.num_heads + kvh * p.G + h;
@@ -288,16 +319,16 @@ __global__ void __launch_bounds__(256, 2) decode_g32_kernel(const __grid_constan
         }
         return;
     }
-    const int t_begin = (int)(((long long)split * lim_tiles) / p.n_split);
-    const int t_end = (int)(((long long)(split + 1) * lim_tiles) / p.n_split);
-    const int n_tiles = t_end - t_begin;
+    const int t_begin = tile0 + (int)(((long long)split * lim_tiles) / p.n_split);     // may run past TT: wrapped below
+    const int n_tiles = (int)(((long long)(split + 1) * lim_tiles) / p.n_split) - (int)(((long long)split * lim_tiles) / p.n_split);
 
     const unsigned char* kmg = p.k_meta + (size_t)b * p.k_meta_seq_stride;
     const unsigned char* vmg = p.v_meta + (size_t)b * p.v_meta_seq_stride;
     auto issue = [&](int i) {
         const int s = i % STAGES;
         unsigned char* st = sbase + (size_t)s * stage_bytes;
-        const int tile = t_begin + i;
+        int tile = t_begin + i;                             // physical tile: the walk starts behind the ring window
+        if (WRAP && tile >= TT) tile -= TT;
         ptx::mbar_expect_tx(&full_bar[s], stage_bytes);
         ptx::tma_load_4d(st, &kmap, &full_bar[s], 0, tile * T, 0, p.layer_seq0 + b);
         ptx::tma_load_4d(st + codes, &vmap, &full_bar[s], 0, tile * T, 0, p.layer_seq0 + b);
@@ -377,7 +408,7 @@ __global__ void __launch_bounds__(256, 2) decode_g32_kernel(const __grid_constan
 #pragma unroll
         for (int gi = 0; gi < NG; gi++) {
             // ---- B = (q s) hi/lo for this group; the zero-point term as row 0 of one more product ---------
-            const uint4* kmeta = reinterpret_cast<const uint4*>(kmeta0 + gi * (kmeta_bytes / NG));
+            const uint4* kmeta = reinterpret_cast<const uint4*>(kmeta0 + FLARE_CK(gi * (kmeta_bytes / NG), 64, kmeta_bytes - (kvh * 4 + tig) * 64, p.err));
             uint32_t bq[4][2];
             float dz[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             {
@@ -404,8 +435,8 @@ __global__ void __launch_bounds__(256, 2) decode_g32_kernel(const __grid_constan
             // ---- scores of slots 32 gi + 16 mt + g and + 8 for head tig -----------------------------------
 #pragma unroll
             for (int mt = 0; mt < 2; mt++) {
-                const uint32_t wa = *reinterpret_cast<const uint32_t*>(kc + (32 * gi + 16 * mt + g) * 16 + 4 * tig);
-                const uint32_t wb = *reinterpret_cast<const uint32_t*>(kc + (32 * gi + 16 * mt + 8 + g) * 16 + 4 * tig);
+                const uint32_t wa = *reinterpret_cast<const uint32_t*>(kc + FLARE_CK((32 * gi + 16 * mt + g) * 16 + 4 * tig, 4, T * 16, p.err));
+                const uint32_t wb = *reinterpret_cast<const uint32_t*>(kc + FLARE_CK((32 * gi + 16 * mt + 8 + g) * 16 + 4 * tig, 4, T * 16, p.err));
                 const uint32_t wa8 = wa >> 8, wb8 = wb >> 8;
                 float d[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
@@ -439,7 +470,7 @@ __global__ void __launch_bounds__(256, 2) decode_g32_kernel(const __grid_constan
         for (int r = 0; r < 4 * NG; r++) {                  // slot 8 r + g
             const float pr = fast_exp2(sc[r] - m_run);
             l_run += pr;
-            const uint2 mv = vmeta[(size_t)(8 * r + g) * nkv];          // (scale, zero) of blocks 0 and 1
+            const uint2 mv = vmeta[FLARE_CK((8 * r + g) * nkv, 1, T * nkv - kvh, p.err)];   // (scale, zero) of blocks 0 and 1
             const float2 m0 = unpack_half2(mv.x), m1 = unpack_half2(mv.y);
             zacc0 = fmaf(pr, m0.y, zacc0);
             zacc1 = fmaf(pr, m1.y, zacc1);
@@ -449,7 +480,8 @@ __global__ void __launch_bounds__(256, 2) decode_g32_kernel(const __grid_constan
 #pragma unroll
         for (int gi = 0; gi < NG; gi++) {
             uint32_t rr[4];
-            ldmatrix_x4_trans(rr, vc + gi * 512 + lane * 16);   // matrix m = slots 32 gi + 8m .. +7, 16 bytes (64 codes) per slot
+            // matrix m = slots 32 gi + 8m .. +7, 16 bytes (64 codes) per slot
+            ldmatrix_x4_trans(rr, vc + FLARE_CK(gi * 512 + lane * 16, 16, T * 16, p.err));
 #pragma unroll
             for (int kstep = 0; kstep < 2; kstep++) {
                 const uint32_t r0 = rr[2 * kstep], r1 = rr[2 * kstep + 1];
@@ -508,41 +540,21 @@ __global__ void __launch_bounds__(256, 2) decode_g32_kernel(const __grid_constan
     if (g == 0) { wrec[0] = m_run; wrec[1] = l_run; }
 }
 
-// merge of the records of a row (m in log2 units, l, unnormalised o) into the attention output
-__global__ void __launch_bounds__(HD) merge_g32_kernel(const float* __restrict__ work, int n_rec, float* __restrict__ out) {
-    __shared__ float s_m[264], s_l[264];
-    pdl_wait();
-    const int row = blockIdx.x, d = threadIdx.x;
-    const float* base = work + (size_t)row * n_rec * (HD + 2);
-    for (int r = d; r < n_rec; r += HD) { s_m[r] = base[r * (HD + 2)]; s_l[r] = base[r * (HD + 2) + 1]; }
-    __syncthreads();
-    float mm = -CUDART_INF_F;
-    for (int r = 0; r < n_rec; r++)
-        if (s_l[r] > 0.0f) mm = fmaxf(mm, s_m[r]);
-    float ll = 0.0f, a = 0.0f;
-#pragma unroll 8
-    for (int r = 0; r < n_rec; r++) {
-        const float w = s_l[r] > 0.0f ? fast_exp2(s_m[r] - mm) : 0.0f;
-        ll = fmaf(s_l[r], w, ll);
-        a = fmaf(base[r * (HD + 2) + 2 + d], w, a);
-    }
-    out[(size_t)row * HD + d] = ll > 0.0f ? a / ll : 0.0f;
-}
-
 }  // namespace
 
 bool flare_decode_g32_supported(const DecodeArgs& a, const flare_kv* kv) {
     if (a.kv.dtype != FLARE_KV_KIVI_G32 || a.kv.head_dim != 64 || a.n_q != 1 || a.kv.num_kv_heads > 8 ||
         a.num_heads / a.kv.num_kv_heads > 4 || !kv->has_g32_maps || a.slot_end >= 0 || a.want_partial || a.window > 0)
         return false;
-    // the quantised slots form a prefix only while the ring has not wrapped; and it has to be worth it
+    // a wrapped ring is served when the whole ring is attended (what the ring state gives once it is full)
     for (int b = 0; b < kv->batch; b++)
-        if (kv->length[b] + a.n_q > kv->max_seq_len) return false;
+        if (kv->length[b] >= kv->max_seq_len && (!a.h_attend || a.h_attend[b] != kv->max_seq_len)) return false;
+    // and it has to be worth it
     return a.max_attend >= 1024;
 }
 
 // One CTA per (sequence, slot range of the quantised prefix) plus one per sequence for the newest tokens,
-// then the merge of their records into a.out.
+// then the merge of their records into a.out (the kernel shared with the other split paths, multi.cu).
 int flare_launch_decode_g32(flare_attn_ctx* ctx, const DecodeArgs& a, const flare_kv* kv) {
     const int nkv = a.kv.num_kv_heads, rows = a.batch * a.num_heads;
     G32Params p;
@@ -558,7 +570,7 @@ int flare_launch_decode_g32(flare_attn_ctx* ctx, const DecodeArgs& a, const flar
     p.v_res = reinterpret_cast<const unsigned char*>(a.kv.plane[FLARE_PLANE_V_RES]);
     p.res_seq_stride = a.kv.stride[FLARE_PLANE_K_RES];
     p.layer_seq0 = a.layer * a.batch;
-    p.num_heads = a.num_heads; p.nkv = nkv; p.G = a.num_heads / nkv;
+    p.num_heads = a.num_heads; p.nkv = nkv; p.G = a.num_heads / nkv; p.max_seq = a.kv.max_seq_len;
     p.err = ctx->d_err;
     p.mask3 = 0x00030003u;
     const size_t stage = 2 * (size_t)nkv * T * 16 + (size_t)NG * nkv * HD * 4 + (size_t)T * nkv * 2 * 4;
@@ -580,8 +592,9 @@ int flare_launch_decode_g32(flare_attn_ctx* ctx, const DecodeArgs& a, const flar
         std::lock_guard<std::mutex> lock(attr_mutex);
         static bool attr_done[64] = {};
         if (!attr_done[ctx->device & 63]) {
-            FLARE_CUDA_OK(ctx, cudaFuncSetAttribute(decode_g32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                    (int)(STAGES * (2 * 8 * T * 16 + NG * 8 * HD * 4 + T * 8 * 2 * 4) + 128)));
+            const int max_smem = (int)(STAGES * (2 * 8 * T * 16 + NG * 8 * HD * 4 + T * 8 * 2 * 4) + 128);
+            FLARE_CUDA_OK(ctx, cudaFuncSetAttribute(decode_g32_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
+            FLARE_CUDA_OK(ctx, cudaFuncSetAttribute(decode_g32_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
             attr_done[ctx->device & 63] = true;
         }
     }
@@ -597,16 +610,13 @@ int flare_launch_decode_g32(flare_attn_ctx* ctx, const DecodeArgs& a, const flar
     cfg.stream = ctx->stream;
     cfg.attrs = attr;
     cfg.numAttrs = ctx->last_launch_overlappable ? 1 : 0;
-    FLARE_CUDA_OK(ctx, cudaLaunchKernelEx(&cfg, decode_g32_kernel, kv->g32_kmap, kv->g32_vmap, p));
+    bool any_wrapped = false;
+    for (int b = 0; b < kv->batch; b++) any_wrapped = any_wrapped || kv->length[b] >= kv->max_seq_len;
+    if (any_wrapped) FLARE_CUDA_OK(ctx, cudaLaunchKernelEx(&cfg, decode_g32_kernel<true>, kv->g32_kmap, kv->g32_vmap, p));
+    else FLARE_CUDA_OK(ctx, cudaLaunchKernelEx(&cfg, decode_g32_kernel<false>, kv->g32_kmap, kv->g32_vmap, p));
     FLARE_LAUNCH_CHECK(ctx);
-    cudaLaunchConfig_t mcfg = {};
-    mcfg.gridDim = dim3(rows);
-    mcfg.blockDim = dim3(HD);
-    mcfg.stream = ctx->stream;
-    mcfg.attrs = attr;
-    mcfg.numAttrs = 1;
-    FLARE_CUDA_OK(ctx, cudaLaunchKernelEx(&mcfg, merge_g32_kernel, (const float*)p.work, n_split + 1, a.out));
-    FLARE_LAUNCH_CHECK(ctx);
+    // log-sum-exp merge of the slot ranges and the newest-token record, chained with programmatic dependent launch
+    FLARE_TRY(flare_launch_merge_splits(ctx, p.work, n_split + 1, rows, HD, a.out, 0));
     ctx->last_launch_overlappable = true;
     return FLARE_OK;
 }

@@ -70,7 +70,6 @@ struct Q8Params {
     int attend_small[64];
     int n_q, causal_q, hgroups;   // grid.z = n_q * hgroups: one query and one group of up to 4 of its heads per kv head
     int cluster;             // the n_split CTAs of a sequence form one thread-block cluster and merge through shared memory
-    int rec_overlap;         // the cluster's record area reuses the stage buffers (no room behind them)
     int whole_rows;             // 1: the maps deliver all heads of a tile in one copy; 0: one copy per head
     int* err;
 };
@@ -125,11 +124,8 @@ __device__ __forceinline__ void cluster_sync_all() {
 __device__ __forceinline__ uint32_t cluster_map(uint32_t smem_addr, uint32_t cta_rank) {
     uint32_t r; asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(cta_rank)); return r;
 }
-__device__ __forceinline__ void cluster_st(uint32_t addr, float v) {
-    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
-}
-__device__ __forceinline__ void cluster_st4(uint32_t addr, float a, float b, float c, float d) {
-    asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+__device__ __forceinline__ float cluster_ld(uint32_t addr) {
+    float v; asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory"); return v;
 }
 
 template <int HD>
@@ -315,15 +311,15 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
 #pragma unroll
             for (int h = 0; h < NB / 2; h++) {
                 // (blk 2h, blk 2h+1) scales of slots 8j + 2tig and 8j + 2tig + 1
-                const float2 kf0 = unpack_half2(*reinterpret_cast<const uint32_t*>(kt + ksoff + (8 * j * bpr + 2 * h) * 2));
-                const float2 kf1 = unpack_half2(*reinterpret_cast<const uint32_t*>(kt + ksoff + ((8 * j + 1) * bpr + 2 * h) * 2));
-                vs[h][j][0] = __half2float(*reinterpret_cast<const __half*>(kt + vsoff + (8 * j * bpr + 2 * h) * 2));
-                vs[h][j][1] = __half2float(*reinterpret_cast<const __half*>(kt + vsoff + ((8 * j + 1) * bpr + 2 * h) * 2));
+                const float2 kf0 = unpack_half2(*reinterpret_cast<const uint32_t*>(kt + FLARE_CK(ksoff + (8 * j * bpr + 2 * h) * 2, 4, stage_bytes, p.err)));
+                const float2 kf1 = unpack_half2(*reinterpret_cast<const uint32_t*>(kt + FLARE_CK(ksoff + ((8 * j + 1) * bpr + 2 * h) * 2, 4, stage_bytes, p.err)));
+                vs[h][j][0] = __half2float(*reinterpret_cast<const __half*>(kt + FLARE_CK(vsoff + (8 * j * bpr + 2 * h) * 2, 2, stage_bytes, p.err)));
+                vs[h][j][1] = __half2float(*reinterpret_cast<const __half*>(kt + FLARE_CK(vsoff + ((8 * j + 1) * bpr + 2 * h) * 2, 2, stage_bytes, p.err)));
 #pragma unroll
                 for (int bb = 0; bb < 2; bb++) {
                     const int blk = 2 * h + bb;
                     // B fragment: 8 contiguous bytes of slot 8j+g, channels blk*32 + 8*tig .. +7
-                    const uint2 kb = *reinterpret_cast<const uint2*>(kt + koff[blk] + j * 8 * HD);
+                    const uint2 kb = *reinterpret_cast<const uint2*>(kt + FLARE_CK(koff[blk] + j * 8 * HD, 8, payload, p.err));
                     int d[4] = {0, 0, 0, 0};
                     mma_s8(d, qa[blk], kb.x, kb.y);
                     // rows g / g+8 = limb 0 / limb 1 of head g & 3; columns = slots 2tig, 2tig+1
@@ -402,7 +398,8 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
 #pragma unroll
                 for (int cp = 0; cp < 2; cp++) {          // chunk pairs of this M-tile's 64 channels
                     uint32_t rr[4];
-                    ldmatrix_x4_trans(rr, vt + voff[mt][cp] + kstep * 16 * HD);
+                    // a row of 16 bytes per lane, inside this head's V tile
+                    ldmatrix_x4_trans(rr, vt + FLARE_CK(voff[mt][cp] + kstep * 16 * HD, 16, 2 * payload, p.err));
 #pragma unroll
                     for (int k = 0; k < 4; k++) rr[k] ^= 0x80808080u;     // int8 -> uint8 (v + 128)
                     // bytes (slot a, ch 0), (slot a, ch 1), (slot a+1, ch 0), (slot a+1, ch 1) ->
@@ -447,60 +444,62 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
         lb[mt] += __shfl_xor_sync(0xffffffffu, lb[mt], 2);
     }
     if (p.cluster) {
-        // The splits of this sequence are the CTAs of one cluster.  Row r of the sequence (a query head) is merged
-        // by CTA r % n: every CTA stores its (o, m, l) record of the row straight into that CTA's shared memory
-        // (distributed shared memory, slot [r / n][own rank]), one cluster barrier makes the stores visible, and
-        // each CTA merges the rows it owns out of its own shared memory.  The record area lies behind the stage
-        // buffers, so that a fast CTA may deliver while the owner is still streaming; where shared memory has no
-        // room for that (head_dim 128) it reuses the stage buffers after one more barrier.  After the last barrier
-        // nobody touches another CTA's memory, so a CTA may leave as soon as it has written its rows.
-        constexpr int RS = HD + 4;                          // floats per record: o[HD], m, l, padding (16-byte rows)
-        const uint32_t rank = cluster_ctarank(), n = (uint32_t)p.n_split;
-        float* rec = reinterpret_cast<float*>(sbase + (p.rec_overlap ? 0 : (size_t)STAGES * stage_bytes));   // [rows owned][n][RS]
-        if (p.rec_overlap) cluster_sync_all();              // no room behind the stages: wait until every CTA has finished streaming
+        // The splits of this sequence are the CTAs of one cluster: every CTA leaves its (m, l, o) records
+        // in its own shared memory, then each merges a share of the rows by reading its peers' records.
+        __syncthreads();                                    // all warps are done with the stage buffers
+        float* rec = reinterpret_cast<float*>(sbase);       // [num_heads][HD + 2]
         if (head_ok) {
-            const uint32_t r = (uint32_t)(kvh * p.G + hq), owner = r % n, k = r / n;
-            const uint32_t dst = cluster_map(ptx::smem_u32(rec) + ((k * n + rank) * RS) * 4, owner);
+            float* r = rec + (kvh * p.G + hq) * (HD + 2);
 #pragma unroll
             for (int mt = 0; mt < MT; mt++) {
                 const float bias = 1152.0f * lb[mt];
 #pragma unroll
                 for (int lc = 0; lc < 2; lc++) {
                     const int d0 = 64 * mt + 16 * (2 * lane_blk + lc) + 4 * tig;
-                    cluster_st4(dst + d0 * 4,
-                                (lane_blk ? acc[mt][2 + lc][0][0] : acc[mt][lc][0][0]) - bias,
-                                (lane_blk ? acc[mt][2 + lc][1][0] : acc[mt][lc][1][0]) - bias,
-                                (lane_blk ? acc[mt][2 + lc][0][1] : acc[mt][lc][0][1]) - bias,
-                                (lane_blk ? acc[mt][2 + lc][1][1] : acc[mt][lc][1][1]) - bias);
+                    r[2 + d0] = (lane_blk ? acc[mt][2 + lc][0][0] : acc[mt][lc][0][0]) - bias;
+                    r[2 + d0 + 1] = (lane_blk ? acc[mt][2 + lc][1][0] : acc[mt][lc][1][0]) - bias;
+                    r[2 + d0 + 2] = (lane_blk ? acc[mt][2 + lc][0][1] : acc[mt][lc][0][1]) - bias;
+                    r[2 + d0 + 3] = (lane_blk ? acc[mt][2 + lc][1][1] : acc[mt][lc][1][1]) - bias;
                 }
             }
-            if (g < 4 && tig == 0) { cluster_st(dst + HD * 4, m_run); cluster_st(dst + (HD + 1) * 4, failed ? 0.0f : l_run); }
+            if (g < 4 && tig == 0) { r[0] = m_run; r[1] = failed ? 0.0f : l_run; }
         }
         cluster_sync_all();
-        TL_STAMP(6);        // every CTA of the cluster has delivered its records
-        const int owned = ((int)p.num_heads - (int)rank + (int)n - 1) / (int)n;        // rows rank, rank + n, ...
-        for (int item = threadIdx.x; item < owned * HD; item += blockDim.x) {
-            const int k = item / HD, d = item % HD;
-            const float* rk = rec + (size_t)k * n * RS;
-            float mm = -CUDART_INF_F;
-            for (uint32_t s2 = 0; s2 < n; s2++)
-                if (rk[s2 * RS + HD + 1] > 0.0f) mm = fmaxf(mm, rk[s2 * RS + HD]);
-            float ll = 0.0f, o = 0.0f;
-            for (uint32_t s2 = 0; s2 < n; s2++) {
-                const float l2 = rk[s2 * RS + HD + 1];
-                const float w = l2 > 0.0f ? fast_exp2(rk[s2 * RS + HD] - mm) : 0.0f;
-                ll = fmaf(l2, w, ll);
-                o = fmaf(rk[s2 * RS + d], w, o);
+        const uint32_t rank = cluster_ctarank(), n = (uint32_t)p.n_split;
+        const uint32_t rec0 = ptx::smem_u32(rec);
+        for (int item = threadIdx.x;; item += blockDim.x) {
+            const int r = (int)rank + (item / HD) * (int)n, d = item % HD;
+            if (r >= p.num_heads) break;
+            float mv[8], lv[8], ov[8];
+#pragma unroll
+            for (uint32_t s2 = 0; s2 < 8; s2++) {
+                if (s2 < n) {
+                    const uint32_t a = cluster_map(rec0 + (uint32_t)r * (HD + 2) * 4, s2);
+                    mv[s2] = cluster_ld(a); lv[s2] = cluster_ld(a + 4); ov[s2] = cluster_ld(a + (2 + d) * 4);
+                } else { mv[s2] = 0.0f; lv[s2] = 0.0f; ov[s2] = 0.0f; }
             }
-            p.out[((size_t)b * p.num_heads + rank + (size_t)k * n) * HD + d] = ll > 0.0f ? o / ll : 0.0f;
+            float mm = -CUDART_INF_F;
+#pragma unroll
+            for (int s2 = 0; s2 < 8; s2++) if (lv[s2] > 0.0f) mm = fmaxf(mm, mv[s2]);
+            float ll = 0.0f, o = 0.0f;
+#pragma unroll
+            for (int s2 = 0; s2 < 8; s2++) {
+                const float w = lv[s2] > 0.0f ? fast_exp2(mv[s2] - mm) : 0.0f;
+                ll = fmaf(lv[s2], w, ll);
+                o = fmaf(ov[s2], w, o);
+            }
+            p.out[((size_t)b * p.num_heads + r) * HD + d] = ll > 0.0f ? o / ll : 0.0f;
         }
-        TL_STAMP(7);
+        cluster_sync_all();                                 // nobody leaves while a peer still reads its records
         return;
     }
     if (!head_ok) return;
     const bool final_out = (p.n_split == 1) && !p.want_partial;
     const float inv_l = l_run > 0.0f ? 1.0f / l_run : 0.0f;
     float* wrec = p.work + (row * p.n_split + split) * (HD + 2);
+#ifdef FLARE_DEBUG_BOUNDS
+    if (row >= (size_t)gridDim.y * p.n_q * p.num_heads || split >= p.n_split) { flare_report(p.err, FLARE_ERR_BOUNDS); return; }
+#endif
 #pragma unroll
     for (int mt = 0; mt < MT; mt++) {
         const float bias = 1152.0f * lb[mt];
@@ -569,65 +568,50 @@ int flare_launch_decode_q8(flare_attn_ctx* ctx, const DecodeArgs& a) {
     if (n_split < 1) n_split = 1;
     if (n_split > 256) n_split = 256;
     // Cluster mode: when a handful of splits per sequence fill the GPU anyway, the splits of a sequence become one
-    // thread-block cluster (2 .. 16 CTAs; more than 8 is the non-portable size the kernel opts in to) and merge
-    // through distributed shared memory: no second kernel, no round trip of the records through global memory.
-    // The size is the largest one for which every sequence's cluster is resident at once: with 32 sequences
-    // 9 CTAs each put two CTAs on (nearly) every SM, where 8 leave 40 of the 296 places empty and the SMs
-    // unevenly loaded.
+    // thread-block cluster (2 .. 8 CTAs) and merge through distributed shared memory: no second kernel, no round
+    // trip of the records through global memory.  The size is the largest one, not far below the number of splits
+    // that would fit, for which every sequence's cluster is resident at once (a second wave costs more than the
+    // merge kernel).  Measured and rejected: clusters of 9 for 32 sequences (only 30 are resident at once); records
+    // pushed into the owner's shared memory with a single cluster barrier (warps that reach the cluster barrier
+    // early poll it and slow the warps still streaming: 37.8 instead of 32.1 us per call).
     int cluster = 0;
-    p.rec_overlap = 0;
-    size_t rec_bytes = 0;          // record area of a cluster CTA: [rows it owns][cluster size][head_dim + 4] floats
     if (!a.want_partial && a.slot_end < 0 && n_split >= 2 && chunks == 1) {
         std::lock_guard<std::mutex> lock(g_table_mutex);
-        // [device][hd == 128][size]: 0 = not asked yet.  Asked with the shapes of the first call (number of heads,
-        // kv heads); other shapes of the same head size have smaller or equal footprints in practice
-        static int max_clusters[64][2][17][2] = {};        // last index: record area behind the stages / over them
+        // [device][hd == 128][size]: 0 = not asked yet.  Asked with the shapes of the first call (number of kv
+        // heads); other shapes of the same head size have smaller or equal footprints
+        static int max_clusters[64][2][9] = {};
         static bool attr_set[64][2] = {};
         bool& as = attr_set[ctx->device & 63][hd == 128];
         if (!as) {
-            // the opt-ins have to precede the occupancy queries
-            int max_smem = STAGES * (8 * 2 * T * hd + 2 * T * 8 * (hd / 32) * 2) + 1024 + (32 + 16) * (hd + 4) * 4;
-            if (max_smem > 225 * 1024) max_smem = 225 * 1024;      // a CTA can opt in to 227 KB, static shared memory included
-            if (hd == 64) {
-                cudaFuncSetAttribute(decode_q8_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
-                cudaFuncSetAttribute(decode_q8_kernel<64>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
-            } else {
-                cudaFuncSetAttribute(decode_q8_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
-                cudaFuncSetAttribute(decode_q8_kernel<128>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
-            }
+            // the opt-in to large dynamic shared memory has to precede the occupancy queries
+            const int max_smem = STAGES * (8 * 2 * T * hd + 2 * T * 8 * (hd / 32) * 2) + 1024;
+            if (hd == 64) cudaFuncSetAttribute(decode_q8_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+            else cudaFuncSetAttribute(decode_q8_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
             cudaGetLastError();
             as = true;
         }
-        int c_first = n_split > 16 ? 16 : n_split;
+        int c_first = n_split > 8 ? 8 : n_split;
         bool forced = false;
 #ifdef FLARE_TUNE
-        if (const char* e = getenv("FLARE_Q8_CLUSTER")) { c_first = atoi(e); forced = true; }     // 0 or 1: no cluster
+        if (const char* e = getenv("FLARE_Q8_CLUSTER")) { c_first = atoi(e) > 8 ? 8 : atoi(e); forced = true; }     // 0 or 1: no cluster
 #endif
         for (int c = c_first; c >= 2 && !cluster; c--) {
             if (c * 5 < n_split * 4 && !forced) break;            // far fewer CTAs than places: the merge kernel is cheaper
-            const size_t rb = (size_t)((a.num_heads + c - 1) / c) * c * (hd + 4) * sizeof(float);
-            for (int ov = 0; ov < 2 && !cluster; ov++) {
-                int& mc = max_clusters[ctx->device & 63][hd == 128][c][ov];
-                if (mc == 0) {
-                    cudaLaunchAttribute ca[1];
-                    ca[0].id = cudaLaunchAttributeClusterDimension;
-                    ca[0].val.clusterDim.x = c; ca[0].val.clusterDim.y = 1; ca[0].val.clusterDim.z = 1;
-                    cudaLaunchConfig_t qc = {};
-                    qc.gridDim = dim3(c, 1); qc.blockDim = dim3(32 * nkv);
-                    qc.dynamicSmemBytes = smem + (ov ? 0 : rb);
-                    qc.attrs = ca; qc.numAttrs = 1;
-                    int n = 0;
-                    cudaError_t e = hd == 64 ? cudaOccupancyMaxActiveClusters(&n, decode_q8_kernel<64>, &qc)
-                                             : cudaOccupancyMaxActiveClusters(&n, decode_q8_kernel<128>, &qc);
-                    if (e != cudaSuccess) { cudaGetLastError(); n = 0; }
-                    mc = n > 0 ? n : -1;
-#ifdef FLARE_TUNE
-                    fprintf(stderr, "[flare tune] cluster size %d (records %s the stages): %d clusters resident (hd %d, %d kv heads)\n",
-                            c, ov ? "over" : "behind", n, hd, nkv);
-#endif
-                }
-                if (mc >= a.batch) { cluster = c; rec_bytes = ov ? 0 : rb; p.rec_overlap = ov; }
+            int& mc = max_clusters[ctx->device & 63][hd == 128][c];
+            if (mc == 0) {
+                cudaLaunchAttribute ca[1];
+                ca[0].id = cudaLaunchAttributeClusterDimension;
+                ca[0].val.clusterDim.x = c; ca[0].val.clusterDim.y = 1; ca[0].val.clusterDim.z = 1;
+                cudaLaunchConfig_t qc = {};
+                qc.gridDim = dim3(c, 1); qc.blockDim = dim3(32 * nkv); qc.dynamicSmemBytes = smem;
+                qc.attrs = ca; qc.numAttrs = 1;
+                int n = 0;
+                cudaError_t e = hd == 64 ? cudaOccupancyMaxActiveClusters(&n, decode_q8_kernel<64>, &qc)
+                                         : cudaOccupancyMaxActiveClusters(&n, decode_q8_kernel<128>, &qc);
+                if (e != cudaSuccess) { cudaGetLastError(); n = 0; }
+                mc = n > 0 ? n : -1;
             }
+            if (mc >= a.batch) cluster = c;
         }
     }
     if (cluster) n_split = cluster;
@@ -649,8 +633,7 @@ int flare_launch_decode_q8(flare_attn_ctx* ctx, const DecodeArgs& a) {
         static bool attr_done[64][2] = {};
         bool& done = attr_done[ctx->device & 63][hd == 128];
         if (!done) {
-            int max_smem = STAGES * (8 * 2 * T * hd + 2 * T * 8 * (hd / 32) * 2) + 1024 + (32 + 16) * (hd + 4) * 4;
-            if (max_smem > 225 * 1024) max_smem = 225 * 1024;      // a CTA can opt in to 227 KB, static shared memory included
+            const int max_smem = STAGES * (8 * 2 * T * hd + 2 * T * 8 * (hd / 32) * 2) + 1024;
             if (hd == 64) FLARE_CUDA_OK(ctx, cudaFuncSetAttribute(decode_q8_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
             else FLARE_CUDA_OK(ctx, cudaFuncSetAttribute(decode_q8_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
             done = true;
@@ -667,7 +650,7 @@ int flare_launch_decode_q8(flare_attn_ctx* ctx, const DecodeArgs& a) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(n_split, a.batch, chunks);
     cfg.blockDim = dim3(32 * nkv);
-    cfg.dynamicSmemBytes = smem + rec_bytes;
+    cfg.dynamicSmemBytes = smem;
     cfg.stream = ctx->stream;
     // the attributes in use are a contiguous run of attr[]: [PDL][cluster]
     cfg.attrs = ctx->last_launch_overlappable ? attr : attr + 1;

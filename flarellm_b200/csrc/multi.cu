@@ -229,8 +229,11 @@ __global__ void __launch_bounds__(256) merge_exchange_kernel(const float* __rest
         st_word(mp.rec[r] + my_slot + i, s_send[i], mp.seq);
     }
     TLX_STAMP(3);
-    // ---- every rank's record of this (row, chunk) out of the own buffer: a word is there when its number matches
+    // ---- every rank's record of this (row, chunk) out of the own buffer: a word is there when its number matches.
+    // Once a wait has run out on this context (status word set, not yet read and cleared by the host) the ranks are
+    // out of step: the calls still queued behind it do not wait their full limit again, they give up at once.
     const unsigned long long t0 = global_ns();
+    const unsigned long long limit = (*reinterpret_cast<volatile int*>(mp.err) != 0) ? 0ull : mp.wait_ns;
     for (int t = tid; t < WORDS * mp.world; t += blockDim.x) {
         const int r = t / WORDS, i = t % WORDS;
         const uint2* src = mp.rec[mp.rank] + ((((size_t)mp.phase * mp.world + r) * mp.rows_max + row) * mp.chunks_max + chunk) * slot_words + i;
@@ -238,7 +241,7 @@ __global__ void __launch_bounds__(256) merge_exchange_kernel(const float* __rest
         for (;;) {
             const uint2 v = ld_word(src);
             if (v.y == mp.seq) { s_recv[r][i] = __uint_as_float(v.x); ok = true; break; }
-            if (global_ns() - t0 > mp.wait_ns) break;
+            if (global_ns() - t0 > limit) break;
             __nanosleep(40);
         }
         if (!ok) s_fail = 1;
@@ -476,6 +479,10 @@ int flare_decode_attn_splitkv_multi(flare_attn_ctx* ctx, flare_kv* kv, int layer
         if (api && api->CommGetAsyncError(ctx->comm->comm, &ar) == ncclSuccess && ar != ncclSuccess && ar != ncclInProgress)
             return flare_set_error(ctx, FLARE_ERR_NCCL, "the communicator reported an asynchronous error: %s", api->GetErrorString(ar));
     }
+    if (ctx->comm && ctx->comm->world > 1 && *reinterpret_cast<volatile int*>(ctx->h_err) != 0)
+        return flare_set_error(ctx, *reinterpret_cast<volatile int*>(ctx->h_err),
+                               "an earlier multi-GPU call on this context gave up waiting for a peer rank; read the status "
+                               "(flare_attn_sync) and re-create the communicator on every rank before calling again");
     std::vector<int> att(kv->batch, n_local_slots);
     return flare_decode_common(ctx, kv, layer, num_heads, q, 1, att.data(), 0.0f, 0, n_local_slots, 1, 0, out, on_device,
                                nullptr, 1);

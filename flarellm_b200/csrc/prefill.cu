@@ -123,6 +123,7 @@ int flare_launch_prefill(flare_attn_ctx* ctx, const PrefillArgs& a) {
             }
             if (a.out_dtype == FLARE_DT_BF16) out = w;
         }
+        ctx->last_path = FLARE_PATH_GENERAL;
         FLARE_TRY(prefill_generic(ctx, a, q, k, v, out));
         if (a.out_dtype == FLARE_DT_BF16) {
             f32_to_bf16_kernel<<<conv_grid, conv_threads, 0, ctx->stream>>>(out, (__nv_bfloat16*)a.out, qn);
@@ -158,5 +159,6 @@ int flare_launch_prefill(flare_attn_ctx* ctx, const PrefillArgs& a) {
         make_qkv_map(&vm, v, a.head_dim, a.num_kv_heads, a.seq_len, a.batch, f16))
         return flare_set_error(ctx, FLARE_ERR_CUDA, "cuTensorMapEncodeTiled failed for the prefill operands (are they 16-byte aligned?)");
     a2.q = q; a2.k = k; a2.v = v;
+    ctx->last_path = FLARE_PATH_PREFILL_TENSOR;
     return flare_launch_prefill_pp(ctx, qm, km, vm, a2);
 }

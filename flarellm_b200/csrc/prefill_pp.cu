@@ -190,12 +190,12 @@ __global__ void __launch_bounds__(320, 1) prefill_pp_kernel(const __grid_constan
                 if (aborted) break;
                 ptx::mbar_expect_tx(&bars->k_full[sk], L::KV_BYTES);
                 for (int pn = 0; pn < L::PANELS; pn++)
-                    ptx::tma_load_4d(sm + L::K_OFF + sk * L::KV_BYTES + pn * (BN * 128), &kmap, &bars->k_full[sk], pn * 64, kvh, row, b);
+                    ptx::tma_load_4d(sm + FLARE_CK(L::K_OFF + sk * L::KV_BYTES + pn * (BN * 128), BN * 128, L::V_OFF, p.err), &kmap, &bars->k_full[sk], pn * 64, kvh, row, b);
                 if (t >= 2) PP_WAIT(&bars->v_empty[s], (uint32_t)(((t >> 1) - 1) & 1));
                 if (aborted) break;
                 ptx::mbar_expect_tx(&bars->v_full[s], L::KV_BYTES);
                 for (int pn = 0; pn < L::PANELS; pn++)
-                    ptx::tma_load_4d(sm + L::V_OFF + s * L::KV_BYTES + pn * (BN * 128), &vmap, &bars->v_full[s], pn * 64, kvh, row, b);
+                    ptx::tma_load_4d(sm + FLARE_CK(L::V_OFF + s * L::KV_BYTES + pn * (BN * 128), BN * 128, L::TOTAL, p.err), &vmap, &bars->v_full[s], pn * 64, kvh, row, b);
             }
         }
     } else if (warp == 8) {
@@ -207,8 +207,8 @@ __global__ void __launch_bounds__(320, 1) prefill_pp_kernel(const __grid_constan
             auto in_range = [&](int x, int j) { return x == 0 ? (j >= jA0 && j < jA1) : (j >= jB0 && j < jB1); };
             auto qk = [&](int x, int t) {      // S_x = Q_x K_t^T
                 const int s = t % KS;
-                const uint32_t q_addr = ptx::smem_u32(sm + L::Q_OFF + x * L::Q_BYTES);
-                const uint32_t k_addr = ptx::smem_u32(sm + L::K_OFF + s * L::KV_BYTES);
+                const uint32_t q_addr = ptx::smem_u32(sm + FLARE_CK(L::Q_OFF + x * L::Q_BYTES, L::Q_BYTES, L::K_OFF, p.err));
+                const uint32_t k_addr = ptx::smem_u32(sm + FLARE_CK(L::K_OFF + s * L::KV_BYTES, L::KV_BYTES, L::V_OFF, p.err));
 #pragma unroll
                 for (int k = 0; k < HD / 16; k++) {
                     const uint64_t ad = desc_kmajor(q_addr + (k >> 2) * (BM * 128) + (k & 3) * 32);
@@ -219,7 +219,7 @@ __global__ void __launch_bounds__(320, 1) prefill_pp_kernel(const __grid_constan
             };
             auto pv = [&](int x, int t, bool first) {      // O_x (+)= P_x V_t, P_x in columns [0,64) of S_x
                 const int s = t & 1;
-                const uint32_t v_addr = ptx::smem_u32(sm + L::V_OFF + s * L::KV_BYTES);
+                const uint32_t v_addr = ptx::smem_u32(sm + FLARE_CK(L::V_OFF + s * L::KV_BYTES, L::KV_BYTES, L::TOTAL, p.err));
 #pragma unroll
                 for (int k = 0; k < BN / 16; k++) {
                     const uint64_t bd = desc_mnmajor(v_addr + k * 2048, BN * 128);
@@ -373,6 +373,9 @@ __global__ void __launch_bounds__(320, 1) prefill_pp_kernel(const __grid_constan
                 uint32_t o[32];
                 tmem_ld32(tO + ch * 32, o);
                 tmem_wait_ld();
+#ifdef FLARE_DEBUG_BOUNDS
+                if (grow < S && (size_t)(orow + ch * 32 + 32) > (size_t)p.batch * S * p.num_heads * HD) flare_report(p.err, FLARE_ERR_BOUNDS);
+#endif
                 if (grow < S) {
                     if (p.out_dtype == FLARE_DT_F32) {
                         float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + orow + ch * 32);

@@ -123,10 +123,18 @@ FLARE_API const char* flare_attn_backend_name(void);
  *           tensor peak for prefill; peaks are the caller's (flare_attn_set_peaks), default 7700 GB/s
  *           and 2250 TFLOP/s (nominal B200). */
 typedef enum { FLARE_OP_NONE = 0, FLARE_OP_DECODE = 1, FLARE_OP_PREFILL = 2 } flare_stat_op;
+/* Which kernel family served the last attention call of the context (whether or not stats are enabled). */
+typedef enum {
+    FLARE_PATH_NONE = 0,
+    FLARE_PATH_GENERAL = 1,        /* CUDA-core split-KV kernel: every cache type and shape */
+    FLARE_PATH_Q8_TENSOR = 2,      /* Q8_0, head_dim 64 / 128: TMA-staged tiles, int8 / f16 tensor-core products */
+    FLARE_PATH_KIVI_TENSOR = 3,    /* group-32 2-bit cache, head_dim 64: TMA-staged code tiles, f16 tensor-core products */
+    FLARE_PATH_PREFILL_TENSOR = 4  /* prefill, head_dim 64 / 128: tcgen05 / tensor-memory kernel */
+} flare_kernel_path;
 typedef struct {
     uint64_t calls;                /* measured calls so far */
     int32_t last_op;               /* flare_stat_op */
-    int32_t reserved;
+    int32_t last_path;             /* flare_kernel_path of the most recent attention call */
     double last_elapsed_us, last_bytes, last_flops, last_gbs, last_tflops, last_frac_of_peak;
     double total_elapsed_us, total_bytes, total_flops;
 } flare_attn_stats;
@@ -250,8 +258,10 @@ FLARE_API int flare_decode_attn(flare_attn_ctx* ctx, flare_kv* kv, int layer, in
  * key/value ([batch][kv_dim], post-RoPE) is stored at sequence b's current ring position exactly as
  * flare_kv_write_step_f32 does, then q ([batch][1][num_heads][head_dim]) attends min(length + 1,
  * max_seq_len) slots exactly as flare_decode_attn does.  The ring state is not advanced.  With host
- * buffers the three inputs cross the bus in one staged transfer (or straight from the caller's
- * buffers when those are page-locked) and the call synchronises once, when `out` is filled. */
+ * buffers the call synchronises once, when `out` is filled, and the inputs cross the bus in as few
+ * transfers as their memory allows: one, straight from the caller's memory, when they are page-locked
+ * and contiguous as [K rows][V rows][q]; three when page-locked but apart; one through a page-locked
+ * staging slot of the library when pageable.  A page-locked `out` is written by the kernel itself. */
 FLARE_API int flare_decode_step(flare_attn_ctx* ctx, flare_kv* kv, int layer, int num_heads,
                                 const float* key, const float* value, const float* q, float* out,
                                 int on_device);
@@ -297,6 +307,27 @@ FLARE_API int flare_decode_attn_partial(flare_attn_ctx* ctx, flare_kv* kv, int l
 /* Log-sum-exp merge of n_parts partials, each [rows][head_dim + 2], into out [rows][head_dim]. */
 FLARE_API int flare_merge_partials(flare_attn_ctx* ctx, const float* partials, int n_parts, int rows,
                                    int head_dim, float* out, int on_device);
+
+/* ---------------------------------------------------------------- projections either side of attention
+ * The Q8_0-weight matrix-vector products that feed attention (the Q, K and V projections,
+ * flare-core/src/model.rs:2016-2136) and follow it (the output projection, model.rs:2249-2291), for `batch`
+ * input vectors; replaces matvec_q8_0_preq_into + quantize_input_q8_0 (model.rs:7976-8100, 5507-5527) and
+ * flare-gpu/shaders/dequant_matvec_q8_0.wgsl.
+ *
+ * flare_weight_upload_q8_0   a weight matrix [rows][cols] as the GGUF Q8_0 block stream the loader hands out
+ *                            (rows * cols / 32 blocks of 34 bytes, flare-loader/src/quantize.rs:188-197), copied
+ *                            to the device once.  cols % 32 == 0.
+ * flare_matvec_q8_0          out[b][r] = row r of the matrix . x[b], computed the reference's way so that the
+ *                            result is bit-identical to the CPU (x86_64 branch): x is quantised per block of 32
+ *                            (scale kept in f32), the int8 dot of a block is exact, and a row's blocks are added
+ *                            in ascending order as sum += (w_scale * x_scale) * dot with separate multiplies
+ *                            and add.  x [batch][cols], out [batch][rows], batch <= 256; a weight row is read
+ *                            from device memory once for the whole batch. */
+typedef struct flare_weight flare_weight;
+FLARE_API int flare_weight_upload_q8_0(flare_attn_ctx* ctx, const void* blocks, int rows, int cols, flare_weight** out_w);
+FLARE_API int flare_weight_free(flare_weight* w);
+FLARE_API int flare_matvec_q8_0(flare_attn_ctx* ctx, const flare_weight* w, const float* x, int batch, float* out,
+                                int on_device);
 
 /* ---------------------------------------------------------------- one sequence over several GPUs
  * No counterpart in the reference (single device).  One process per GPU; every process creates its context,

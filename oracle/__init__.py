@@ -325,6 +325,31 @@ def apply_rope_with_table(data, num_heads, head_dim, pos, theta, cos, sin) -> np
     return d
 
 
+# ---------------------------------------------------------------- Q8_0-weight matrix-vector product
+def quantize_input_q8_0(x):
+    """quantize_input_q8_0: f32 [n] -> (f32 scales [n/32], i8 quants [n])."""
+    x, xp = _f(x)
+    n = x.size
+    assert n % 32 == 0
+    scales, quants = np.empty(n // 32, np.float32), np.empty(n, np.int8)
+    L = lib()
+    L.orc_quantize_input_q8_0.argtypes = [_f32p, _sz, _f32p, C.POINTER(C.c_int8)]
+    L.orc_quantize_input_q8_0(xp, n, scales.ctypes.data_as(_f32p), quants.ctypes.data_as(C.POINTER(C.c_int8)))
+    return scales, quants
+
+
+def matvec_q8_0(weight_blocks, x, rows) -> np.ndarray:
+    """matvec_q8_0_preq_into on quantize_input_q8_0(x): weight_blocks is the Q8_0 block stream [rows][cols/32 x 34]."""
+    w, wp = _u8(weight_blocks)
+    scales, quants = quantize_input_q8_0(x)
+    out = np.empty(rows, np.float32)
+    L = lib()
+    L.orc_matvec_q8_0_preq.argtypes = [_u8p, _f32p, C.POINTER(C.c_int8), _sz, _sz, _f32p]
+    L.orc_matvec_q8_0_preq(wp, scales.ctypes.data_as(_f32p), quants.ctypes.data_as(C.POINTER(C.c_int8)), rows, scales.size,
+                           out.ctypes.data_as(_f32p))
+    return out
+
+
 # ---------------------------------------------------------------- caches
 class KvCache:
     """flare-core/src/kv_cache.rs:431-546."""

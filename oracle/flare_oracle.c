@@ -939,6 +939,54 @@ ORC_API void orc_apply_rope_with_table(float* data, size_t num_heads, size_t hea
 }
 
 
+/* ------------------------------------------------------------------------ */
+/* Q8_0-weight matrix-vector product (the projections either side of attention) */
+/* ------------------------------------------------------------------------ */
+
+/* flare-core/src/model.rs:5507-5527 (quantize_input_q8_0, the branch compiled on x86_64): per
+ * block of 32: amax, d = amax / 127, id = 127 / amax (0 when d == 0), q = round(x * id) as i8;
+ * the scale stays f32.  n must be a multiple of 32. */
+ORC_API void orc_quantize_input_q8_0(const float* input, size_t n, float* scales, int8_t* quants) {
+    for (size_t b = 0; b < n / Q8_BLOCK; b++) {
+        const float* blk = input + b * Q8_BLOCK;
+        float amax = 0.0f;
+        for (int j = 0; j < Q8_BLOCK; j++) amax = fmaxf(amax, fabsf(blk[j]));
+        float d = amax / 127.0f;
+        float id = (d != 0.0f) ? 127.0f / amax : 0.0f;
+        scales[b] = d;
+        for (int j = 0; j < Q8_BLOCK; j++) quants[b * Q8_BLOCK + j] = sat_i8(roundf(blk[j] * id));
+    }
+}
+
+/* flare-core/src/model.rs:8066-8100 (matvec_q8_0_preq_into, the scalar branch): per row, blocks in
+ * ascending order, sum += (w_scale * x_scale[block]) * (s0 + s1 + s2 + s3) as f32 with four
+ * interleaved int32 partial sums. */
+ORC_API void orc_matvec_q8_0_preq(const uint8_t* weight_data, const float* in_scales, const int8_t* in_quants,
+                                  size_t rows, size_t blocks_per_row, float* output) {
+    size_t bytes_per_row = blocks_per_row * Q8_BYTES;
+    for (size_t i = 0; i < rows; i++) {
+        const uint8_t* row_bytes = weight_data + i * bytes_per_row;
+        float sum = 0.0f;
+        for (size_t block = 0; block < blocks_per_row; block++) {
+            size_t block_start = block * Q8_BYTES;
+            float w_scale = orc_f16_to_f32((uint16_t)(row_bytes[block_start] | (row_bytes[block_start + 1] << 8)));
+            const uint8_t* w_quants = row_bytes + block_start + 2;
+            size_t input_offset = block * Q8_BLOCK;
+            float combined_scale = w_scale * in_scales[block];
+            int32_t s0 = 0, s1 = 0, s2 = 0, s3 = 0;
+            for (int j = 0; j < 32; j += 4) {
+                s0 += (int32_t)(int8_t)w_quants[j] * (int32_t)in_quants[input_offset + j];
+                s1 += (int32_t)(int8_t)w_quants[j + 1] * (int32_t)in_quants[input_offset + j + 1];
+                s2 += (int32_t)(int8_t)w_quants[j + 2] * (int32_t)in_quants[input_offset + j + 2];
+                s3 += (int32_t)(int8_t)w_quants[j + 3] * (int32_t)in_quants[input_offset + j + 3];
+            }
+            sum += combined_scale * (float)(s0 + s1 + s2 + s3);
+        }
+        output[i] = sum;
+    }
+}
+
+
 ORC_API int orc_max_threads(void) {
     long n = sysconf(_SC_NPROCESSORS_ONLN);
     return n > 0 ? (int)n : 1;

@@ -200,6 +200,41 @@ def test_g32_long_context_decode_takes_the_tensor_core_path(eng, fb, orc, nh, nk
     kv.free()
 
 
+@pytest.mark.parametrize("extra", [[5, 63], [64, 127], [128, 200], [2048 + 1000, 31]])
+def test_g32_wrapped_ring_stays_on_the_tensor_core_path(eng, fb, orc, extra):
+    """A ring of 2048 slots that has wrapped (2048 + extra tokens written): the 128 ring tokens then sit in two or
+    three tiles somewhere in the middle of the physical slots, possibly across the end of the ring, with the oldest
+    2-bit tokens right behind them.  The call must still be served by the code-tile kernel and match the CPU; the
+    second batch entry has another phase of the ring, and a third one has not wrapped at all."""
+    nh, nkv, hd, ms = 32, 8, 64, 2048
+    kvd = nkv * hd
+    totals = [ms + extra[0], ms + extra[1], 1500]
+    B = len(totals)
+    kv = eng.kv_alloc(1, B, ms, nkv, hd, fb.KV_KIVI_G32)
+    ks, vs = [], []
+    for b, n in enumerate(totals):
+        k, v = _g32_inputs(400 + 10 * b + extra[0], n + 3, kvd)
+        ks.append(k); vs.append(v)
+        done = 0
+        while done < n:                        # in pieces, as prefill then decode steps would arrive
+            c = min(777, n - done)
+            kv.append(0, b, k[done:done + c], v[done:done + c]); kv.advance(b, c)
+            done += c
+    for step in range(3):
+        q = normal(500 + step, (B, 1, nh, hd), 0.4)
+        for b, n in enumerate(totals):
+            kv.write(0, b, n + step, ks[b][n + step], vs[b][n + step])
+        got = eng.decode(kv, 0, nh, q)
+        assert eng.last_path() == fb.PATH_KIVI_TENSOR
+        for b, n in enumerate(totals):
+            oc = _g32_oracle(orc, ms, kvd, ks[b][:n + step + 1], vs[b][:n + step + 1])
+            ok, ov = oc.dequant()
+            want = orc.gqa_decode(q[b], ok, ov, nh, nkv, hd, oc.attend_len())
+            assert_close(got[b], want, f"wrapped ring, extra {extra}, step {step}, seq {b}")
+        kv.advance()
+    kv.free()
+
+
 def test_g32_ragged_batch_long_context(eng, fb, orc):
     """Sequences of different lengths (long, short, shorter than the residual ring) in one call."""
     nh, nkv, hd, ms, B = 8, 2, 64, 2048, 3

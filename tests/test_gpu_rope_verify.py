@@ -175,3 +175,29 @@ def test_batched_verify_equals_the_sequential_loop(eng, fb, orc):
             (ka, va), (kb, vb) = kv_bat.export_dequant(layer, 0), kv_seq.export_dequant(layer, 0)
             assert np.mean(np.abs(ka[:n] - kb[:n])) < 1e-3 and np.mean(np.abs(va[:n] - vb[:n])) < 1e-3
         kv_seq.free(); kv_bat.free()
+
+
+@pytest.mark.parametrize("rows,cols,batch", [(2048, 2048, 1), (512, 2048, 32), (96, 4096, 5), (33, 64, 40), (2048, 2048, 32)])
+def test_q8_0_projection_is_bit_exact(eng, fb, orc, rows, cols, batch):
+    """The Q / K / V and output projections (flare-core/src/model.rs:2016-2136, 2249-2291): matvec_q8_0_preq_into on
+    quantize_input_q8_0, bit for bit — the integer dots are exact and the f32 sum over a row's blocks runs in the
+    CPU's order.  Shapes: Llama-3.2-1B's q / kv projections at batch 1 and 32, a wide row (several 64-block
+    chunks), a matrix smaller than a warp tile with a ragged batch."""
+    rng = np.random.default_rng(rows + cols + batch)
+    W = rng.standard_normal((rows, cols), dtype=np.float32) * np.float32(0.05)
+    x = rng.standard_normal((batch, cols), dtype=np.float32)
+    x[0, :32] = 0.0                                        # a zero block: d == 0, id == 0
+    if batch > 1:
+        x[1, 5] = 1.0e4                                    # a block dominated by one value
+    blocks = orc.quantize_q8_0(W)
+    w = eng.weight_upload_q8_0(blocks, rows, cols)
+    got = eng.matvec_q8_0(w, x)
+    want = np.stack([orc.matvec_q8_0(blocks, x[b], rows) for b in range(batch)])
+    assert_bits_equal(got, want, f"Q8_0 projection {rows}x{cols}, batch {batch}")
+    # device buffers in and out give the same bits
+    import torch
+    xd, od = torch.from_numpy(x).cuda(), torch.empty(batch, rows, device="cuda")
+    eng.matvec_q8_0(w, xd.data_ptr(), out=(od.data_ptr(), batch))
+    eng.sync()
+    assert_bits_equal(od.cpu().numpy(), want, "device buffers")
+    w.free()

@@ -167,3 +167,29 @@ def test_q2_constant_vector_is_all_zero_codes(orc):
 def test_q2_odd_length_packs_round_up(orc):
     packed, scale, mn = orc.q2_quantize_to_packed(np.array([0, 3, 1, 2, 3], dtype=np.float32))
     assert packed.size == 2 and packed[0] == (0 | 3 << 2 | 1 << 4 | 2 << 6) and packed[1] == 3
+
+
+def test_q8_0_matvec_restatement(orc):
+    """quantize_input_q8_0 + matvec_q8_0_preq_into (flare-core/src/model.rs:5507-5527, 8066-8100) on numbers that can
+    be checked by hand: one block, weights 1..32 scaled by 0.5, input all ones -> quants 127, scale 1/127."""
+    w = np.zeros(34, np.uint8)
+    w[0:2] = [0x00, 0x38]                                  # f16 0.5
+    w[2:] = np.arange(1, 33, dtype=np.int8).view(np.uint8)
+    x = np.ones(32, np.float32)
+    scales, quants = orc.quantize_input_q8_0(x)
+    assert quants.tolist() == [127] * 32 and scales[0] == np.float32(1.0) / np.float32(127.0)
+    got = orc.matvec_q8_0(w, x, 1)
+    want = (np.float32(0.5) * scales[0]) * np.float32(127 * 528)           # sum 1..32 = 528
+    assert got[0] == want and abs(got[0] - 264.0) < 1e-3
+    # against a float64 evaluation of the same quantised operands on a random matrix
+    rng = np.random.default_rng(3)
+    rows, cols = 7, 256
+    W = rng.standard_normal((rows, cols), dtype=np.float32)
+    xb = rng.standard_normal(cols, dtype=np.float32)
+    blocks = orc.quantize_q8_0(W)
+    got = orc.matvec_q8_0(blocks, xb, rows)
+    Wd = orc.dequant_q8_0(blocks).astype(np.float64)
+    s, qv = orc.quantize_input_q8_0(xb)
+    xd = (qv.reshape(-1, 32).astype(np.float64) * s[:, None].astype(np.float64)).reshape(-1)
+    assert np.max(np.abs(got - Wd @ xd)) < 1e-4
+    assert np.max(np.abs(got - W @ xb)) < 0.5            # and it is the product, up to the two quantisations
