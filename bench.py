@@ -229,6 +229,8 @@ class Run:
         maximum over ranks is taken.  Returns a dict with the median / min / max ms per step and the clocks
         sampled while the regions ran."""
         torch = self.torch
+        if self.args.quick:
+            min_repeats, min_seconds = 1, 0.0
         for _ in range(warmup):
             fn()
         times = []
@@ -503,7 +505,12 @@ def case_longctx(R: Run, steps=None, total=131072):
     return rec
 
 
-CASES = {"prefill": lambda R, **kw: case_prefill(R, 0, **kw), "prefill_window": lambda R, **kw: case_prefill(R, 4096, **kw),
+def _prefill_batch(R):
+    return R.args.batch if R.args.batch != BATCH else 4          # --batch: a smaller case for profiler captures
+
+
+CASES = {"prefill": lambda R, **kw: case_prefill(R, 0, _prefill_batch(R), **kw),
+         "prefill_window": lambda R, **kw: case_prefill(R, 4096, _prefill_batch(R), **kw),
          "kivi": case_kivi, "longctx": case_longctx, "f32": case_f32}
 
 
@@ -608,6 +615,7 @@ def main():
     ap.add_argument("--batch", type=int, default=BATCH, help=argparse.SUPPRESS)
     ap.add_argument("--case-steps", type=int, default=0, help=argparse.SUPPRESS)
     ap.add_argument("--no-cpu", action="store_true", help=argparse.SUPPRESS)
+    ap.add_argument("--quick", action="store_true", help=argparse.SUPPRESS)             # one timed region: profiler captures
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)

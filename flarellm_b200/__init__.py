@@ -89,6 +89,7 @@ SYMBOLS = [
     ("flare_attn_comm_enable_direct", _i, [_vp, _i, _i]),
     ("flare_attn_comm_set_wait_ms", _i, [_vp, C.c_uint]),
     ("flare_attn_comm_info", _i, [_vp, _ip, _ip, _ip]),
+    ("flare_attn_comm_probe_us", C.c_double, [_vp]),
     ("flare_attn_comm_destroy", _i, [_vp]),
     ("flare_decode_attn_splitkv_multi", _i, [_vp, _vp, _i, _i, _vp, _i, _vp, _i]),
     ("flare_attn_comm_selftest_missing_peer", _i, [_vp]),
@@ -302,6 +303,15 @@ class Engine:
 
     def comm_enable_direct(self, max_rows: int, head_dim: int):
         self.check(self.L.flare_attn_comm_enable_direct(self.h, max_rows, head_dim))
+
+    def comm_info(self):
+        """(rank, world, direct) of the context's communicator."""
+        r, w, d = C.c_int(), C.c_int(), C.c_int()
+        self.check(self.L.flare_attn_comm_info(self.h, C.byref(r), C.byref(w), C.byref(d)))
+        return int(r.value), int(w.value), bool(d.value)
+
+    def comm_probe_us(self) -> float:
+        return float(self.L.flare_attn_comm_probe_us(self.h))
 
     def comm_set_wait_ms(self, ms: int):
         self.check(self.L.flare_attn_comm_set_wait_ms(self.h, ms))

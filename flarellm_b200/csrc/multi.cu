@@ -20,6 +20,7 @@
 #include "common.cuh"
 #include <dlfcn.h>
 #include <math_constants.h>
+#include <algorithm>
 #include <mutex>
 #include <nccl.h>
 
@@ -103,6 +104,7 @@ struct FlareComm {
     void* peer_buf[kMaxWorld] = {};       // the same buffer of every rank as mapped here; [rank] = local_buf
     uint32_t seq = 0;
     unsigned wait_ms = 2000;
+    float probe_us = 0.0f;               // time of one exchange measured at set-up, the slowest rank's median
 };
 
 namespace {
@@ -127,6 +129,7 @@ struct ExchangeParams {
     uint2* rec[kMaxWorld];          // record buffer of rank r (as mapped in this process): [2][world][rows_max][chunks][WORDS]
     int rank, world, rows_max, chunks_max;
     int phase;                      // which half of the record buffers this call uses
+    int fence;                      // issue a system-scope fence after the stores
     uint32_t seq;                   // this call's sequence number
     unsigned long long wait_ns;
     int* err;
@@ -137,6 +140,10 @@ __device__ __forceinline__ void st_word(uint2* p, float v, uint32_t seq) {
 }
 __device__ __forceinline__ uint2 ld_word(const uint2* p) {
     uint2 v; asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory"); return v;
+}
+// The same with acquire semantics at system scope: a load that must observe what another GPU has stored.
+__device__ __forceinline__ uint2 ld_word_acquire(const uint2* p) {
+    uint2 v; asm volatile("ld.acquire.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory"); return v;
 }
 
 enum { MODE_FINAL = 0, MODE_RECORD = 1, MODE_EXCHANGE = 2 };
@@ -224,25 +231,43 @@ __global__ void __launch_bounds__(256) merge_exchange_kernel(const float* __rest
     // ---- this rank's record into slot `rank` of every rank's buffer: {value, call number} words ------------
     const size_t slot_words = (size_t)WORDS;
     const size_t my_slot = ((((size_t)mp.phase * mp.world + mp.rank) * mp.rows_max + row) * mp.chunks_max + chunk) * slot_words;
-    for (int t = tid; t < WORDS * mp.world; t += blockDim.x) {
-        const int r = t / WORDS, i = t % WORDS;
-        st_word(mp.rec[r] + my_slot + i, s_send[i], mp.seq);
+    // one destination GPU per store instruction: warp w serves ranks w, w + 8, ...
+    for (int r = tid >> 5; r < mp.world; r += (int)(blockDim.x >> 5)) {
+        uint2* dst = mp.rec[r] + my_slot;
+        for (int i = tid & 31; i < WORDS; i += 32) st_word(dst + i, s_send[i], mp.seq);
     }
+    if (mp.fence) __threadfence_system();
     TLX_STAMP(3);
     // ---- every rank's record of this (row, chunk) out of the own buffer: a word is there when its number matches.
     // Once a wait has run out on this context (status word set, not yet read and cleared by the host) the ranks are
     // out of step: the calls still queued behind it do not wait their full limit again, they give up at once.
     const unsigned long long t0 = global_ns();
     const unsigned long long limit = (*reinterpret_cast<volatile int*>(mp.err) != 0) ? 0ull : mp.wait_ns;
-    for (int t = tid; t < WORDS * mp.world; t += blockDim.x) {
+    const size_t in_base = (((size_t)mp.phase * mp.world) * mp.rows_max + row) * mp.chunks_max + chunk;   // + r * rows_max * chunks_max
+    const size_t in_rank_stride = (size_t)mp.rows_max * mp.chunks_max;
+    // First one thread per rank waits for the LAST word of that rank's record, pausing between looks: thousands of
+    // threads polling every word at once take so much L2 bandwidth that the incoming stores themselves are held
+    // up (at 4 GPUs a call then took 1 ms instead of 30 us).
+    if (tid < mp.world) {
+        const uint2* src = mp.rec[mp.rank] + (in_base + (size_t)tid * in_rank_stride) * slot_words + (WORDS - 1);
+        for (;;) {
+            if ((mp.fence & 2 ? ld_word_acquire(src) : ld_word(src)).y == mp.seq) break;
+            if (global_ns() - t0 > limit) { s_fail = 1; break; }
+            __nanosleep(200);
+        }
+    }
+    __syncthreads();
+    // Then every word is checked for itself (stores of different threads may arrive in any order), which now
+    // almost always succeeds at the first look.
+    for (int t = tid; t < WORDS * mp.world && !s_fail; t += blockDim.x) {
         const int r = t / WORDS, i = t % WORDS;
-        const uint2* src = mp.rec[mp.rank] + ((((size_t)mp.phase * mp.world + r) * mp.rows_max + row) * mp.chunks_max + chunk) * slot_words + i;
+        const uint2* src = mp.rec[mp.rank] + (in_base + (size_t)r * in_rank_stride) * slot_words + i;
         bool ok = false;
         for (;;) {
-            const uint2 v = ld_word(src);
+            const uint2 v = (mp.fence & 2) ? ld_word_acquire(src) : ld_word(src);
             if (v.y == mp.seq) { s_recv[r][i] = __uint_as_float(v.x); ok = true; break; }
             if (global_ns() - t0 > limit) break;
-            __nanosleep(40);
+            __nanosleep(100);
         }
         if (!ok) s_fail = 1;
     }
@@ -281,6 +306,9 @@ int launch_merge_exchange(flare_attn_ctx* ctx, const float* work, int n_split, i
     cfg.stream = ctx->stream;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+#ifdef FLARE_TUNE
+    if (const char* e = getenv("FLARE_MX_NOPDL")) if (atoi(e)) cfg.numAttrs = 0;
+#endif
     FLARE_CUDA_OK(ctx, cudaLaunchKernelEx(&cfg, merge_exchange_kernel<MODE>, work, n_split, hd, mp, out));
     FLARE_LAUNCH_CHECK(ctx);
     return FLARE_OK;
@@ -303,6 +331,10 @@ void fill_exchange_params(const FlareComm* c, ExchangeParams* mp, int* err) {
     mp->rank = c->rank; mp->world = c->world; mp->rows_max = c->rows_max; mp->chunks_max = c->hd_max / CW;
     mp->wait_ns = (unsigned long long)c->wait_ms * 1000000ull;
     mp->err = err;
+    mp->fence = 0;
+#ifdef FLARE_TUNE
+    if (const char* e = getenv("FLARE_MX_FENCE")) mp->fence = atoi(e);
+#endif
 }
 
 }  // namespace
@@ -345,6 +377,9 @@ int flare_multi_tail(flare_attn_ctx* ctx, const float* work, int n_split, int ro
         mp.seq = c->seq; mp.phase = (int)(c->seq & 1u);
         FLARE_TRY(launch_merge_exchange<MODE_EXCHANGE>(ctx, work, n_split, rows, head_dim, mp, out));
         ctx->last_launch_overlappable = true;
+#ifdef FLARE_TUNE
+        if (const char* e = getenv("FLARE_MX_NOPDL")) if (atoi(e)) ctx->last_launch_overlappable = false;
+#endif
         return FLARE_OK;
     }
     NcclApi* api = nccl_api();
@@ -456,6 +491,77 @@ int flare_attn_comm_enable_direct(flare_attn_ctx* ctx, int max_rows, int head_di
     }
     c->rows_max = max_rows; c->hd_max = head_dim; c->seq = 0;
     c->direct = true;
+    // Probe: a few exchanges of one small record, timed on the device.  Peer stores normally arrive within a
+    // microsecond or two, but on some multi-GPU leases of this pool every exchange took almost exactly one
+    // millisecond (each rank's stores became visible to its peers that late, whatever the fences or the load
+    // flavour), while NCCL's all-gather on the same GPUs took 20 us.  The slower rank decides for everybody:
+    // above 100 us per exchange the direct mode is switched off again and the calls use ncclAllGather.
+    {
+        const int probe_rounds = 12;
+        float* work = nullptr;
+        cudaEvent_t ev[2] = {nullptr, nullptr};
+        float worst_us = 0.0f;
+        int st = FLARE_OK;
+        do {
+            if (cudaMalloc(&work, (size_t)(head_dim + 2) * 4 + head_dim * 4 + 2 * sizeof(float)) != cudaSuccess ||
+                cudaMemsetAsync(work, 0, (size_t)(head_dim + 2) * 4 + head_dim * 4, ctx->stream) != cudaSuccess ||
+                cudaEventCreate(&ev[0]) != cudaSuccess || cudaEventCreate(&ev[1]) != cudaSuccess) { st = FLARE_ERR_CUDA; break; }
+            // line the ranks up first (opening the peers' handles takes them different times)
+            float* d_bar = nullptr;
+            if (cudaMalloc(&d_bar, sizeof(float) * (c->world + 1)) != cudaSuccess) { st = FLARE_ERR_CUDA; break; }
+            const bool lined_up = cudaMemsetAsync(d_bar, 0, sizeof(float) * (c->world + 1), ctx->stream) == cudaSuccess &&
+                                  api->AllGather(d_bar, d_bar + 1, 1, ncclFloat, c->comm, ctx->stream) == ncclSuccess &&
+                                  cudaStreamSynchronize(ctx->stream) == cudaSuccess;
+            cudaFree(d_bar);
+            if (!lined_up) { st = FLARE_ERR_NCCL; break; }
+            std::vector<float> us;
+            int probe_st = FLARE_OK;
+            for (int i = 0; i < probe_rounds && probe_st == FLARE_OK; i++) {
+                ExchangeParams mp;
+                fill_exchange_params(c, &mp, ctx->d_err);
+                c->seq++;
+                mp.seq = c->seq; mp.phase = (int)(c->seq & 1u);
+                mp.wait_ns = 200ull * 1000000ull;
+                ctx->last_launch_overlappable = false;
+                cudaEventRecord(ev[0], ctx->stream);
+                probe_st = launch_merge_exchange<MODE_EXCHANGE>(ctx, work, 1, 1, head_dim, mp, work + head_dim + 2);
+                cudaEventRecord(ev[1], ctx->stream);
+                if (probe_st == FLARE_OK && cudaEventSynchronize(ev[1]) != cudaSuccess) probe_st = FLARE_ERR_CUDA;
+                if (probe_st != FLARE_OK) break;
+                if (*reinterpret_cast<volatile int*>(ctx->h_err) != 0) { probe_st = FLARE_ERR_TIMEOUT; break; }
+                float ms = 0.0f;
+                cudaEventElapsedTime(&ms, ev[0], ev[1]);
+                if (i >= 2) us.push_back(ms * 1e3f);           // the first rounds include what skew is left
+            }
+            // a rank whose probe failed still takes part in the vote below, with a time nobody accepts
+            float median_us = 1.0e9f;
+            if (probe_st == FLARE_OK && !us.empty()) {
+                std::sort(us.begin(), us.end());
+                median_us = us[us.size() / 2];
+            }
+            float* d_all = nullptr;
+            if (cudaMalloc(&d_all, sizeof(float) * (c->world + 1)) != cudaSuccess) { st = FLARE_ERR_CUDA; break; }
+            std::vector<float> all_med(c->world, 0.0f);
+            bool ok = cudaMemcpyAsync(d_all, &median_us, sizeof(float), cudaMemcpyHostToDevice, ctx->stream) == cudaSuccess &&
+                      api->AllGather(d_all, d_all + 1, 1, ncclFloat, c->comm, ctx->stream) == ncclSuccess &&
+                      cudaMemcpyAsync(all_med.data(), d_all + 1, sizeof(float) * c->world, cudaMemcpyDeviceToHost, ctx->stream) == cudaSuccess &&
+                      cudaStreamSynchronize(ctx->stream) == cudaSuccess;
+            cudaFree(d_all);
+            if (!ok) { st = FLARE_ERR_NCCL; break; }
+            for (float m : all_med) worst_us = m > worst_us ? m : worst_us;
+        } while (0);
+        cudaFree(work);
+        if (ev[0]) cudaEventDestroy(ev[0]);
+        if (ev[1]) cudaEventDestroy(ev[1]);
+        // a probe that timed out has left a status behind: take it off the context
+        if (*reinterpret_cast<volatile int*>(ctx->h_err) != 0) { *reinterpret_cast<volatile int*>(ctx->h_err) = 0; if (st == FLARE_OK) st = FLARE_ERR_TIMEOUT; }
+        c->probe_us = worst_us;
+        if (st != FLARE_OK || worst_us > 100.0f) {
+            c->direct = false;        // the buffers stay mapped until the communicator goes; the calls use ncclAllGather
+            if (st != FLARE_OK) flare_set_error(ctx, FLARE_OK, "direct exchange probe failed (status %d): using ncclAllGather", st);
+            else flare_set_error(ctx, FLARE_OK, "direct exchange probe: %.0f us per exchange on the slowest rank: using ncclAllGather", (double)worst_us);
+        }
+    }
     return FLARE_OK;
 }
 
@@ -466,6 +572,8 @@ int flare_attn_comm_info(const flare_attn_ctx* ctx, int* rank, int* world, int* 
     if (direct) *direct = ctx->comm->direct ? 1 : 0;
     return FLARE_OK;
 }
+
+double flare_attn_comm_probe_us(const flare_attn_ctx* ctx) { return ctx && ctx->comm ? (double)ctx->comm->probe_us : 0.0; }
 
 int flare_decode_attn_splitkv_multi(flare_attn_ctx* ctx, flare_kv* kv, int layer, int num_heads, const float* q,
                                     int n_local_slots, float* out, int on_device) {

@@ -127,15 +127,20 @@ class CAbiSplitDecoder:
                 # the set-up is collective: every rank must attempt it, and all must agree on the outcome
                 try:
                     eng.comm_enable_direct(rows, hd)
-                    ok = 1
+                    ok = 1 if eng.comm_info()[2] else 0      # the library's own probe may have switched it off again
+                    if not ok:
+                        self.direct_error = eng.L.flare_attn_last_error(eng.h).decode()
                 except Exception as e:      # FlareError: no peer access / IPC refused
                     self.direct_error, ok = str(e), 0
                 flag = torch.tensor([ok], device="cuda")
                 dist.all_reduce(flag, op=dist.ReduceOp.MIN)
                 if int(flag.item()) == 1:
-                    self.how = "records stored into the peers' buffers by the merging kernel (peer stores, bounded wait, no collective)"
+                    self.how = ("records stored into the peers' buffers by the merging kernel (peer stores, bounded wait, "
+                                "no collective; probe %.1f us per exchange)" % eng.comm_probe_us())
                 elif ok:
                     raise RuntimeError("direct exchange set up on this rank but not on every rank")
+                else:
+                    self.how += " (direct exchange not used: %s)" % self.direct_error
             if wait_ms:
                 eng.comm_set_wait_ms(wait_ms)
         else:

@@ -346,6 +346,10 @@ FLARE_API int flare_matvec_q8_0(flare_attn_ctx* ctx, const flare_weight* w, cons
  *                             have arrived, waiting at most the limit of flare_attn_comm_set_wait_ms (default
  *                             2000 ms); when the wait runs out the call reports FLARE_ERR_TIMEOUT and the
  *                             context stays usable.  Without it the records travel by ncclAllGather.
+ *                             The set-up ends with a timed probe of a few exchanges; if the slowest rank needs
+ *                             more than 100 us per exchange the mode is switched off again on every rank (the
+ *                             call still returns FLARE_OK; flare_attn_comm_info tells, flare_attn_comm_probe_us
+ *                             gives the measured time, flare_attn_last_error the reason).
  * flare_attn_comm_destroy     frees the buffers and the communicator; make sure no rank is still inside a
  *                             multi-GPU call (a host barrier) before any rank destroys.
  *
@@ -362,6 +366,7 @@ FLARE_API int flare_attn_comm_init(flare_attn_ctx* ctx, const void* id, int rank
 FLARE_API int flare_attn_comm_enable_direct(flare_attn_ctx* ctx, int max_rows, int head_dim);
 FLARE_API int flare_attn_comm_set_wait_ms(flare_attn_ctx* ctx, unsigned wait_ms);
 FLARE_API int flare_attn_comm_info(const flare_attn_ctx* ctx, int* rank, int* world, int* direct);
+FLARE_API double flare_attn_comm_probe_us(const flare_attn_ctx* ctx);
 FLARE_API int flare_attn_comm_destroy(flare_attn_ctx* ctx);
 FLARE_API int flare_decode_attn_splitkv_multi(flare_attn_ctx* ctx, flare_kv* kv, int layer, int num_heads,
                                               const float* q, int n_local_slots, float* out, int on_device);
