@@ -67,6 +67,7 @@ int flare_check_device_error(flare_attn_ctx* ctx) {
     const int h = *reinterpret_cast<volatile int*>(ctx->h_err);
     if (h != 0) {
         *reinterpret_cast<volatile int*>(ctx->h_err) = 0;      // nothing is running on the stream
+        cudaMemsetAsync(ctx->d_gaveup, 0, sizeof(int), ctx->stream);
         return flare_set_error(ctx, h, h == FLARE_ERR_TIMEOUT ? "a kernel gave up waiting (for its own memory copies, or for a peer rank's records): status %d"
                                                               : "a kernel reported status %d", h);
     }
@@ -160,7 +161,9 @@ int flare_attn_create(int device, flare_attn_ctx** out_ctx) {
     }
     ctx->stream = ctx->own_stream;
     if (cudaHostAlloc((void**)&ctx->h_err, 64, cudaHostAllocMapped) != cudaSuccess ||
-        cudaHostGetDevicePointer((void**)&ctx->d_err, ctx->h_err, 0) != cudaSuccess) {
+        cudaHostGetDevicePointer((void**)&ctx->d_err, ctx->h_err, 0) != cudaSuccess ||
+        cudaMalloc((void**)&ctx->d_gaveup, 256) != cudaSuccess || cudaMemset(ctx->d_gaveup, 0, 256) != cudaSuccess) {
+        cudaFree(ctx->d_gaveup);
         if (ctx->h_err) cudaFreeHost(ctx->h_err);
         cudaStreamDestroy(ctx->own_stream);
         delete ctx;
@@ -179,6 +182,7 @@ int flare_attn_destroy(flare_attn_ctx* ctx) {
     if (ctx->backend_kv) flare_kv_free(ctx->backend_kv);
     flare_comm_free(ctx);
     if (ctx->h_err) cudaFreeHost(ctx->h_err);
+    cudaFree(ctx->d_gaveup);
     cudaFree(ctx->d_misc2); cudaFree(ctx->d_conv);
     cudaFree(ctx->d_work); cudaFree(ctx->d_stage_in); cudaFree(ctx->d_stage_out); cudaFree(ctx->d_misc);
     if (ctx->h_pinned) cudaFreeHost(ctx->h_pinned);

@@ -55,6 +55,9 @@ struct flare_attn_ctx {
     bool last_launch_overlappable = false;
     int* h_err = nullptr;            // status word in page-locked, device-mapped host memory: a kernel whose bounded wait gives up stores a code here
     int* d_err = nullptr;            // the device's address of the same word (what kernels are given)
+    int* d_gaveup = nullptr;         // device memory: set by an exchange whose wait ran out, so that the calls queued behind
+                                     // it give up at once; looked at by every CTA, hence not in host memory (a read of
+                                     // the mapped word crosses PCIe: 1024 warps doing so cost a call a millisecond)
     int sm_count = 148;
     flare_kv* backend_kv = nullptr;  // cache created by flare_backend_init_gpu_kv_cache
     FlareComm* comm = nullptr;       // set by flare_attn_comm_init

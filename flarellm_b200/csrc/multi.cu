@@ -132,7 +132,8 @@ struct ExchangeParams {
     int fence;                      // issue a system-scope fence after the stores
     uint32_t seq;                   // this call's sequence number
     unsigned long long wait_ns;
-    int* err;
+    int* err;                       // status word (mapped host memory): written once, by a wait that ran out
+    int* gaveup;                    // device memory: non-zero once a wait has run out on this context
 };
 
 __device__ __forceinline__ void st_word(uint2* p, float v, uint32_t seq) {
@@ -164,7 +165,7 @@ __global__ void __launch_bounds__(256) merge_exchange_kernel(const float* __rest
     __shared__ float s_part[16][CW];
     __shared__ float s_send[WORDS];
     __shared__ float s_recv[kMaxWorld][WORDS];
-    __shared__ int s_fail;
+    __shared__ int s_fail, s_gaveup;
     TLX_STAMP(0);
     pdl_trigger();          // the next call's attention kernel may begin its prologue (it never writes what is read here)
     pdl_wait();             // the attention kernel has written every slot-range record
@@ -179,7 +180,10 @@ __global__ void __launch_bounds__(256) merge_exchange_kernel(const float* __rest
 #pragma unroll
     for (int off = 16; off; off >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, off));
     if ((tid & 31) == 0) s_red[tid >> 5] = mm;
-    if (tid == 0) s_fail = 0;
+    if (tid == 0) {
+        s_fail = 0;
+        if (MODE == MODE_EXCHANGE) s_gaveup = *reinterpret_cast<volatile int*>(mp.gaveup);
+    }
     __syncthreads();
     mm = s_red[0];
 #pragma unroll
@@ -239,15 +243,14 @@ __global__ void __launch_bounds__(256) merge_exchange_kernel(const float* __rest
     if (mp.fence) __threadfence_system();
     TLX_STAMP(3);
     // ---- every rank's record of this (row, chunk) out of the own buffer: a word is there when its number matches.
-    // Once a wait has run out on this context (status word set, not yet read and cleared by the host) the ranks are
+    // Once a wait has run out on this context (flag in device memory set, not yet cleared by the host) the ranks are
     // out of step: the calls still queued behind it do not wait their full limit again, they give up at once.
     const unsigned long long t0 = global_ns();
-    const unsigned long long limit = (*reinterpret_cast<volatile int*>(mp.err) != 0) ? 0ull : mp.wait_ns;
+    const unsigned long long limit = s_gaveup ? 0ull : mp.wait_ns;
     const size_t in_base = (((size_t)mp.phase * mp.world) * mp.rows_max + row) * mp.chunks_max + chunk;   // + r * rows_max * chunks_max
     const size_t in_rank_stride = (size_t)mp.rows_max * mp.chunks_max;
-    // First one thread per rank waits for the LAST word of that rank's record, pausing between looks: thousands of
-    // threads polling every word at once take so much L2 bandwidth that the incoming stores themselves are held
-    // up (at 4 GPUs a call then took 1 ms instead of 30 us).
+    // First one thread per rank waits for the LAST word of that rank's record, pausing between looks, so that the
+    // wait costs a few loads per CTA rather than a poll by every thread.
     if (tid < mp.world) {
         const uint2* src = mp.rec[mp.rank] + (in_base + (size_t)tid * in_rank_stride) * slot_words + (WORDS - 1);
         for (;;) {
@@ -274,7 +277,7 @@ __global__ void __launch_bounds__(256) merge_exchange_kernel(const float* __rest
     __syncthreads();
     TLX_STAMP(5);
     if (s_fail) {       // a rank did not show up in time: report, leave zeros, return (the context stays usable)
-        if (tid == 0) flare_report(mp.err, FLARE_ERR_TIMEOUT);
+        if (tid == 0) { *reinterpret_cast<volatile int*>(mp.gaveup) = 1; flare_report(mp.err, FLARE_ERR_TIMEOUT); }
         if (tid < CW) out[(size_t)row * hd + d] = 0.0f;
         return;
     }
@@ -325,12 +328,13 @@ int ensure_nccl_buffers(flare_attn_ctx* ctx, FlareComm* c, size_t part_floats) {
     return FLARE_OK;
 }
 
-void fill_exchange_params(const FlareComm* c, ExchangeParams* mp, int* err) {
+void fill_exchange_params(const FlareComm* c, ExchangeParams* mp, int* err, int* gaveup) {
     memset(mp, 0, sizeof(*mp));
     for (int r = 0; r < c->world; r++) mp->rec[r] = reinterpret_cast<uint2*>(c->peer_buf[r]);
     mp->rank = c->rank; mp->world = c->world; mp->rows_max = c->rows_max; mp->chunks_max = c->hd_max / CW;
     mp->wait_ns = (unsigned long long)c->wait_ms * 1000000ull;
     mp->err = err;
+    mp->gaveup = gaveup;
     mp->fence = 0;
 #ifdef FLARE_TUNE
     if (const char* e = getenv("FLARE_MX_FENCE")) mp->fence = atoi(e);
@@ -372,7 +376,7 @@ int flare_multi_tail(flare_attn_ctx* ctx, const float* work, int n_split, int ro
         return FLARE_OK;
     }
     if (c->direct && rows <= c->rows_max && head_dim <= c->hd_max) {
-        fill_exchange_params(c, &mp, ctx->d_err);
+        fill_exchange_params(c, &mp, ctx->d_err, ctx->d_gaveup);
         c->seq++;
         mp.seq = c->seq; mp.phase = (int)(c->seq & 1u);
         FLARE_TRY(launch_merge_exchange<MODE_EXCHANGE>(ctx, work, n_split, rows, head_dim, mp, out));
@@ -492,10 +496,9 @@ int flare_attn_comm_enable_direct(flare_attn_ctx* ctx, int max_rows, int head_di
     c->rows_max = max_rows; c->hd_max = head_dim; c->seq = 0;
     c->direct = true;
     // Probe: a few exchanges of one small record, timed on the device.  Peer stores normally arrive within a
-    // microsecond or two, but on some multi-GPU leases of this pool every exchange took almost exactly one
-    // millisecond (each rank's stores became visible to its peers that late, whatever the fences or the load
-    // flavour), while NCCL's all-gather on the same GPUs took 20 us.  The slower rank decides for everybody:
-    // above 100 us per exchange the direct mode is switched off again and the calls use ncclAllGather.
+    // microsecond or two; a machine on which they do not (peer access through the host bridge, a fabric in a
+    // degraded state) is better served by NCCL's all-gather.  The slowest rank decides for everybody: above
+    // 100 us per exchange the direct mode is switched off again and the calls use ncclAllGather.
     {
         const int probe_rounds = 12;
         float* work = nullptr;
@@ -518,7 +521,7 @@ int flare_attn_comm_enable_direct(flare_attn_ctx* ctx, int max_rows, int head_di
             int probe_st = FLARE_OK;
             for (int i = 0; i < probe_rounds && probe_st == FLARE_OK; i++) {
                 ExchangeParams mp;
-                fill_exchange_params(c, &mp, ctx->d_err);
+                fill_exchange_params(c, &mp, ctx->d_err, ctx->d_gaveup);
                 c->seq++;
                 mp.seq = c->seq; mp.phase = (int)(c->seq & 1u);
                 mp.wait_ns = 200ull * 1000000ull;
@@ -554,7 +557,11 @@ int flare_attn_comm_enable_direct(flare_attn_ctx* ctx, int max_rows, int head_di
         if (ev[0]) cudaEventDestroy(ev[0]);
         if (ev[1]) cudaEventDestroy(ev[1]);
         // a probe that timed out has left a status behind: take it off the context
-        if (*reinterpret_cast<volatile int*>(ctx->h_err) != 0) { *reinterpret_cast<volatile int*>(ctx->h_err) = 0; if (st == FLARE_OK) st = FLARE_ERR_TIMEOUT; }
+        if (*reinterpret_cast<volatile int*>(ctx->h_err) != 0) {
+            *reinterpret_cast<volatile int*>(ctx->h_err) = 0;
+            cudaMemsetAsync(ctx->d_gaveup, 0, sizeof(int), ctx->stream);
+            if (st == FLARE_OK) st = FLARE_ERR_TIMEOUT;
+        }
         c->probe_us = worst_us;
         if (st != FLARE_OK || worst_us > 100.0f) {
             c->direct = false;        // the buffers stay mapped until the communicator goes; the calls use ncclAllGather
@@ -616,6 +623,7 @@ int flare_attn_comm_selftest_missing_peer(flare_attn_ctx* ctx) {
     mp.rank = 0; mp.world = world; mp.rows_max = rows; mp.chunks_max = hd / CW; mp.phase = 1; mp.seq = 1;
     mp.wait_ns = 50ull * 1000000ull;
     mp.err = ctx->d_err;
+    mp.gaveup = ctx->d_gaveup;
     ctx->last_launch_overlappable = false;
     int st = launch_merge_exchange<MODE_EXCHANGE>(ctx, work, 1, rows, hd, mp, work + (size_t)rows * (hd + 2));
     if (st == FLARE_OK) st = flare_check_device_error(ctx);
