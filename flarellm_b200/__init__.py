@@ -84,6 +84,11 @@ SYMBOLS = [
     ("flare_weight_upload_q8_0", _i, [_vp, _vp, _i, _i, C.POINTER(_vp)]),
     ("flare_weight_free", _i, [_vp]),
     ("flare_matvec_q8_0", _i, [_vp, _vp, _vp, _i, _vp, _i]),
+    ("flare_model_create", _i, [_vp, _vp, _vp]),
+    ("flare_model_set_layer", _i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
+    ("flare_model_set_output", _i, [_vp, _vp, _vp, _vp]),
+    ("flare_model_free", _i, [_vp]),
+    ("flare_forward_token", _i, [_vp, _vp, _vp, _vp, _vp, _vp]),
     ("flare_attn_comm_unique_id", _i, [_vp]),
     ("flare_attn_comm_init", _i, [_vp, _vp, _i, _i]),
     ("flare_attn_comm_enable_direct", _i, [_vp, _i, _i]),
@@ -270,6 +275,11 @@ class Engine:
         return out
 
     # ---- Q8_0-weight projections -----------------------------------------------------------------
+    def model_create(self, hidden_dim, num_heads, num_kv_heads, head_dim, intermediate_dim, vocab_size, num_layers,
+                     rms_norm_eps) -> "ResidentModel":
+        return ResidentModel(self, hidden_dim, num_heads, num_kv_heads, head_dim, intermediate_dim, vocab_size, num_layers,
+                             rms_norm_eps)
+
     def weight_upload_q8_0(self, blocks, rows: int, cols: int) -> "Q8Weight":
         return Q8Weight(self, blocks, rows, cols)
 
@@ -372,6 +382,77 @@ class Q8Weight:
     def free(self):
         if getattr(self, "h", None) and getattr(self.eng, "h", None):
             self.L.flare_weight_free(self.h)
+        self.h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class ModelConfig(C.Structure):
+    _fields_ = [("hidden_dim", C.c_int), ("num_heads", C.c_int), ("num_kv_heads", C.c_int), ("head_dim", C.c_int),
+                ("intermediate_dim", C.c_int), ("vocab_size", C.c_int), ("num_layers", C.c_int), ("rms_norm_eps", C.c_float)]
+
+
+class ResidentModel:
+    """Weights of a Llama-style model with Q8_0 matrices on the device (flare_model), and the single-token forward
+    pass that stays there: the counterpart of WebGpuBackend::upload_weights_to_gpu + forward_single_token_gpu
+    (flare-gpu/src/backend.rs:4010-4375), computing what Model::forward computes on its Q8_0 path."""
+
+    def __init__(self, eng: Engine, hidden_dim, num_heads, num_kv_heads, head_dim, intermediate_dim, vocab_size, num_layers,
+                 rms_norm_eps):
+        self.eng, self.L = eng, eng.L
+        self.cfg = ModelConfig(hidden_dim, num_heads, num_kv_heads, head_dim, intermediate_dim, vocab_size, num_layers,
+                               rms_norm_eps)
+        h = _vp()
+        eng.check(self.L.flare_model_create(eng.h, C.byref(self.cfg), C.byref(h)))
+        self.h = h
+
+    def set_layer(self, layer, attn_norm, qkv, wo, ffn_norm, gate_up, down):
+        """Norms: f32 [hidden_dim]; matrices: Q8_0 block streams (uint8), qkv = wq, wk, wv stacked by rows, gate_up =
+        w_gate, w_up stacked by rows."""
+        c = self.cfg
+        q_dim, kv_dim = c.num_heads * c.head_dim, c.num_kv_heads * c.head_dim
+        f = lambda a: np.ascontiguousarray(a, dtype=np.float32).reshape(-1)
+        u = lambda a, rows, cols: self._blocks(a, rows, cols)
+        an, fn = f(attn_norm), f(ffn_norm)
+        assert an.size == c.hidden_dim and fn.size == c.hidden_dim
+        mats = [u(qkv, q_dim + 2 * kv_dim, c.hidden_dim), u(wo, c.hidden_dim, q_dim),
+                u(gate_up, 2 * c.intermediate_dim, c.hidden_dim), u(down, c.hidden_dim, c.intermediate_dim)]
+        self.eng.check(self.L.flare_model_set_layer(self.h, layer, _ptr(an), _ptr(mats[0]), _ptr(mats[1]), _ptr(fn),
+                                                    _ptr(mats[2]), _ptr(mats[3])))
+
+    @staticmethod
+    def _blocks(a, rows, cols):
+        a = np.ascontiguousarray(a, dtype=np.uint8).reshape(-1)
+        assert a.size == rows * (cols // 32) * 34, (a.size, rows, cols)
+        return a
+
+    def set_output(self, output_norm, output_q8=None, output_f32=None):
+        c = self.cfg
+        on = np.ascontiguousarray(output_norm, dtype=np.float32).reshape(-1)
+        assert on.size == c.hidden_dim and (output_q8 is None) != (output_f32 is None)
+        q8 = None if output_q8 is None else self._blocks(output_q8, c.vocab_size, c.hidden_dim)
+        f32 = None if output_f32 is None else np.ascontiguousarray(output_f32, dtype=np.float32).reshape(-1)
+        assert f32 is None or f32.size == c.vocab_size * c.hidden_dim
+        self.eng.check(self.L.flare_model_set_output(self.h, _ptr(on), None if q8 is None else _ptr(q8),
+                                                     None if f32 is None else _ptr(f32)))
+
+    def forward(self, kv: "KvCache", token_embed, positions) -> np.ndarray:
+        """One token per sequence of ``kv``: token_embed [batch][hidden_dim], positions [batch] -> logits
+        [batch][vocab_size].  Writes every layer's K/V row and advances the cache by one (Model::forward)."""
+        x = np.ascontiguousarray(token_embed, dtype=np.float32).reshape(-1, self.cfg.hidden_dim)
+        pos = np.ascontiguousarray(positions, dtype=np.int64).reshape(-1)
+        assert x.shape[0] == kv.batch == pos.size
+        logits = np.empty((kv.batch, self.cfg.vocab_size), dtype=np.float32)
+        self.eng.check(self.L.flare_forward_token(self.eng.h, self.h, kv.h, _ptr(x), _ptr(pos), _ptr(logits)))
+        return logits
+
+    def free(self):
+        if getattr(self, "h", None) and getattr(self.eng, "h", None):
+            self.L.flare_model_free(self.h)
         self.h = None
 
     def __del__(self):

@@ -12,6 +12,7 @@
 // is kept sequential: the lanes of a warp each own one input vector of the batch for that sum, so 32 sums run side
 // by side.  A weight row is read from HBM once for the whole batch.
 #include "common.cuh"
+#include <mutex>
 
 struct flare_weight {
     flare_attn_ctx* ctx = nullptr;
@@ -187,25 +188,8 @@ int flare_matvec_q8_0(flare_attn_ctx* ctx, const flare_weight* w, const float* x
         FLARE_CUDA_OK(ctx, cudaMemcpyAsync(d + x_off, x, xn * 4, cudaMemcpyHostToDevice, ctx->stream));
         dx = (const float*)(d + x_off); dout = (float*)(d + o_off);
     }
-    ctx->last_launch_overlappable = false;
-    {
-        const int threads = 256;
-        size_t g = (nblk * 32 + threads - 1) / threads;
-        if (g > 148 * 16) g = 148 * 16;
-        quantize_input_kernel<<<(int)g, threads, 0, ctx->stream>>>(dx, nblk, (int8_t*)(d + q_off), (float*)(d + s_off));
-        FLARE_LAUNCH_CHECK(ctx);
-    }
-    MatvecParams p;
-    p.w = w->blocks; p.xq = (const int8_t*)(d + q_off); p.xs = (const float*)(d + s_off); p.out = dout;
-    p.rows = w->rows; p.cols = w->cols; p.batch = batch;
-    const int smem = WARPS * WARP_SMEM;
-    static bool attr_done[64] = {};
-    if (!attr_done[ctx->device & 63]) {
-        FLARE_CUDA_OK(ctx, cudaFuncSetAttribute(matvec_q8_0_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        attr_done[ctx->device & 63] = true;
-    }
-    matvec_q8_0_kernel<<<(w->rows + WARPS - 1) / WARPS, 32 * WARPS, smem, ctx->stream>>>(p);
-    FLARE_LAUNCH_CHECK(ctx);
+    FLARE_TRY(flare_launch_quantize_input(ctx, dx, nblk, (int8_t*)(d + q_off), (float*)(d + s_off)));
+    FLARE_TRY(flare_launch_matvec_q8_0_preq(ctx, w, (const int8_t*)(d + q_off), (const float*)(d + s_off), batch, dout));
     if (!on_device) {
         FLARE_CUDA_OK(ctx, cudaMemcpyAsync(out, dout, on * 4, cudaMemcpyDeviceToHost, ctx->stream));
         FLARE_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
@@ -214,3 +198,39 @@ int flare_matvec_q8_0(flare_attn_ctx* ctx, const flare_weight* w, const float* x
 }
 
 }  // extern "C"
+
+// quantize_input_q8_0 of n_blocks blocks of 32 values, all on the device
+int flare_launch_quantize_input(flare_attn_ctx* ctx, const float* d_x, size_t n_blocks, int8_t* d_xq, float* d_xs) {
+    const int threads = 256;
+    size_t g = (n_blocks * 32 + threads - 1) / threads;
+    if (g > 148 * 16) g = 148 * 16;
+    if (g < 1) g = 1;
+    ctx->last_launch_overlappable = false;
+    quantize_input_kernel<<<(int)g, threads, 0, ctx->stream>>>(d_x, n_blocks, d_xq, d_xs);
+    FLARE_LAUNCH_CHECK(ctx);
+    return FLARE_OK;
+}
+
+// matvec_q8_0_preq_into for `batch` quantised input vectors, all on the device
+int flare_launch_matvec_q8_0_preq(flare_attn_ctx* ctx, const flare_weight* w, const int8_t* d_xq, const float* d_xs, int batch,
+                                  float* d_out) {
+    MatvecParams p;
+    p.w = w->blocks; p.xq = d_xq; p.xs = d_xs; p.out = d_out;
+    p.rows = w->rows; p.cols = w->cols; p.batch = batch;
+    const int smem = WARPS * WARP_SMEM;
+    {
+        static std::mutex m;
+        std::lock_guard<std::mutex> lock(m);
+        static bool attr_done[64] = {};
+        if (!attr_done[ctx->device & 63]) {
+            FLARE_CUDA_OK(ctx, cudaFuncSetAttribute(matvec_q8_0_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+            attr_done[ctx->device & 63] = true;
+        }
+    }
+    ctx->last_launch_overlappable = false;
+    matvec_q8_0_kernel<<<(w->rows + WARPS - 1) / WARPS, 32 * WARPS, smem, ctx->stream>>>(p);
+    FLARE_LAUNCH_CHECK(ctx);
+    return FLARE_OK;
+}
+
+void flare_weight_dims(const flare_weight* w, int* rows, int* cols) { *rows = w->rows; *cols = w->cols; }

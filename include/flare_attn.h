@@ -329,6 +329,43 @@ FLARE_API int flare_weight_free(flare_weight* w);
 FLARE_API int flare_matvec_q8_0(flare_attn_ctx* ctx, const flare_weight* w, const float* x, int batch, float* out,
                                 int on_device);
 
+/* ---------------------------------------------------------------- the whole token on the device
+ * Replaces ComputeBackend::forward_single_token_gpu (flare-core/src/model.rs:1697-1734;
+ * flare-gpu/src/backend.rs:4010-4375): weights, cache and every intermediate stay on the device, a token costs one
+ * upload of its embedding row and one download of its logits.  The arithmetic is the CPU's Q8_0 path
+ * (Model::forward_layers, model.rs:2010-2548, with use_q8_attn / use_q8_ffn): rmsnorm_quantize_q8_0 -> fused
+ * [wq; wk; wv] -> RoPE -> cache write -> attention -> wo -> residual -> rmsnorm_quantize_q8_0 -> fused
+ * [w_gate; w_up] -> silu(gate) * up -> w_down -> residual; then the final norm and the output matrix (Q8_0 as at
+ * model.rs:1759-1770, or f32 as at 1771-1779).  Integer dots, block sums, the rotation and every quantisation step
+ * are the reference's operation for operation; the sum of squares of a norm is a tree where the CPU adds left to
+ * right and exp() is the device's, so logits agree with the CPU within a tolerance, not bit for bit.
+ * Not handled: biases (Qwen2), post-norms and soft-caps (Gemma 2), MoE, LoRA.
+ *
+ * flare_model_set_layer   host pointers: the norms are [hidden_dim] f32; the matrices are GGUF Q8_0 block streams,
+ *                         qkv [(num_heads + 2 num_kv_heads) * head_dim][hidden_dim] = wq, wk, wv stacked by rows
+ *                         (FusedLayerWeights::qkv), wo [hidden_dim][num_heads * head_dim], gate_up
+ *                         [2 * intermediate_dim][hidden_dim] = w_gate, w_up stacked, down [hidden_dim][intermediate_dim].
+ * flare_model_set_output  output_norm [hidden_dim] and exactly one of the output matrix as Q8_0 blocks or as f32,
+ *                         [vocab_size][hidden_dim].
+ * flare_forward_token     one token for each of the cache's `batch` sequences: token_embed [batch][hidden_dim] and
+ *                         positions[batch] (absolute, for the rotary table set with flare_kv_set_rope_table) from the
+ *                         host, logits [batch][vocab_size] to the host.  Every layer's K/V row is written at the
+ *                         ring position and the cache is advanced by one at the end, as Model::forward does. */
+typedef struct flare_model flare_model;
+typedef struct flare_model_config {
+    int hidden_dim, num_heads, num_kv_heads, head_dim, intermediate_dim, vocab_size, num_layers;
+    float rms_norm_eps;
+} flare_model_config;
+FLARE_API int flare_model_create(flare_attn_ctx* ctx, const flare_model_config* cfg, flare_model** out_model);
+FLARE_API int flare_model_set_layer(flare_model* m, int layer, const float* attn_norm, const void* qkv_q8_0,
+                                    const void* wo_q8_0, const float* ffn_norm, const void* gate_up_q8_0,
+                                    const void* down_q8_0);
+FLARE_API int flare_model_set_output(flare_model* m, const float* output_norm, const void* output_q8_0,
+                                     const float* output_f32);
+FLARE_API int flare_model_free(flare_model* m);
+FLARE_API int flare_forward_token(flare_attn_ctx* ctx, flare_model* m, flare_kv* kv, const float* token_embed,
+                                  const int64_t* positions, float* logits);
+
 /* ---------------------------------------------------------------- one sequence over several GPUs
  * No counterpart in the reference (single device).  One process per GPU; every process creates its context,
  * then all of them make the same sequence of calls below.  The recurrence merged across GPUs is the block

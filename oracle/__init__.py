@@ -350,6 +350,98 @@ def matvec_q8_0(weight_blocks, x, rows) -> np.ndarray:
     return out
 
 
+def matvec_q8_0_preq(weight_blocks, scales, quants, rows) -> np.ndarray:
+    """matvec_q8_0_preq_into on an input that is already quantised."""
+    w, wp = _u8(weight_blocks)
+    scales = np.ascontiguousarray(scales, np.float32)
+    quants = np.ascontiguousarray(quants, np.int8)
+    out = np.empty(rows, np.float32)
+    L = lib()
+    L.orc_matvec_q8_0_preq.argtypes = [_u8p, _f32p, C.POINTER(C.c_int8), _sz, _sz, _f32p]
+    L.orc_matvec_q8_0_preq(wp, scales.ctypes.data_as(_f32p), quants.ctypes.data_as(C.POINTER(C.c_int8)), rows, scales.size,
+                           out.ctypes.data_as(_f32p))
+    return out
+
+
+# ---------------------------------------------------------------- the rest of a token's forward pass
+def rmsnorm_quantize_q8_0(x, weight, eps):
+    """rmsnorm_quantize_q8_0_into (model.rs:5581-5641): (f32 scales [n/32], i8 quants [n])."""
+    x, xp = _f(x)
+    weight, wp = _f(weight)
+    n = x.size
+    scales, quants = np.empty(n // 32, np.float32), np.empty(n, np.int8)
+    L = lib()
+    L.orc_rmsnorm_quantize_q8_0.argtypes = [_f32p, _f32p, C.c_float, _sz, _f32p, C.POINTER(C.c_int8)]
+    L.orc_rmsnorm_quantize_q8_0(xp, wp, eps, n, scales.ctypes.data_as(_f32p), quants.ctypes.data_as(C.POINTER(C.c_int8)))
+    return scales, quants
+
+
+def rmsnorm(x, weight, eps) -> np.ndarray:
+    """rmsnorm_into (model.rs:7456-7478)."""
+    x, xp = _f(x)
+    weight, wp = _f(weight)
+    out = np.empty(x.size, np.float32)
+    L = lib()
+    L.orc_rmsnorm_into.argtypes = [_f32p, _f32p, C.c_float, _sz, _f32p]
+    L.orc_rmsnorm_into(xp, wp, eps, x.size, out.ctypes.data_as(_f32p))
+    return out
+
+
+def silu_mul(gate, up) -> np.ndarray:
+    """silu_mul_cpu (model.rs:7078-7099)."""
+    gate, gp = _f(gate)
+    up, up_p = _f(up)
+    out = np.empty(gate.size, np.float32)
+    L = lib()
+    L.orc_silu_mul.argtypes = [_f32p, _f32p, _sz, _f32p]
+    L.orc_silu_mul(gp, up_p, gate.size, out.ctypes.data_as(_f32p))
+    return out
+
+
+def matvec_f32(mat, vec, rows, cols) -> np.ndarray:
+    mat, mp = _f(mat)
+    vec, vp = _f(vec)
+    out = np.empty(rows, np.float32)
+    L = lib()
+    L.orc_matvec_f32.argtypes = [_f32p, _f32p, _sz, _sz, _f32p]
+    L.orc_matvec_f32(mp, vp, rows, cols, out.ctypes.data_as(_f32p))
+    return out
+
+
+def forward_token_q8(cfg, layers, output_norm, output_q8, output_f32, cos, sin, theta, k_cache, v_cache, length, x, pos,
+                     store=None):
+    """One token of Model::forward on the Q8_0 path (model.rs:1740-1790, 2010-2548) for one sequence.
+
+    cfg: dict(hidden_dim, num_heads, num_kv_heads, head_dim, intermediate_dim, vocab_size, rms_norm_eps);
+    layers: list of dict(attn_norm, qkv, wo, ffn_norm, gate_up, down) with Q8_0 block streams (uint8);
+    k_cache / v_cache: per layer f32 arrays [max_seq][kv_dim], written at slot `length` (no ring wrap here);
+    store: what the cache does to a row before attention reads it back (None: kept as f32; a Q8_0 cache:
+    lambda r: dequant_q8_0(quantize_q8_0(r)));
+    x: the token's embedding row.  Returns the logits; the caller advances `length`."""
+    store = store or (lambda r: r)
+    dim, nh, nkv, hd = cfg["hidden_dim"], cfg["num_heads"], cfg["num_kv_heads"], cfg["head_dim"]
+    inter, eps = cfg["intermediate_dim"], cfg["rms_norm_eps"]
+    q_dim, kv_dim = nh * hd, nkv * hd
+    x = np.array(x, np.float32).copy()
+    for li, lw in enumerate(layers):
+        s, qn = rmsnorm_quantize_q8_0(x, lw["attn_norm"], eps)
+        qkv = matvec_q8_0_preq(lw["qkv"], s, qn, q_dim + 2 * kv_dim)
+        q = apply_rope_with_table(qkv[:q_dim], nh, hd, pos, theta, cos, sin)
+        k = apply_rope_with_table(qkv[q_dim:q_dim + kv_dim], nkv, hd, pos, theta, cos, sin)
+        k_cache[li][length] = store(k)
+        v_cache[li][length] = store(qkv[q_dim + kv_dim:])
+        attn = gqa_decode(q, k_cache[li], v_cache[li], nh, nkv, hd, length + 1)
+        x = x + matvec_q8_0(lw["wo"], attn, dim)
+        s, qn = rmsnorm_quantize_q8_0(x, lw["ffn_norm"], eps)
+        gu = matvec_q8_0_preq(lw["gate_up"], s, qn, 2 * inter)
+        hidden = silu_mul(gu[:inter], gu[inter:])
+        x = x + matvec_q8_0(lw["down"], hidden, dim)
+    normed = rmsnorm(x, output_norm, eps)
+    if output_q8 is not None:
+        return matvec_q8_0(output_q8, normed, cfg["vocab_size"])
+    return matvec_f32(output_f32, normed, cfg["vocab_size"], dim)
+
+
 # ---------------------------------------------------------------- caches
 class KvCache:
     """flare-core/src/kv_cache.rs:431-546."""

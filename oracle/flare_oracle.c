@@ -987,6 +987,58 @@ ORC_API void orc_matvec_q8_0_preq(const uint8_t* weight_data, const float* in_sc
 }
 
 
+/* flare-core/src/model.rs:5610-5641 (rmsnorm_quantize_q8_0_scalar): rms over the vector (squares added left to
+ * right in f32), then per block of 32: n = x * weight * inv_rms, amax, scale = amax / 127,
+ * inv_scale = 127 / amax (0 when scale == 0), q = round(n * inv_scale) as i8. */
+ORC_API void orc_rmsnorm_quantize_q8_0(const float* x, const float* weight, float eps, size_t dim, float* scales,
+                                       int8_t* quants) {
+    float sum_sq = 0.0f;
+    for (size_t i = 0; i < dim; i++) sum_sq += x[i] * x[i];
+    float rms = sqrtf(sum_sq / (float)dim + eps);
+    float inv_rms = 1.0f / rms;
+    for (size_t b = 0; b < dim / Q8_BLOCK; b++) {
+        float normed[Q8_BLOCK];
+        float amax = 0.0f;
+        for (int j = 0; j < Q8_BLOCK; j++) {
+            float n = x[b * Q8_BLOCK + j] * weight[b * Q8_BLOCK + j] * inv_rms;
+            normed[j] = n;
+            amax = fmaxf(amax, fabsf(n));
+        }
+        float scale = amax / 127.0f;
+        scales[b] = scale;
+        float inv_scale = (scale != 0.0f) ? 127.0f / amax : 0.0f;
+        for (int j = 0; j < Q8_BLOCK; j++) quants[b * Q8_BLOCK + j] = sat_i8(roundf(normed[j] * inv_scale));
+    }
+}
+
+/* flare-core/src/model.rs:7469-7478 (rmsnorm_scalar_into): out = (x * inv_rms) * weight. */
+ORC_API void orc_rmsnorm_into(const float* x, const float* weight, float eps, size_t dim, float* out) {
+    float sum_sq = 0.0f;
+    for (size_t i = 0; i < dim; i++) sum_sq += x[i] * x[i];
+    float rms = sqrtf(sum_sq / (float)dim + eps);
+    float inv_rms = 1.0f / rms;
+    for (size_t i = 0; i < dim; i++) out[i] = (x[i] * inv_rms) * weight[i];
+}
+
+/* flare-core/src/model.rs:7091-7099 (silu_mul_scalar): (g / (1 + exp(-g))) * up. */
+ORC_API void orc_silu_mul(const float* gate, const float* up, size_t n, float* out) {
+    for (size_t i = 0; i < n; i++) {
+        float g = gate[i];
+        out[i] = (g / (1.0f + expf(-g))) * up[i];
+    }
+}
+
+/* The f32 product of the output matrix (matvec, flare-core/src/model.rs:4968-5016, dispatches by platform: AVX2,
+ * NEON, Accelerate or matvec_scalar); restated as the plain left-to-right sum of a row.  The platform kernels add
+ * in other orders, so this one is compared within a tolerance on either side. */
+ORC_API void orc_matvec_f32(const float* mat, const float* vec, size_t rows, size_t cols, float* out) {
+    for (size_t r = 0; r < rows; r++) {
+        float s = 0.0f;
+        for (size_t c = 0; c < cols; c++) s += mat[r * cols + c] * vec[c];
+        out[r] = s;
+    }
+}
+
 ORC_API int orc_max_threads(void) {
     long n = sysconf(_SC_NPROCESSORS_ONLN);
     return n > 0 ? (int)n : 1;
