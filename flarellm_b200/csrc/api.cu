@@ -524,6 +524,23 @@ int flare_kv_write_step_rope_f32(flare_kv* kv, int layer, const float* key, cons
     return FLARE_OK;
 }
 
+// The same on device buffers with the positions already on the device (one upload per token, not per layer).
+int flare_kv_write_step_rope_device(flare_kv* kv, int layer, const float* d_key, const float* d_value, const long long* d_pos) {
+    FLARE_TRY(check_layer_seq(kv, layer, 0));
+    flare_attn_ctx* ctx = kv->ctx;
+    BIND(ctx);
+    const int* d_att; const int2* d_ring; int mx;
+    FLARE_TRY(upload_small(ctx, kv, 1, nullptr, &d_att, &d_ring, &mx));
+    if (kv->dtype == FLARE_KV_KIVI_REF || kv->dtype == FLARE_KV_KIVI_G32) {
+        const size_t bytes = (size_t)kv->batch * kv->kv_dim * sizeof(float);
+        FLARE_TRY(flare_ensure(ctx, &ctx->d_conv, &ctx->conv_bytes, bytes));
+        FLARE_CUDA_OK(ctx, cudaMemcpyAsync(ctx->d_conv, d_key, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+        FLARE_TRY(flare_launch_rope_rows(kv, (float*)ctx->d_conv, kv->batch, kv->num_kv_heads, d_pos));
+        return flare_launch_kv_write_step(kv, layer, d_ring, (const float*)ctx->d_conv, d_value);
+    }
+    return flare_launch_kv_write_step(kv, layer, d_ring, d_key, d_value, d_pos);
+}
+
 int flare_rope_rows_f32(flare_kv* kv, float* rows, int n_rows, int num_heads, const int64_t* positions, int on_device) {
     if (!kv) return FLARE_ERR_INVALID_ARG;
     flare_attn_ctx* ctx = kv->ctx;

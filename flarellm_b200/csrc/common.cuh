@@ -200,6 +200,7 @@ int flare_launch_kv_write(flare_kv* kv, int layer, int seq, int64_t first_abs_po
 int flare_launch_kv_write_step(flare_kv* kv, int layer, const int2* d_ring, const float* d_key, const float* d_value,
                                const long long* d_positions = nullptr);
 int flare_launch_rope_rows(flare_kv* kv, float* d_rows, int n_rows, int num_heads, const long long* d_positions);
+extern "C" int flare_kv_write_step_rope_device(flare_kv* kv, int layer, const float* d_key, const float* d_value, const long long* d_pos);
 // matvec.cu: the two halves of flare_matvec_q8_0 on device buffers
 struct flare_weight;
 int flare_launch_quantize_input(flare_attn_ctx* ctx, const float* d_x, size_t n_blocks, int8_t* d_xq, float* d_xs);

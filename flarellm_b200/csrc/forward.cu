@@ -40,6 +40,7 @@ struct flare_model {
     float *x = nullptr, *qkv = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *attn = nullptr, *proj = nullptr,
           *gate_up = nullptr, *normed = nullptr, *logits = nullptr, *xs = nullptr;
     int8_t* xq = nullptr;
+    long long* pos = nullptr;        // the token's absolute positions, uploaded once per call
 };
 
 namespace {
@@ -48,10 +49,8 @@ __device__ __forceinline__ int8_t to_i8_saturating(float r) {       // Rust `as 
     return (int8_t)((r != r) ? 0 : (r >= 127.0f ? 127 : (r <= -128.0f ? -128 : (int)r)));
 }
 
-// sum of squares of one row by a block of 256 threads, every thread gets the total
-__device__ __forceinline__ float block_sum_sq(const float* __restrict__ x, int dim, float* s_red) {
-    float s = 0.0f;
-    for (int i = threadIdx.x; i < dim; i += blockDim.x) s = fmaf(x[i], x[i], s);
+// sum over the block of one value per thread; every thread gets the total
+__device__ __forceinline__ float block_sum(float s, float* s_red) {
 #pragma unroll
     for (int off = 16; off; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
     if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = s;
@@ -61,33 +60,64 @@ __device__ __forceinline__ float block_sum_sq(const float* __restrict__ x, int d
     return t;
 }
 
-// rmsnorm_quantize_q8_0: one block per input vector; n = x * weight * inv_rms, then quantize_input_q8_0 per 32
-__global__ void __launch_bounds__(256) rmsnorm_quantize_kernel(const float* __restrict__ x, const float* __restrict__ weight,
-                                                               float eps, int dim, int8_t* __restrict__ xq,
-                                                               float* __restrict__ xs) {
-    __shared__ float s_red[8];
-    const float* row = x + (size_t)blockIdx.x * dim;
-    const float sum_sq = block_sum_sq(row, dim, s_red);
-    const float rms = __fsqrt_rn(__fadd_rn(__fdiv_rn(sum_sq, (float)dim), eps));
-    const float inv_rms = __fdiv_rn(1.0f, rms);
-    const int lane = threadIdx.x & 31, nb = dim / 32;
-    for (int blk = threadIdx.x >> 5; blk < nb; blk += blockDim.x >> 5) {
-        const int i = blk * 32 + lane;
-        const float n = __fmul_rn(__fmul_rn(row[i], weight[i]), inv_rms);
-        float amax = fabsf(n);
+__device__ __forceinline__ float block_sum_sq(const float* __restrict__ x, int dim, float* s_red) {
+    float s = 0.0f;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) s = fmaf(x[i], x[i], s);
+    return block_sum(s, s_red);
+}
+
+__device__ __forceinline__ void quantize_block_of_32(float n, int lane, int8_t* __restrict__ q_out, float* __restrict__ s_out) {
+    float amax = fabsf(n);
 #pragma unroll
-        for (int off = 16; off; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
-        const float scale = __fdiv_rn(amax, 127.0f);
-        const float inv_scale = scale != 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
-        xq[(size_t)blockIdx.x * dim + i] = to_i8_saturating(roundf(__fmul_rn(n, inv_scale)));
-        if (lane == 0) xs[(size_t)blockIdx.x * nb + blk] = scale;
+    for (int off = 16; off; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    const float scale = __fdiv_rn(amax, 127.0f);
+    const float inv_scale = scale != 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+    q_out[lane] = to_i8_saturating(roundf(__fmul_rn(n, inv_scale)));
+    if (lane == 0) *s_out = scale;
+}
+
+// rmsnorm_quantize_q8_0: one block per input vector; n = x * weight * inv_rms, then quantize_input_q8_0 per 32.
+// A warp owns the blocks warp, warp + n_warps, ...; up to eight of them stay in registers between the sum of squares
+// and the quantisation, so the row is read once and all its loads are in flight together.
+__global__ void __launch_bounds__(1024) rmsnorm_quantize_kernel(const float* __restrict__ x, const float* __restrict__ weight,
+                                                                float eps, int dim, int8_t* __restrict__ xq,
+                                                                float* __restrict__ xs) {
+    __shared__ float s_red[32];
+    const float* row = x + (size_t)blockIdx.x * dim;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5, nb = dim / 32;
+    int8_t* q_row = xq + (size_t)blockIdx.x * dim;
+    float* s_row = xs + (size_t)blockIdx.x * nb;
+    if (nb <= 8 * nw) {
+        float xv[8], wv[8];
+        float s = 0.0f;
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+            const int blk = warp + k * nw;
+            xv[k] = blk < nb ? row[blk * 32 + lane] : 0.0f;
+            wv[k] = blk < nb ? weight[blk * 32 + lane] : 0.0f;
+        }
+#pragma unroll
+        for (int k = 0; k < 8; k++) s = fmaf(xv[k], xv[k], s);
+        const float sum_sq = block_sum(s, s_red);
+        const float inv_rms = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sum_sq, (float)dim), eps)));
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+            const int blk = warp + k * nw;
+            if (blk < nb) quantize_block_of_32(__fmul_rn(__fmul_rn(xv[k], wv[k]), inv_rms), lane, q_row + blk * 32, s_row + blk);
+        }
+        return;
     }
+    const float sum_sq = block_sum_sq(row, dim, s_red);
+    const float inv_rms = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sum_sq, (float)dim), eps)));
+    for (int blk = warp; blk < nb; blk += nw)
+        quantize_block_of_32(__fmul_rn(__fmul_rn(row[blk * 32 + lane], weight[blk * 32 + lane]), inv_rms), lane,
+                             q_row + blk * 32, s_row + blk);
 }
 
 // rmsnorm_into: out = (x * inv_rms) * weight
-__global__ void __launch_bounds__(256) rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ weight, float eps,
+__global__ void __launch_bounds__(1024) rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ weight, float eps,
                                                       int dim, float* __restrict__ out) {
-    __shared__ float s_red[8];
+    __shared__ float s_red[32];
     const float* row = x + (size_t)blockIdx.x * dim;
     const float sum_sq = block_sum_sq(row, dim, s_red);
     const float rms = __fsqrt_rn(__fadd_rn(__fdiv_rn(sum_sq, (float)dim), eps));
@@ -169,6 +199,7 @@ void free_buffers(flare_model* m) {
     float** bufs[] = {&m->x, &m->qkv, &m->q, &m->k, &m->v, &m->attn, &m->proj, &m->gate_up, &m->normed, &m->logits, &m->xs};
     for (float** b : bufs) { cudaFree(*b); *b = nullptr; }
     cudaFree(m->xq); m->xq = nullptr;
+    cudaFree(m->pos); m->pos = nullptr;
     m->buf_batch = 0;
 }
 
@@ -187,7 +218,7 @@ int ensure_buffers(flare_model* m, int batch) {
         {&m->normed, B * c.hidden_dim}, {&m->logits, B * c.vocab_size}, {&m->xs, B * widest / 32 + 8}};
     for (auto& w : want)
         if (cudaMalloc((void**)w.p, w.n * sizeof(float)) != cudaSuccess) { cudaGetLastError(); free_buffers(m); return flare_set_error(ctx, FLARE_ERR_OOM, "forward buffers for %d sequences", batch); }
-    if (cudaMalloc((void**)&m->xq, B * widest) != cudaSuccess) { cudaGetLastError(); free_buffers(m); return flare_set_error(ctx, FLARE_ERR_OOM, "forward buffers for %d sequences", batch); }
+    if (cudaMalloc((void**)&m->xq, B * widest) != cudaSuccess || cudaMalloc((void**)&m->pos, B * sizeof(long long)) != cudaSuccess) { cudaGetLastError(); free_buffers(m); return flare_set_error(ctx, FLARE_ERR_OOM, "forward buffers for %d sequences", batch); }
     m->buf_batch = batch;
     return FLARE_OK;
 }
@@ -287,25 +318,32 @@ int flare_forward_token(flare_attn_ctx* ctx, flare_model* m, flare_kv* kv, const
     FLARE_TRY(ensure_buffers(m, B));
     const int dim = c.hidden_dim, inter = c.intermediate_dim, q_dim = c.num_heads * c.head_dim, kv_dim = c.num_kv_heads * c.head_dim;
     cudaStream_t st = ctx->stream;
+    const int norm_threads = dim >= 1024 ? 1024 : (dim >= 256 ? 256 : 32 * ((dim / 32 + 0) > 0 ? (dim / 32 < 8 ? dim / 32 : 8) : 1));
+    if (!kv->rope_cos) return flare_set_error(ctx, FLARE_ERR_STATE, "no rotary table: call flare_kv_set_rope_table first");
+    for (int b = 0; b < B; b++)
+        if (positions[b] < 0 || positions[b] >= kv->rope_len)
+            return flare_set_error(ctx, FLARE_ERR_INVALID_ARG, "positions[%d] = %lld is outside the rotary table of %d rows", b,
+                                   (long long)positions[b], kv->rope_len);
     FLARE_CUDA_OK(ctx, cudaMemcpyAsync(m->x, token_embed, (size_t)B * dim * sizeof(float), cudaMemcpyHostToDevice, st));
+    FLARE_CUDA_OK(ctx, cudaMemcpyAsync(m->pos, positions, (size_t)B * sizeof(long long), cudaMemcpyHostToDevice, st));
     ctx->last_launch_overlappable = false;
     for (int layer = 0; layer < c.num_layers; layer++) {
         const flare_model::Layer& L = m->layers[layer];
         // attention block
-        rmsnorm_quantize_kernel<<<B, 256, 0, st>>>(m->x, L.attn_norm, c.rms_norm_eps, dim, m->xq, m->xs);
+        rmsnorm_quantize_kernel<<<B, norm_threads, 0, st>>>(m->x, L.attn_norm, c.rms_norm_eps, dim, m->xq, m->xs);
         FLARE_LAUNCH_CHECK(ctx);
         FLARE_TRY(flare_launch_matvec_q8_0_preq(ctx, L.qkv, m->xq, m->xs, B, m->qkv));
         split_qkv_kernel<<<dim3(grid_for((size_t)q_dim + 2 * kv_dim), B), 256, 0, st>>>(m->qkv, q_dim, kv_dim, m->q, m->k, m->v);
         FLARE_LAUNCH_CHECK(ctx);
-        FLARE_TRY(flare_rope_rows_f32(kv, m->q, B, c.num_heads, positions, 1));
-        FLARE_TRY(flare_kv_write_step_rope_f32(kv, layer, m->k, m->v, positions, 1));
+        FLARE_TRY(flare_launch_rope_rows(kv, m->q, B, c.num_heads, m->pos));
+        FLARE_TRY(flare_kv_write_step_rope_device(kv, layer, m->k, m->v, m->pos));
         FLARE_TRY(flare_decode_attn(ctx, kv, layer, c.num_heads, m->q, 1, nullptr, 0.0f, m->attn, 1));
         FLARE_TRY(flare_launch_quantize_input(ctx, m->attn, (size_t)B * q_dim / 32, m->xq, m->xs));
         FLARE_TRY(flare_launch_matvec_q8_0_preq(ctx, L.wo, m->xq, m->xs, B, m->proj));
         add_rows_kernel<<<grid_for((size_t)B * dim), 256, 0, st>>>(m->x, m->proj, (size_t)B * dim);
         FLARE_LAUNCH_CHECK(ctx);
         // feed-forward block
-        rmsnorm_quantize_kernel<<<B, 256, 0, st>>>(m->x, L.ffn_norm, c.rms_norm_eps, dim, m->xq, m->xs);
+        rmsnorm_quantize_kernel<<<B, norm_threads, 0, st>>>(m->x, L.ffn_norm, c.rms_norm_eps, dim, m->xq, m->xs);
         FLARE_LAUNCH_CHECK(ctx);
         FLARE_TRY(flare_launch_matvec_q8_0_preq(ctx, L.gate_up, m->xq, m->xs, B, m->gate_up));
         silu_mul_quantize_kernel<<<grid_for((size_t)B * inter), 256, 0, st>>>(m->gate_up, inter, (size_t)B * inter / 32, m->xq, m->xs);
@@ -315,7 +353,7 @@ int flare_forward_token(flare_attn_ctx* ctx, flare_model* m, flare_kv* kv, const
         FLARE_LAUNCH_CHECK(ctx);
         ctx->last_launch_overlappable = false;
     }
-    rmsnorm_kernel<<<B, 256, 0, st>>>(m->x, m->output_norm, c.rms_norm_eps, dim, m->normed);
+    rmsnorm_kernel<<<B, norm_threads, 0, st>>>(m->x, m->output_norm, c.rms_norm_eps, dim, m->normed);
     FLARE_LAUNCH_CHECK(ctx);
     if (m->output_q8) {
         FLARE_TRY(flare_launch_quantize_input(ctx, m->normed, (size_t)B * dim / 32, m->xq, m->xs));

@@ -17,15 +17,29 @@
 struct flare_weight {
     flare_attn_ctx* ctx = nullptr;
     int rows = 0, cols = 0;
-    unsigned char* blocks = nullptr;     // [rows][cols / 32] x 34 bytes: f16 LE scale, 32 x i8 (GGUF Q8_0)
+    // the GGUF block stream (f16 LE scale + 32 x i8 per 34 bytes) taken apart at upload, so that the 32 weights
+    // of a block start on a 32-byte boundary: same numbers, same bytes per block read
+    int8_t* qs = nullptr;        // [rows][cols]
+    __half* sc = nullptr;        // [rows][cols / 32]
 };
 
 namespace {
 
 constexpr int CHUNK = 64;            // blocks of a row handled per pass: two per lane
 constexpr int WARPS = 8;
-constexpr int TS = CHUNK + 1;        // floats per input vector in the product buffer
-constexpr int WARP_SMEM = CHUNK * 34 + 32 * TS * 4;      // 2176 + 8320 bytes, a multiple of 16
+constexpr int TS = CHUNK + 1;        // floats per input vector in the product buffer (odd: no bank conflicts in the sums)
+
+// one thread per block: 34 bytes -> scale plane + weight plane
+__global__ void repack_q8_0_kernel(const unsigned char* __restrict__ blocks, size_t n_blocks, int8_t* __restrict__ qs,
+                                   __half* __restrict__ sc) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n_blocks; i += (size_t)gridDim.x * blockDim.x) {
+        const uint16_t* b16 = reinterpret_cast<const uint16_t*>(blocks + i * 34);
+        sc[i] = __ushort_as_half(b16[0]);
+        uint16_t* d16 = reinterpret_cast<uint16_t*>(qs + i * 32);
+#pragma unroll
+        for (int j = 0; j < 16; j++) d16[j] = b16[1 + j];
+    }
+}
 
 // quantize_input_q8_0: one warp per 32-value block, lane = element
 __global__ void quantize_input_kernel(const float* __restrict__ x, size_t n_blocks, int8_t* __restrict__ xq,
@@ -46,88 +60,87 @@ __global__ void quantize_input_kernel(const float* __restrict__ x, size_t n_bloc
 }
 
 struct MatvecParams {
-    const unsigned char* w;      // weight blocks
+    const int8_t* wq;            // [rows][cols]
+    const __half* ws;            // [rows][cols / 32]
     const int8_t* xq;            // [batch][cols]
     const float* xs;             // [batch][cols / 32]
     float* out;                  // [batch][rows]
     int rows, cols, batch;
+    int bt;                      // input vectors per tile: min(batch, 32); sizes the product buffer
 };
 
+// A warp owns one row at a time.  Per chunk of 64 blocks every lane holds two blocks of the row in registers
+// (two 16-byte loads each, the warp reads 2 KB contiguous), multiplies them with every input vector of the tile
+// and leaves the products in shared memory; then lane b adds the chunk's products of input vector b in block order.
 __global__ void __launch_bounds__(32 * WARPS) matvec_q8_0_kernel(MatvecParams p) {
-    extern __shared__ __align__(16) unsigned char smem[];
+    extern __shared__ __align__(16) float terms_all[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int row = blockIdx.x * WARPS + warp;
-    if (row >= p.rows) return;
     const int nb = p.cols / 32;
-    // per warp: the current chunk of the weight row (CHUNK x 34 = 2176 bytes) and the products
-    // [input vector of the batch tile][block of the chunk], rows padded by one float against bank conflicts
-    unsigned char* wrow = smem + (size_t)warp * WARP_SMEM;
-    float* terms = reinterpret_cast<float*>(wrow + CHUNK * 34);
-    const unsigned char* src = p.w + (size_t)row * nb * 34;
+    float* terms = terms_all + (size_t)warp * p.bt * TS;
     const int n_tiles = (p.batch + 31) / 32;
-    float sum[8];                                     // running sums of this lane's input vector in each batch tile (batch <= 256)
+    for (int row = blockIdx.x * WARPS + warp; row < p.rows; row += gridDim.x * WARPS) {
+        const int8_t* wrow = p.wq + (size_t)row * p.cols;
+        const __half* srow = p.ws + (size_t)row * nb;
+        float sum[8];                                 // running sums of this lane's input vector in each batch tile (batch <= 256)
 #pragma unroll
-    for (int t = 0; t < 8; t++) sum[t] = 0.0f;
-    for (int c0 = 0; c0 < nb; c0 += CHUNK) {
-        const int cn = min(CHUNK, nb - c0);
-        __syncwarp();
-        // the chunk's bytes, as 16-bit units (a row of 34-byte blocks starts on a 2-byte boundary)
-        const uint16_t* s16 = reinterpret_cast<const uint16_t*>(src + (size_t)c0 * 34);
-        uint16_t* d16 = reinterpret_cast<uint16_t*>(wrow);
-        for (int i = lane; i < cn * 17; i += 32) d16[i] = __ldg(s16 + i);
-        __syncwarp();
-        // this lane's (up to) two blocks of the chunk: scale and the 32 weights as eight 32-bit words
-        float wsc[2];
-        int wq[2][8];
+        for (int t = 0; t < 8; t++) sum[t] = 0.0f;
+        for (int c0 = 0; c0 < nb; c0 += CHUNK) {
+            const int cn = min(CHUNK, nb - c0);
+            // this lane's (up to) two blocks of the chunk
+            float wsc[2];
+            int4 w0[2], w1[2];
 #pragma unroll
-        for (int k = 0; k < 2; k++) {
-            const int blk = lane + 32 * k;
-            if (blk < cn) {
-                const uint16_t* b16 = d16 + blk * 17;
-                wsc[k] = __half2float(__ushort_as_half(b16[0]));
-#pragma unroll
-                for (int j = 0; j < 8; j++) wq[k][j] = (int)b16[1 + 2 * j] | ((int)b16[2 + 2 * j] << 16);
-            } else {
-                wsc[k] = 0.0f;
-#pragma unroll
-                for (int j = 0; j < 8; j++) wq[k][j] = 0;
-            }
-        }
-#pragma unroll 1
-        for (int t = 0; t < n_tiles; t++) {
-            const int bn = min(32, p.batch - 32 * t);
-            // products of this lane's blocks with every input vector of the tile
-            for (int b = 0; b < bn; b++) {
-                const size_t vec = (size_t)(32 * t + b);
-#pragma unroll
-                for (int k = 0; k < 2; k++) {
-                    const int blk = lane + 32 * k;
-                    if (blk < cn) {
-                        const int4* xp = reinterpret_cast<const int4*>(p.xq + vec * p.cols + (size_t)(c0 + blk) * 32);
-                        const int4 x0 = __ldg(xp), x1 = __ldg(xp + 1);
-                        int acc = 0;
-                        acc = __dp4a(wq[k][0], x0.x, acc); acc = __dp4a(wq[k][1], x0.y, acc);
-                        acc = __dp4a(wq[k][2], x0.z, acc); acc = __dp4a(wq[k][3], x0.w, acc);
-                        acc = __dp4a(wq[k][4], x1.x, acc); acc = __dp4a(wq[k][5], x1.y, acc);
-                        acc = __dp4a(wq[k][6], x1.z, acc); acc = __dp4a(wq[k][7], x1.w, acc);
-                        const float cs = __fmul_rn(wsc[k], __ldg(p.xs + vec * nb + c0 + blk));
-                        terms[b * TS + blk] = __fmul_rn(cs, (float)acc);
-                    }
+            for (int k = 0; k < 2; k++) {
+                const int blk = lane + 32 * k;
+                if (blk < cn) {
+                    const int4* wp = reinterpret_cast<const int4*>(wrow + (size_t)(c0 + blk) * 32);
+                    asm volatile("ld.global.nc.L1::no_allocate.v4.s32 {%0, %1, %2, %3}, [%4];"
+                                 : "=r"(w0[k].x), "=r"(w0[k].y), "=r"(w0[k].z), "=r"(w0[k].w) : "l"(wp));
+                    asm volatile("ld.global.nc.L1::no_allocate.v4.s32 {%0, %1, %2, %3}, [%4];"
+                                 : "=r"(w1[k].x), "=r"(w1[k].y), "=r"(w1[k].z), "=r"(w1[k].w) : "l"(wp + 1));
+                    wsc[k] = __half2float(srow[c0 + blk]);
+                } else {
+                    wsc[k] = 0.0f;
+                    w0[k] = make_int4(0, 0, 0, 0); w1[k] = make_int4(0, 0, 0, 0);
                 }
             }
-            __syncwarp();
-            // lane b adds the chunk's products of input vector b in block order
-            if (lane < bn) {
-                float s = sum[t];
-                for (int blk = 0; blk < cn; blk++) s = __fadd_rn(s, terms[lane * TS + blk]);
-                sum[t] = s;
-            }
-            __syncwarp();
-        }
-    }
+#pragma unroll 1
+            for (int t = 0; t < n_tiles; t++) {
+                const int bn = min(32, p.batch - 32 * t);
+                __syncwarp();                         // the sums of the previous pass have read the buffer
+                for (int b = 0; b < bn; b++) {
+                    const size_t vec = (size_t)(32 * t + b);
 #pragma unroll
-    for (int t = 0; t < 8; t++)
-        if (t < n_tiles && 32 * t + lane < p.batch) p.out[(size_t)(32 * t + lane) * p.rows + row] = sum[t];
+                    for (int k = 0; k < 2; k++) {
+                        const int blk = lane + 32 * k;
+                        if (blk < cn) {
+                            const int4* xp = reinterpret_cast<const int4*>(p.xq + vec * p.cols + (size_t)(c0 + blk) * 32);
+                            const int4 x0 = __ldg(xp), x1 = __ldg(xp + 1);
+                            int acc = 0;
+                            acc = __dp4a(w0[k].x, x0.x, acc); acc = __dp4a(w0[k].y, x0.y, acc);
+                            acc = __dp4a(w0[k].z, x0.z, acc); acc = __dp4a(w0[k].w, x0.w, acc);
+                            acc = __dp4a(w1[k].x, x1.x, acc); acc = __dp4a(w1[k].y, x1.y, acc);
+                            acc = __dp4a(w1[k].z, x1.z, acc); acc = __dp4a(w1[k].w, x1.w, acc);
+                            const float cs = __fmul_rn(wsc[k], __ldg(p.xs + vec * nb + c0 + blk));
+                            terms[b * TS + blk] = __fmul_rn(cs, (float)acc);
+                        }
+                    }
+                }
+                __syncwarp();
+                // lane b adds the chunk's products of input vector b in block order
+                if (lane < bn) {
+                    float s = sum[t];
+                    const float* tp = terms + lane * TS;
+#pragma unroll 8
+                    for (int blk = 0; blk < cn; blk++) s = __fadd_rn(s, tp[blk]);
+                    sum[t] = s;
+                }
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < 8; t++)
+            if (t < n_tiles && 32 * t + lane < p.batch) p.out[(size_t)(32 * t + lane) * p.rows + row] = sum[t];
+    }
 }
 
 }  // namespace
@@ -144,15 +157,25 @@ int flare_weight_upload_q8_0(flare_attn_ctx* ctx, const void* blocks, int rows, 
     flare_weight* w = new (std::nothrow) flare_weight();
     if (!w) return FLARE_ERR_OOM;
     w->ctx = ctx; w->rows = rows; w->cols = cols;
-    const size_t bytes = (size_t)rows * (cols / 32) * 34;
-    cudaError_t e = cudaMalloc(&w->blocks, bytes + 64);
-    if (e == cudaSuccess) e = cudaMemcpyAsync(w->blocks, blocks, bytes, cudaMemcpyHostToDevice, ctx->stream);
+    const size_t n_blocks = (size_t)rows * (cols / 32), bytes = n_blocks * 34;
+    unsigned char* raw = nullptr;
+    cudaError_t e = cudaMalloc(&raw, bytes + 64);
+    if (e == cudaSuccess) e = cudaMalloc(&w->qs, n_blocks * 32);
+    if (e == cudaSuccess) e = cudaMalloc(&w->sc, n_blocks * sizeof(__half));
+    if (e == cudaSuccess) e = cudaMemcpyAsync(raw, blocks, bytes, cudaMemcpyHostToDevice, ctx->stream);
+    if (e == cudaSuccess) {
+        size_t g = (n_blocks + 255) / 256;
+        if (g > 148 * 32) g = 148 * 32;
+        repack_q8_0_kernel<<<(int)g, 256, 0, ctx->stream>>>(raw, n_blocks, w->qs, w->sc);
+        e = cudaGetLastError();
+    }
     if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    cudaFree(raw);
     if (e != cudaSuccess) {
         const int code = e == cudaErrorMemoryAllocation ? FLARE_ERR_OOM : FLARE_ERR_CUDA;
         flare_set_error(ctx, code, "flare_weight_upload_q8_0: %zu bytes: %s", bytes, cudaGetErrorString(e));
         cudaGetLastError();
-        cudaFree(w->blocks);
+        cudaFree(w->qs); cudaFree(w->sc);
         delete w;
         return code;
     }
@@ -164,7 +187,7 @@ int flare_weight_free(flare_weight* w) {
     if (!w) return FLARE_OK;
     cudaSetDevice(w->ctx->device);
     cudaStreamSynchronize(w->ctx->stream);
-    cudaFree(w->blocks);
+    cudaFree(w->qs); cudaFree(w->sc);
     delete w;
     return FLARE_OK;
 }
@@ -215,20 +238,26 @@ int flare_launch_quantize_input(flare_attn_ctx* ctx, const float* d_x, size_t n_
 int flare_launch_matvec_q8_0_preq(flare_attn_ctx* ctx, const flare_weight* w, const int8_t* d_xq, const float* d_xs, int batch,
                                   float* d_out) {
     MatvecParams p;
-    p.w = w->blocks; p.xq = d_xq; p.xs = d_xs; p.out = d_out;
+    p.wq = w->qs; p.ws = w->sc; p.xq = d_xq; p.xs = d_xs; p.out = d_out;
     p.rows = w->rows; p.cols = w->cols; p.batch = batch;
-    const int smem = WARPS * WARP_SMEM;
+    p.bt = batch < 32 ? batch : 32;
+    const int smem = WARPS * p.bt * TS * (int)sizeof(float);
     {
         static std::mutex m;
         std::lock_guard<std::mutex> lock(m);
         static bool attr_done[64] = {};
         if (!attr_done[ctx->device & 63]) {
-            FLARE_CUDA_OK(ctx, cudaFuncSetAttribute(matvec_q8_0_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+            FLARE_CUDA_OK(ctx, cudaFuncSetAttribute(matvec_q8_0_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                    WARPS * 32 * TS * (int)sizeof(float)));
             attr_done[ctx->device & 63] = true;
         }
     }
+    // a row per warp; many more warps than the SMs hold at once are pointless, so large matrices loop
+    int grid = (w->rows + WARPS - 1) / WARPS;
+    const int max_grid = 148 * 8 * 4;
+    if (grid > max_grid) grid = max_grid;
     ctx->last_launch_overlappable = false;
-    matvec_q8_0_kernel<<<(w->rows + WARPS - 1) / WARPS, 32 * WARPS, smem, ctx->stream>>>(p);
+    matvec_q8_0_kernel<<<grid, 32 * WARPS, smem, ctx->stream>>>(p);
     FLARE_LAUNCH_CHECK(ctx);
     return FLARE_OK;
 }

@@ -35,14 +35,15 @@ def _make_model(orc, rng, cfg, n_layers, output_q8):
     return layers, output_norm, None, rng.standard_normal((cfg["vocab_size"], dim), dtype=np.float32) * np.float32(dim ** -0.5)
 
 
-@pytest.mark.parametrize("kv_dtype,output_q8,batch,nh,nkv,hd", [
-    ("f32", True, 1, 4, 2, 64),          # the f32 cache the reference's own forward keeps
-    ("q8_0", False, 2, 8, 2, 64),        # quantised cache (tensor-core attention), f32 output matrix, two sequences
+@pytest.mark.parametrize("kv_dtype,output_q8,batch,nh,nkv,hd,dim,inter,vocab", [
+    ("f32", True, 1, 4, 2, 64, 256, 512, 1000),        # the f32 cache the reference's own forward keeps
+    ("q8_0", False, 2, 8, 2, 64, 256, 512, 1000),      # quantised cache (tensor-core attention), f32 output matrix, two sequences
+    ("f32", True, 1, 16, 4, 64, 1024, 2048, 4096),     # rows of 32 and 64 blocks: the 16-byte weight loads of the product
 ])
-def test_forward_token_matches_the_cpu_path(orc, kv_dtype, output_q8, batch, nh, nkv, hd):
+def test_forward_token_matches_the_cpu_path(orc, kv_dtype, output_q8, batch, nh, nkv, hd, dim, inter, vocab):
     import flarellm_b200 as fb
     rng = np.random.default_rng(11 + batch)
-    cfg = dict(hidden_dim=256, num_heads=nh, num_kv_heads=nkv, head_dim=hd, intermediate_dim=512, vocab_size=1000,
+    cfg = dict(hidden_dim=dim, num_heads=nh, num_kv_heads=nkv, head_dim=hd, intermediate_dim=inter, vocab_size=vocab,
                rms_norm_eps=1e-5)
     n_layers, max_seq, theta, n_tokens = 2, 64, 10000.0, 6
     layers, output_norm, out_q8, out_f32 = _make_model(orc, rng, cfg, n_layers, output_q8)
