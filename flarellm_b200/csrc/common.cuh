@@ -201,11 +201,30 @@ int flare_launch_kv_write_step(flare_kv* kv, int layer, const int2* d_ring, cons
                                const long long* d_positions = nullptr);
 int flare_launch_rope_rows(flare_kv* kv, float* d_rows, int n_rows, int num_heads, const long long* d_positions);
 extern "C" int flare_kv_write_step_rope_device(flare_kv* kv, int layer, const float* d_key, const float* d_value, const long long* d_pos);
+// Programmatic dependent launch for chains of small kernels (the forward pass): a kernel launched with
+// flare_launch_pdl may be scheduled while its predecessor in the stream still runs; it begins with
+// flare_pdl_wait(), which returns once the predecessor has completed and its writes are visible, and then lets its
+// own successor be scheduled with flare_pdl_trigger().  Nothing is read or written before the wait, so the only
+// effect is that the launch latency of a kernel hides behind the kernel before it.
+#ifdef __CUDACC__
+__device__ __forceinline__ void flare_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void flare_pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+template <typename... KArgs, typename... Args>
+inline cudaError_t flare_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
 // matvec.cu: the two halves of flare_matvec_q8_0 on device buffers
 struct flare_weight;
 int flare_launch_quantize_input(flare_attn_ctx* ctx, const float* d_x, size_t n_blocks, int8_t* d_xq, float* d_xs);
 int flare_launch_matvec_q8_0_preq(flare_attn_ctx* ctx, const flare_weight* w, const int8_t* d_xq, const float* d_xs, int batch,
-                                  float* d_out);
+                                  float* d_out, int accumulate);
 void flare_weight_dims(const flare_weight* w, int* rows, int* cols);
 int flare_launch_kv_export_dequant(flare_kv* kv, int layer, int seq, float* d_k, float* d_v);
 int flare_launch_q8_blocks(flare_kv* kv, int layer, int seq, int first_slot, int n_slots, void* d_kb, void* d_vb,

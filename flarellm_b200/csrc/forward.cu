@@ -20,6 +20,7 @@
 // CPU adds left to right, and exp() is the device's expf; so a forward pass agrees with the CPU within a
 // tolerance, not bit for bit.  Biases (Qwen2), post-norms and soft-caps (Gemma 2), MoE and LoRA are not handled.
 #include "common.cuh"
+#include "q8_input.cuh"
 
 #include <vector>
 
@@ -45,78 +46,28 @@ struct flare_model {
 
 namespace {
 
-__device__ __forceinline__ int8_t to_i8_saturating(float r) {       // Rust `as i8`
-    return (int8_t)((r != r) ? 0 : (r >= 127.0f ? 127 : (r <= -128.0f ? -128 : (int)r)));
-}
-
-// sum over the block of one value per thread; every thread gets the total
-__device__ __forceinline__ float block_sum(float s, float* s_red) {
-#pragma unroll
-    for (int off = 16; off; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-    if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = s;
-    __syncthreads();
-    float t = 0.0f;
-    for (int w = 0; w < (int)(blockDim.x >> 5); w++) t += s_red[w];
-    return t;
+// rmsnorm_quantize_q8_0: one block per input vector
+__global__ void __launch_bounds__(256) rmsnorm_quantize_kernel(const float* __restrict__ x, const float* __restrict__ weight,
+                                                                float eps, int dim, int8_t* __restrict__ xq,
+                                                                float* __restrict__ xs) {
+    flare_pdl_wait();
+    flare_pdl_trigger();
+    __shared__ float s_red[32];
+    flare_quantize_vector(x + (size_t)blockIdx.x * dim, weight, eps, dim, xq + (size_t)blockIdx.x * dim,
+                          xs + (size_t)blockIdx.x * (dim / 32), s_red);
 }
 
 __device__ __forceinline__ float block_sum_sq(const float* __restrict__ x, int dim, float* s_red) {
     float s = 0.0f;
     for (int i = threadIdx.x; i < dim; i += blockDim.x) s = fmaf(x[i], x[i], s);
-    return block_sum(s, s_red);
-}
-
-__device__ __forceinline__ void quantize_block_of_32(float n, int lane, int8_t* __restrict__ q_out, float* __restrict__ s_out) {
-    float amax = fabsf(n);
-#pragma unroll
-    for (int off = 16; off; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
-    const float scale = __fdiv_rn(amax, 127.0f);
-    const float inv_scale = scale != 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
-    q_out[lane] = to_i8_saturating(roundf(__fmul_rn(n, inv_scale)));
-    if (lane == 0) *s_out = scale;
-}
-
-// rmsnorm_quantize_q8_0: one block per input vector; n = x * weight * inv_rms, then quantize_input_q8_0 per 32.
-// A warp owns the blocks warp, warp + n_warps, ...; up to eight of them stay in registers between the sum of squares
-// and the quantisation, so the row is read once and all its loads are in flight together.
-__global__ void __launch_bounds__(1024) rmsnorm_quantize_kernel(const float* __restrict__ x, const float* __restrict__ weight,
-                                                                float eps, int dim, int8_t* __restrict__ xq,
-                                                                float* __restrict__ xs) {
-    __shared__ float s_red[32];
-    const float* row = x + (size_t)blockIdx.x * dim;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5, nb = dim / 32;
-    int8_t* q_row = xq + (size_t)blockIdx.x * dim;
-    float* s_row = xs + (size_t)blockIdx.x * nb;
-    if (nb <= 8 * nw) {
-        float xv[8], wv[8];
-        float s = 0.0f;
-#pragma unroll
-        for (int k = 0; k < 8; k++) {
-            const int blk = warp + k * nw;
-            xv[k] = blk < nb ? row[blk * 32 + lane] : 0.0f;
-            wv[k] = blk < nb ? weight[blk * 32 + lane] : 0.0f;
-        }
-#pragma unroll
-        for (int k = 0; k < 8; k++) s = fmaf(xv[k], xv[k], s);
-        const float sum_sq = block_sum(s, s_red);
-        const float inv_rms = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sum_sq, (float)dim), eps)));
-#pragma unroll
-        for (int k = 0; k < 8; k++) {
-            const int blk = warp + k * nw;
-            if (blk < nb) quantize_block_of_32(__fmul_rn(__fmul_rn(xv[k], wv[k]), inv_rms), lane, q_row + blk * 32, s_row + blk);
-        }
-        return;
-    }
-    const float sum_sq = block_sum_sq(row, dim, s_red);
-    const float inv_rms = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sum_sq, (float)dim), eps)));
-    for (int blk = warp; blk < nb; blk += nw)
-        quantize_block_of_32(__fmul_rn(__fmul_rn(row[blk * 32 + lane], weight[blk * 32 + lane]), inv_rms), lane,
-                             q_row + blk * 32, s_row + blk);
+    return flare_block_sum(s, s_red);
 }
 
 // rmsnorm_into: out = (x * inv_rms) * weight
 __global__ void __launch_bounds__(1024) rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ weight, float eps,
                                                       int dim, float* __restrict__ out) {
+    flare_pdl_wait();
+    flare_pdl_trigger();
     __shared__ float s_red[32];
     const float* row = x + (size_t)blockIdx.x * dim;
     const float sum_sq = block_sum_sq(row, dim, s_red);
@@ -126,14 +77,11 @@ __global__ void __launch_bounds__(1024) rmsnorm_kernel(const float* __restrict__
         out[(size_t)blockIdx.x * dim + i] = __fmul_rn(__fmul_rn(row[i], inv_rms), weight[i]);
 }
 
-__global__ void add_rows_kernel(float* __restrict__ x, const float* __restrict__ y, size_t n) {
-    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
-        x[i] = __fadd_rn(x[i], y[i]);
-}
-
 // rows of [q | k | v] -> three dense buffers
 __global__ void split_qkv_kernel(const float* __restrict__ qkv, int q_dim, int kv_dim, float* __restrict__ q,
                                  float* __restrict__ k, float* __restrict__ v) {
+    flare_pdl_wait();
+    flare_pdl_trigger();
     const int b = blockIdx.y, total = q_dim + 2 * kv_dim;
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
         const float val = qkv[(size_t)b * total + i];
@@ -146,6 +94,8 @@ __global__ void split_qkv_kernel(const float* __restrict__ qkv, int q_dim, int k
 // hidden = silu(gate) * up out of rows of [gate | up], quantised per 32 as quantize_input_q8_0 does: a warp per block
 __global__ void silu_mul_quantize_kernel(const float* __restrict__ gate_up, int inter, size_t n_blocks,
                                          int8_t* __restrict__ xq, float* __restrict__ xs) {
+    flare_pdl_wait();
+    flare_pdl_trigger();
     const int lane = threadIdx.x & 31, nb = inter / 32;
     for (size_t w = (blockIdx.x * (size_t)blockDim.x + threadIdx.x) >> 5; w < n_blocks; w += ((size_t)gridDim.x * blockDim.x) >> 5) {
         const size_t b = w / nb, blk = w % nb;
@@ -157,7 +107,7 @@ __global__ void silu_mul_quantize_kernel(const float* __restrict__ gate_up, int 
         for (int off = 16; off; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
         const float d = __fdiv_rn(amax, 127.0f);
         const float id = d != 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
-        xq[w * 32 + lane] = to_i8_saturating(roundf(__fmul_rn(h, id)));
+        xq[w * 32 + lane] = flare_to_i8_saturating(roundf(__fmul_rn(h, id)));
         if (lane == 0) xs[w] = d;
     }
 }
@@ -165,6 +115,8 @@ __global__ void silu_mul_quantize_kernel(const float* __restrict__ gate_up, int 
 // f32 output matrix: a warp per row, the input vectors of the batch one after the other
 __global__ void __launch_bounds__(256) matvec_f32_kernel(const float* __restrict__ w, const float* __restrict__ x, int rows,
                                                          int cols, int batch, float* __restrict__ out) {
+    flare_pdl_wait();
+    flare_pdl_trigger();
     const int lane = threadIdx.x & 31;
     const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= rows) return;
@@ -318,7 +270,8 @@ int flare_forward_token(flare_attn_ctx* ctx, flare_model* m, flare_kv* kv, const
     FLARE_TRY(ensure_buffers(m, B));
     const int dim = c.hidden_dim, inter = c.intermediate_dim, q_dim = c.num_heads * c.head_dim, kv_dim = c.num_kv_heads * c.head_dim;
     cudaStream_t st = ctx->stream;
-    const int norm_threads = dim >= 1024 ? 1024 : (dim >= 256 ? 256 : 32 * ((dim / 32 + 0) > 0 ? (dim / 32 < 8 ? dim / 32 : 8) : 1));
+    // 256 threads, like a CTA of the matrix-vector kernel: the fused and the standalone norm add in the same order
+    const int norm_threads = dim >= 256 ? 256 : 32 * (dim / 32);
     if (!kv->rope_cos) return flare_set_error(ctx, FLARE_ERR_STATE, "no rotary table: call flare_kv_set_rope_table first");
     for (int b = 0; b < B; b++)
         if (positions[b] < 0 || positions[b] >= kv->rope_len)
@@ -327,39 +280,41 @@ int flare_forward_token(flare_attn_ctx* ctx, flare_model* m, flare_kv* kv, const
     FLARE_CUDA_OK(ctx, cudaMemcpyAsync(m->x, token_embed, (size_t)B * dim * sizeof(float), cudaMemcpyHostToDevice, st));
     FLARE_CUDA_OK(ctx, cudaMemcpyAsync(m->pos, positions, (size_t)B * sizeof(long long), cudaMemcpyHostToDevice, st));
     ctx->last_launch_overlappable = false;
+    // a single sequence needs no copy to take [q | k | v] apart
+    float* q = B == 1 ? m->qkv : m->q;
+    float* k = B == 1 ? m->qkv + q_dim : m->k;
+    float* v = B == 1 ? m->qkv + q_dim + kv_dim : m->v;
     for (int layer = 0; layer < c.num_layers; layer++) {
         const flare_model::Layer& L = m->layers[layer];
         // attention block
-        rmsnorm_quantize_kernel<<<B, norm_threads, 0, st>>>(m->x, L.attn_norm, c.rms_norm_eps, dim, m->xq, m->xs);
+        FLARE_CUDA_OK(ctx, flare_launch_pdl(rmsnorm_quantize_kernel, dim3(B), dim3(norm_threads), 0, st, m->x, L.attn_norm, c.rms_norm_eps, dim, m->xq, m->xs));
         FLARE_LAUNCH_CHECK(ctx);
-        FLARE_TRY(flare_launch_matvec_q8_0_preq(ctx, L.qkv, m->xq, m->xs, B, m->qkv));
-        split_qkv_kernel<<<dim3(grid_for((size_t)q_dim + 2 * kv_dim), B), 256, 0, st>>>(m->qkv, q_dim, kv_dim, m->q, m->k, m->v);
-        FLARE_LAUNCH_CHECK(ctx);
-        FLARE_TRY(flare_launch_rope_rows(kv, m->q, B, c.num_heads, m->pos));
-        FLARE_TRY(flare_kv_write_step_rope_device(kv, layer, m->k, m->v, m->pos));
-        FLARE_TRY(flare_decode_attn(ctx, kv, layer, c.num_heads, m->q, 1, nullptr, 0.0f, m->attn, 1));
+        FLARE_TRY(flare_launch_matvec_q8_0_preq(ctx, L.qkv, m->xq, m->xs, B, m->qkv, 0));
+        if (B > 1) {
+            FLARE_CUDA_OK(ctx, flare_launch_pdl(split_qkv_kernel, dim3(grid_for((size_t)q_dim + 2 * kv_dim), B), dim3(256), 0, st, m->qkv, q_dim, kv_dim, m->q, m->k, m->v));
+            FLARE_LAUNCH_CHECK(ctx);
+        }
+        FLARE_TRY(flare_launch_rope_rows(kv, q, B, c.num_heads, m->pos));
+        FLARE_TRY(flare_kv_write_step_rope_device(kv, layer, k, v, m->pos));
+        FLARE_TRY(flare_decode_attn(ctx, kv, layer, c.num_heads, q, 1, nullptr, 0.0f, m->attn, 1));
         FLARE_TRY(flare_launch_quantize_input(ctx, m->attn, (size_t)B * q_dim / 32, m->xq, m->xs));
-        FLARE_TRY(flare_launch_matvec_q8_0_preq(ctx, L.wo, m->xq, m->xs, B, m->proj));
-        add_rows_kernel<<<grid_for((size_t)B * dim), 256, 0, st>>>(m->x, m->proj, (size_t)B * dim);
-        FLARE_LAUNCH_CHECK(ctx);
+        FLARE_TRY(flare_launch_matvec_q8_0_preq(ctx, L.wo, m->xq, m->xs, B, m->x, 1));
         // feed-forward block
-        rmsnorm_quantize_kernel<<<B, norm_threads, 0, st>>>(m->x, L.ffn_norm, c.rms_norm_eps, dim, m->xq, m->xs);
+        FLARE_CUDA_OK(ctx, flare_launch_pdl(rmsnorm_quantize_kernel, dim3(B), dim3(norm_threads), 0, st, m->x, L.ffn_norm, c.rms_norm_eps, dim, m->xq, m->xs));
         FLARE_LAUNCH_CHECK(ctx);
-        FLARE_TRY(flare_launch_matvec_q8_0_preq(ctx, L.gate_up, m->xq, m->xs, B, m->gate_up));
-        silu_mul_quantize_kernel<<<grid_for((size_t)B * inter), 256, 0, st>>>(m->gate_up, inter, (size_t)B * inter / 32, m->xq, m->xs);
+        FLARE_TRY(flare_launch_matvec_q8_0_preq(ctx, L.gate_up, m->xq, m->xs, B, m->gate_up, 0));
+        FLARE_CUDA_OK(ctx, flare_launch_pdl(silu_mul_quantize_kernel, dim3(grid_for((size_t)B * inter)), dim3(256), 0, st, m->gate_up, inter, (size_t)B * inter / 32, m->xq, m->xs));
         FLARE_LAUNCH_CHECK(ctx);
-        FLARE_TRY(flare_launch_matvec_q8_0_preq(ctx, L.down, m->xq, m->xs, B, m->proj));
-        add_rows_kernel<<<grid_for((size_t)B * dim), 256, 0, st>>>(m->x, m->proj, (size_t)B * dim);
-        FLARE_LAUNCH_CHECK(ctx);
+        FLARE_TRY(flare_launch_matvec_q8_0_preq(ctx, L.down, m->xq, m->xs, B, m->x, 1));
         ctx->last_launch_overlappable = false;
     }
-    rmsnorm_kernel<<<B, norm_threads, 0, st>>>(m->x, m->output_norm, c.rms_norm_eps, dim, m->normed);
+    FLARE_CUDA_OK(ctx, flare_launch_pdl(rmsnorm_kernel, dim3(B), dim3(norm_threads), 0, st, m->x, m->output_norm, c.rms_norm_eps, dim, m->normed));
     FLARE_LAUNCH_CHECK(ctx);
     if (m->output_q8) {
         FLARE_TRY(flare_launch_quantize_input(ctx, m->normed, (size_t)B * dim / 32, m->xq, m->xs));
-        FLARE_TRY(flare_launch_matvec_q8_0_preq(ctx, m->output_q8, m->xq, m->xs, B, m->logits));
+        FLARE_TRY(flare_launch_matvec_q8_0_preq(ctx, m->output_q8, m->xq, m->xs, B, m->logits, 0));
     } else {
-        matvec_f32_kernel<<<(c.vocab_size + 7) / 8, 256, 0, st>>>(m->output_f32, m->normed, c.vocab_size, dim, B, m->logits);
+        FLARE_CUDA_OK(ctx, flare_launch_pdl(matvec_f32_kernel, dim3((c.vocab_size + 7) / 8), dim3(256), 0, st, m->output_f32, m->normed, c.vocab_size, dim, B, m->logits));
         FLARE_LAUNCH_CHECK(ctx);
     }
     FLARE_CUDA_OK(ctx, cudaMemcpyAsync(logits, m->logits, (size_t)B * c.vocab_size * sizeof(float), cudaMemcpyDeviceToHost, st));

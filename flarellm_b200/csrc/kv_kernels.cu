@@ -77,6 +77,8 @@ __device__ __forceinline__ float rope_channel(const float* __restrict__ row, int
 }
 // In-place rotation of [n_rows][num_heads][head_dim] (used for q, and for the key rows of the 2-bit caches).
 __global__ void rope_rows_kernel(float* __restrict__ rows, int n_rows, int num_heads, RopeArgs r) {
+    flare_pdl_wait();
+    flare_pdl_trigger();
     const int half = r.head_dim >> 1;
     const size_t total = (size_t)n_rows * num_heads * half;
     for (size_t t = blockIdx.x * (size_t)blockDim.x + threadIdx.x; t < total; t += (size_t)gridDim.x * blockDim.x) {
@@ -454,7 +456,8 @@ int flare_launch_rope_rows(flare_kv* kv, float* d_rows, int n_rows, int num_head
     flare_attn_ctx* ctx = kv->ctx;
     if (n_rows <= 0) return FLARE_OK;
     RopeArgs r = {kv->rope_cos, kv->rope_sin, d_positions, kv->head_dim};
-    rope_rows_kernel<<<grid_for((size_t)n_rows * num_heads * (kv->head_dim / 2), 256), 256, 0, ctx->stream>>>(d_rows, n_rows, num_heads, r);
+    FLARE_CUDA_OK(ctx, flare_launch_pdl(rope_rows_kernel, dim3(grid_for((size_t)n_rows * num_heads * (kv->head_dim / 2), 256)), dim3(256), 0,
+                                        ctx->stream, d_rows, n_rows, num_heads, r));
     FLARE_LAUNCH_CHECK(ctx);
     return FLARE_OK;
 }
