@@ -9,6 +9,7 @@
 // loads; the 32/TPS lane groups of the 4 warps take interleaved slots and hold independent
 // softmax states that are combined once at the end (shuffles, then shared memory).
 #include "common.cuh"
+#include <algorithm>
 #include <math_constants.h>
 #include <mutex>
 
@@ -139,6 +140,8 @@ template <bool IS_V> struct Row<FLARE_KV_KIVI_G32, IS_V> {
     }
 };
 
+constexpr long long kMaxGridZ = 65535;
+
 struct DecodeParams {
     KvLayerView kv;
     const float* q;
@@ -147,6 +150,7 @@ struct DecodeParams {
     const int* attend_len;
     const int2* ring;
     int n_q, num_heads, n_chunks, slot_begin, slot_end, want_partial, range_max, causal_q, window;
+    int bq0;           // (sequence, query) index of blockIdx.z == 0: more than 65535 of them take several launches
 };
 
 __device__ __forceinline__ SeqKv seq_view(const DecodeParams& p, int b, int n_q) {
@@ -168,7 +172,8 @@ __global__ void __launch_bounds__(128) decode_splitkv_kernel(DecodeParams p) {
     constexpr int SPW = 32 / TPS;           // slots per warp per iteration
     const int split = blockIdx.x, n_split = gridDim.x;
     const int kvh = blockIdx.y / p.n_chunks, chunk = blockIdx.y % p.n_chunks;
-    const int b = blockIdx.z / p.n_q, qi = blockIdx.z % p.n_q;
+    const int bq = p.bq0 + (int)blockIdx.z;
+    const int b = bq / p.n_q, qi = bq % p.n_q;
     const int G = p.num_heads / p.kv.num_kv_heads;
     const int h0 = kvh * G + chunk * GC;
     const int heads_here = min(GC, G - chunk * GC);
@@ -306,7 +311,8 @@ __global__ void __launch_bounds__(128) decode_splitkv_kernel(DecodeParams p) {
 // flare-core/src/model.rs:10427-10435) run on the device as well.
 __global__ void decode_f32_anyshape_kernel(DecodeParams p) {
     const int hd = p.kv.head_dim;
-    const int h = blockIdx.x, b = blockIdx.z / p.n_q, qi = blockIdx.z % p.n_q;
+    const int bq = p.bq0 + (int)blockIdx.z;
+    const int h = blockIdx.x, b = bq / p.n_q, qi = bq % p.n_q;
     const int lane = threadIdx.x;
     const int kvh = h / (p.num_heads / p.kv.num_kv_heads);
     int n = p.attend_len[b] - (p.causal_q ? (p.n_q - 1 - qi) : 0);
@@ -446,9 +452,12 @@ int flare_launch_decode_generic(flare_attn_ctx* ctx, const DecodeArgs& a) {
         if (a.kv.dtype != FLARE_KV_F32 || hd > 256)
             return flare_set_error(ctx, FLARE_ERR_UNSUPPORTED, "head_dim %d is not supported for this cache format", hd);
         p.n_chunks = 1;
-        dim3 grid(a.num_heads, 1, a.batch * a.n_q);
-        decode_f32_anyshape_kernel<<<grid, 32, 0, ctx->stream>>>(p);
-        FLARE_LAUNCH_CHECK(ctx);
+        for (long long z0 = 0; z0 < (long long)a.batch * a.n_q; z0 += kMaxGridZ) {
+            p.bq0 = (int)z0;
+            dim3 grid(a.num_heads, 1, (unsigned)std::min<long long>(kMaxGridZ, (long long)a.batch * a.n_q - z0));
+            decode_f32_anyshape_kernel<<<grid, 32, 0, ctx->stream>>>(p);
+            FLARE_LAUNCH_CHECK(ctx);
+        }
         return FLARE_OK;
     }
     const int gc = G >= 4 ? 4 : G;
@@ -465,18 +474,23 @@ int flare_launch_decode_generic(flare_attn_ctx* ctx, const DecodeArgs& a) {
         FLARE_TRY(flare_ensure(ctx, &ctx->d_work, &ctx->work_bytes, need));
         p.work = (float*)ctx->d_work;
     }
-    dim3 grid(n_split, nkv * p.n_chunks, a.batch * a.n_q);
-    bool ok = false;
-    switch (a.kv.dtype) {
-        case FLARE_KV_F32:
-            ok = launch_tps<FLARE_KV_F32>(hd, gc, grid, ctx->stream, p) || launch_f32_small(hd, gc, grid, ctx->stream, p);
-            break;
-        case FLARE_KV_Q8_0: ok = launch_tps<FLARE_KV_Q8_0>(hd, gc, grid, ctx->stream, p); break;
-        case FLARE_KV_KIVI_REF: ok = launch_tps<FLARE_KV_KIVI_REF>(hd, gc, grid, ctx->stream, p); break;
-        case FLARE_KV_KIVI_G32: ok = launch_tps<FLARE_KV_KIVI_G32>(hd, gc, grid, ctx->stream, p); break;
+    // grid.z = (sequence, query) pairs, at most 65535 per launch: a long prompt through the general prefill path
+    // (every row a query) takes several launches
+    for (long long z0 = 0; z0 < (long long)a.batch * a.n_q; z0 += kMaxGridZ) {
+        p.bq0 = (int)z0;
+        dim3 grid(n_split, nkv * p.n_chunks, (unsigned)std::min<long long>(kMaxGridZ, (long long)a.batch * a.n_q - z0));
+        bool ok = false;
+        switch (a.kv.dtype) {
+            case FLARE_KV_F32:
+                ok = launch_tps<FLARE_KV_F32>(hd, gc, grid, ctx->stream, p) || launch_f32_small(hd, gc, grid, ctx->stream, p);
+                break;
+            case FLARE_KV_Q8_0: ok = launch_tps<FLARE_KV_Q8_0>(hd, gc, grid, ctx->stream, p); break;
+            case FLARE_KV_KIVI_REF: ok = launch_tps<FLARE_KV_KIVI_REF>(hd, gc, grid, ctx->stream, p); break;
+            case FLARE_KV_KIVI_G32: ok = launch_tps<FLARE_KV_KIVI_G32>(hd, gc, grid, ctx->stream, p); break;
+        }
+        if (!ok) return flare_set_error(ctx, FLARE_ERR_UNSUPPORTED, "no decode kernel for dtype %d head_dim %d", a.kv.dtype, hd);
+        FLARE_LAUNCH_CHECK(ctx);
     }
-    if (!ok) return flare_set_error(ctx, FLARE_ERR_UNSUPPORTED, "no decode kernel for dtype %d head_dim %d", a.kv.dtype, hd);
-    FLARE_LAUNCH_CHECK(ctx);
     if (a.defer_merge && a.want_partial) {          // the caller merges: tell it where the records are
         *a.work_out = p.work; *a.n_split_out = n_split;
         return FLARE_OK;
@@ -595,6 +609,7 @@ int flare_decode_noalloc(flare_attn_ctx* ctx, const flare_kv* kv, int layer, int
     // its own copy of `small` by the time each of these calls returns.
     FLARE_CUDA_OK(ctx, cudaMemcpyAsync(scratch, small.ring, sizeof(int2) * B, cudaMemcpyHostToDevice, ctx->stream));
     FLARE_CUDA_OK(ctx, cudaMemcpyAsync(d_att, small.att, sizeof(int) * B, cudaMemcpyHostToDevice, ctx->stream));
+    p.bq0 = 0;
     dim3 grid(n_split, nkv * p.n_chunks, B * n_q);
     bool ok = kv->dtype == FLARE_KV_F32 ? launch_tps<FLARE_KV_F32>(hd, gc, grid, ctx->stream, p)
                                         : launch_tps<FLARE_KV_Q8_0>(hd, gc, grid, ctx->stream, p);

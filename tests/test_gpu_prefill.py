@@ -57,6 +57,19 @@ def test_generic_window(eng, fb, orc):
     check(orc, got, q, k, v, S, nh, nkv, hd, window=W, what="generic window")
 
 
+def test_generic_path_with_more_rows_than_one_launch_holds(eng, fb, orc):
+    """head_dim 32 takes the general path, where every prompt row is one grid.z entry: 8 x 8200 = 65600 rows are more
+    than the 65535 a launch can hold, so the rows go out in two launches."""
+    B, S, nh, nkv, hd, W = 8, 8200, 2, 1, 32, 64
+    q, k, v = normal(61, (B, S, nh * hd)), normal(62, (B, S, nkv * hd)), normal(63, (B, S, nkv * hd))
+    got = eng.prefill(q, k, v, B, S, nh, nkv, hd, window=W).reshape(B, S, nh * hd)
+    for b in (0, B - 1):             # the last rows of the last sequence are the ones past the first launch
+        want = orc.prefill(q[b], k[b], v[b], S, nh, nkv, hd, window=W, row_start=S - 1 - 7 * 1000, row_step=1000)
+        rows = ~np.isnan(want[:, 0])
+        assert rows.sum() == 8
+        assert_close(got[b][rows], want[rows], f"general path, 65600 rows, seq {b}")
+
+
 @pytest.mark.parametrize("B,S,nh,nkv,hd", [(1, 128, 2, 1, 128), (2, 300, 4, 2, 128), (1, 257, 4, 4, 64), (1, 640, 8, 2, 128)])
 def test_tensor_core_causal(eng, fb, orc, B, S, nh, nkv, hd):
     q, k, v = bf16_inputs(orc, 10 + S, B, S, nh, nkv, hd)
