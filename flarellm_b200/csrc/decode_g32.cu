@@ -307,10 +307,10 @@ __global__ void __launch_bounds__(256, 2) decode_g32_kernel(const __grid_constan
             const int s_n = ring.x, w0 = (s_n - (FLARE_G32_RESIDUAL - 1) + p.max_seq) % p.max_seq;
             ca0 = (w0 / T) * T; ca1 = w0; cb0 = s_n + 1; cb1 = (s_n / T + 1) * T; rr0 = w0; rr1 = w0 + FLARE_G32_RESIDUAL;
         }
+        pdl_trigger();
         pdl_wait();
         NewestScratch* ws = reinterpret_cast<NewestScratch*>(sbase) + warp;
         g32_newest_tokens(p, b, kvh, lane, ca0, ca1, cb0, cb1, rr0, rr1, ws);
-        pdl_trigger();
         for (int h = 0; h < p.G; h++) {
             const size_t row = (size_t)b * p.num_heads + kvh * p.G + h;
             float* wrec = p.work + (row * (p.n_split + 1) + split) * (HD + 2);
@@ -342,6 +342,7 @@ __global__ void __launch_bounds__(256, 2) decode_g32_kernel(const __grid_constan
         for (int i = 0; i < STAGES && i < n_tiles; i++) issue(i);
     }
     __syncthreads();
+    pdl_trigger();          // the next kernel may be scheduled: its CTAs take the places this grid's CTAs leave
     pdl_wait();
 
     // ---- the q side (B operand, column g): head g >> 1, hi part in even columns, lo part in odd ones.
@@ -510,7 +511,6 @@ __global__ void __launch_bounds__(256, 2) decode_g32_kernel(const __grid_constan
             }
         }
     }
-    pdl_trigger();
     if (failed) {
         if (lane == 0) flare_report(p.err, FLARE_ERR_TIMEOUT);
         return;
