@@ -37,6 +37,33 @@ __device__ __forceinline__ void flare_quantize_block_of_32(float n, int lane, in
 __device__ __forceinline__ void flare_quantize_vector(const float* __restrict__ x, const float* __restrict__ norm_weight,
                                                       float eps, int dim, int8_t* q_out, float* s_out, float* s_red) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5, nb = dim / 32;
+    if (nb <= 8 * nw) {
+        // the whole vector fits in registers: read once, all loads in flight together
+        float xv[8], wv[8];
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+            const int blk = warp + k * nw;
+            xv[k] = blk < nb ? x[blk * 32 + lane] : 0.0f;
+            wv[k] = (norm_weight && blk < nb) ? norm_weight[blk * 32 + lane] : 1.0f;
+        }
+        float inv_rms = 1.0f;
+        if (norm_weight) {
+            float s = 0.0f;
+#pragma unroll
+            for (int k = 0; k < 8; k++) s = fmaf(xv[k], xv[k], s);
+            const float sum_sq = flare_block_sum(s, s_red);
+            inv_rms = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sum_sq, (float)dim), eps)));
+        }
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+            const int blk = warp + k * nw;
+            if (blk < nb) {
+                const float n = norm_weight ? __fmul_rn(__fmul_rn(xv[k], wv[k]), inv_rms) : xv[k];
+                flare_quantize_block_of_32(n, lane, q_out + blk * 32, s_out + blk);
+            }
+        }
+        return;
+    }
     float inv_rms = 1.0f;
     if (norm_weight) {
         float s = 0.0f;
