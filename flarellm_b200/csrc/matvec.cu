@@ -13,6 +13,7 @@
 // by side.  A weight row is read from HBM once for the whole batch.
 #include "common.cuh"
 #include "q8_input.cuh"
+#include "tma.cuh"
 #include <mutex>
 
 struct flare_weight {
@@ -61,6 +62,7 @@ struct MatvecParams {
     int rows, cols, batch;
     int bt;                      // input vectors per tile: min(batch, 32); sizes the product buffer
     int accumulate;              // out += product (the residual connection) instead of out = product
+    int* err;                    // status word of the context (a bulk copy that never arrives)
 };
 
 // A warp owns one row at a time.  Per chunk of 64 blocks every lane holds two blocks of the row in registers
@@ -142,6 +144,100 @@ __global__ void __launch_bounds__(32 * WARPS) matvec_q8_0_kernel(MatvecParams p)
                 *o = p.accumulate ? __fadd_rn(*o, sum[t]) : sum[t];
             }
     }
+}
+
+// The same product with the weights staged through shared memory by bulk copies: every warp keeps a ring of
+// RING chunk buffers (64 blocks: 2 KB of weights + 128 B of scales) that lane 0 refills with cp.async.bulk as soon as
+// the warp has taken a chunk into registers, so several chunks per warp are on their way from HBM at any time without
+// costing registers.  Needs rows and chunks on 16-byte boundaries (cols % 256 == 0); used for one or two input vectors.
+constexpr int RING = 4;
+constexpr int RING_CHUNK_BYTES = CHUNK * 32 + CHUNK * 2;        // 2176
+
+__global__ void __launch_bounds__(32 * WARPS) matvec_q8_0_ring_kernel(MatvecParams p) {
+    extern __shared__ __align__(128) unsigned char ring_smem[];
+    __shared__ uint64_t full_bar[WARPS][RING];
+    flare_pdl_wait();
+    flare_pdl_trigger();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nb = p.cols / 32;
+    const int chunks_per_row = (nb + CHUNK - 1) / CHUNK;
+    unsigned char* my_ring = ring_smem + (size_t)warp * RING * RING_CHUNK_BYTES;
+    float* terms = reinterpret_cast<float*>(ring_smem + (size_t)WARPS * RING * RING_CHUNK_BYTES) + (size_t)warp * p.bt * TS;
+    uint64_t* bars = full_bar[warp];
+    // this warp's rows: first_row, first_row + row_step, ...; its units are (row, chunk) pairs in that order
+    const int first_row = blockIdx.x * WARPS + warp, row_step = gridDim.x * WARPS;
+    const int my_rows = first_row < p.rows ? (p.rows - first_row + row_step - 1) / row_step : 0;
+    const long long n_units = (long long)my_rows * chunks_per_row;
+    auto issue = [&](long long u) {                    // lane 0 only
+        const int s = (int)(u % RING);
+        const int row = first_row + (int)(u / chunks_per_row) * row_step, c0 = (int)(u % chunks_per_row) * CHUNK;
+        const int cn = min(CHUNK, nb - c0);
+        unsigned char* dst = my_ring + (size_t)s * RING_CHUNK_BYTES;
+        ptx::mbar_expect_tx(&bars[s], (uint32_t)cn * 34);
+        ptx::bulk_load(dst, p.wq + (size_t)row * p.cols + (size_t)c0 * 32, (uint32_t)cn * 32, &bars[s]);
+        ptx::bulk_load(dst + CHUNK * 32, p.ws + (size_t)row * nb + c0, (uint32_t)cn * 2, &bars[s]);
+    };
+    if (lane == 0) {
+        for (int s = 0; s < RING; s++) ptx::mbar_init(&bars[s], 1);
+        ptx::fence_barrier_init();
+        ptx::fence_proxy_async();
+        for (long long u = 0; u < RING && u < n_units; u++) issue(u);
+    }
+    __syncwarp();
+    float sum = 0.0f;                                  // lane b: running sum of input vector b for the current row
+    bool failed = false;
+    for (long long u = 0; u < n_units; u++) {
+        const int s = (int)(u % RING);
+        const int row = first_row + (int)(u / chunks_per_row) * row_step, chunk = (int)(u % chunks_per_row), c0 = chunk * CHUNK;
+        const int cn = min(CHUNK, nb - c0);
+        if (!ptx::mbar_wait(&bars[s], (uint32_t)((u / RING) & 1))) { failed = true; break; }
+        const unsigned char* buf = my_ring + (size_t)s * RING_CHUNK_BYTES;
+        float wsc[2];
+        int4 w0[2], w1[2];
+#pragma unroll
+        for (int k = 0; k < 2; k++) {
+            const int blk = lane + 32 * k;
+            if (blk < cn) {
+                const int4* wp = reinterpret_cast<const int4*>(buf + blk * 32);
+                w0[k] = wp[0]; w1[k] = wp[1];
+                wsc[k] = __half2float(*reinterpret_cast<const __half*>(buf + CHUNK * 32 + blk * 2));
+            } else {
+                wsc[k] = 0.0f; w0[k] = make_int4(0, 0, 0, 0); w1[k] = make_int4(0, 0, 0, 0);
+            }
+        }
+        __syncwarp();                                  // every lane has its blocks: the buffer may be refilled
+        if (lane == 0 && u + RING < n_units) { ptx::fence_proxy_async(); issue(u + RING); }
+        for (int b = 0; b < p.batch; b++) {
+#pragma unroll
+            for (int k = 0; k < 2; k++) {
+                const int blk = lane + 32 * k;
+                if (blk < cn) {
+                    const int4* xp = reinterpret_cast<const int4*>(p.xq + (size_t)b * p.cols + (size_t)(c0 + blk) * 32);
+                    const int4 x0 = __ldg(xp), x1 = __ldg(xp + 1);
+                    int acc = 0;
+                    acc = __dp4a(w0[k].x, x0.x, acc); acc = __dp4a(w0[k].y, x0.y, acc);
+                    acc = __dp4a(w0[k].z, x0.z, acc); acc = __dp4a(w0[k].w, x0.w, acc);
+                    acc = __dp4a(w1[k].x, x1.x, acc); acc = __dp4a(w1[k].y, x1.y, acc);
+                    acc = __dp4a(w1[k].z, x1.z, acc); acc = __dp4a(w1[k].w, x1.w, acc);
+                    const float cs = __fmul_rn(wsc[k], __ldg(p.xs + (size_t)b * nb + c0 + blk));
+                    terms[b * TS + blk] = __fmul_rn(cs, (float)acc);
+                }
+            }
+        }
+        __syncwarp();
+        if (lane < p.batch) {
+            if (chunk == 0) sum = 0.0f;
+            const float* tp = terms + lane * TS;
+#pragma unroll 8
+            for (int blk = 0; blk < cn; blk++) sum = __fadd_rn(sum, tp[blk]);
+            if (chunk == chunks_per_row - 1) {
+                float* o = p.out + (size_t)lane * p.rows + row;
+                *o = p.accumulate ? __fadd_rn(*o, sum) : sum;
+            }
+        }
+        __syncwarp();                                  // the sums have read the products before the next chunk writes them
+    }
+    if (failed && lane == 0) flare_report(p.err, FLARE_ERR_TIMEOUT);
 }
 
 }  // namespace
@@ -256,11 +352,35 @@ int flare_launch_matvec_q8_0_preq(flare_attn_ctx* ctx, const flare_weight* w, co
             attr_done[ctx->device & 63] = true;
         }
     }
+    p.err = ctx->d_err;
+    ctx->last_launch_overlappable = false;
+    if (w->cols % 256 == 0 && batch <= 2) {
+        // One or two input vectors: the product is bound by memory, and rows and chunks start on 16-byte boundaries, so
+        // the weights go through a ring of bulk copies.  (From 8 input vectors on the dots dominate and the direct-load
+        // kernel with its many more warps is faster: 212 against 289 us for 128256 x 2048 at batch 8.)
+        const int ring_smem = WARPS * RING * RING_CHUNK_BYTES + smem;
+        {
+            static std::mutex m2;
+            std::lock_guard<std::mutex> lock(m2);
+            static bool ring_attr[64] = {};
+            if (!ring_attr[ctx->device & 63]) {
+                FLARE_CUDA_OK(ctx, cudaFuncSetAttribute(matvec_q8_0_ring_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                        WARPS * RING * RING_CHUNK_BYTES + WARPS * 32 * TS * (int)sizeof(float)));
+                ring_attr[ctx->device & 63] = true;
+            }
+        }
+        // enough CTAs to fill the SMs (3 per SM at batch 1); each warp then walks its rows through the ring
+        int grid = (w->rows + WARPS - 1) / WARPS;
+        const int max_grid = 148 * 3;
+        if (grid > max_grid) grid = max_grid;
+        FLARE_CUDA_OK(ctx, flare_launch_pdl(matvec_q8_0_ring_kernel, dim3(grid), dim3(32 * WARPS), (size_t)ring_smem, ctx->stream, p));
+        FLARE_LAUNCH_CHECK(ctx);
+        return FLARE_OK;
+    }
     // a row per warp; many more warps than the SMs hold at once are pointless, so large matrices loop
     int grid = (w->rows + WARPS - 1) / WARPS;
     const int max_grid = 148 * 8 * 4;
     if (grid > max_grid) grid = max_grid;
-    ctx->last_launch_overlappable = false;
     FLARE_CUDA_OK(ctx, flare_launch_pdl(matvec_q8_0_kernel, dim3(grid), dim3(32 * WARPS), (size_t)smem, ctx->stream, p));
     FLARE_LAUNCH_CHECK(ctx);
     return FLARE_OK;

@@ -177,7 +177,8 @@ def test_batched_verify_equals_the_sequential_loop(eng, fb, orc):
         kv_seq.free(); kv_bat.free()
 
 
-@pytest.mark.parametrize("rows,cols,batch", [(2048, 2048, 1), (512, 2048, 32), (96, 4096, 5), (33, 64, 40), (2048, 2048, 32)])
+@pytest.mark.parametrize("rows,cols,batch", [(2048, 2048, 1), (512, 2048, 32), (96, 4096, 5), (33, 64, 40), (2048, 2048, 32),
+                                             (5000, 8192, 2), (37, 256, 1), (64, 96, 2)])
 def test_q8_0_projection_is_bit_exact(eng, fb, orc, rows, cols, batch):
     """The Q / K / V and output projections (flare-core/src/model.rs:2016-2136, 2249-2291): matvec_q8_0_preq_into on
     quantize_input_q8_0, bit for bit — the integer dots are exact and the f32 sum over a row's blocks runs in the
