@@ -524,8 +524,10 @@ int flare_kv_write_step_rope_f32(flare_kv* kv, int layer, const float* key, cons
     return FLARE_OK;
 }
 
-// The same on device buffers with the positions already on the device (one upload per token, not per layer).
-int flare_kv_write_step_rope_device(flare_kv* kv, int layer, const float* d_key, const float* d_value, const long long* d_pos) {
+// The same on device buffers with the positions already on the device (one upload per token, not per layer); the
+// step's query rows [batch][q_heads][head_dim], when given, are rotated in place by the same launch.
+int flare_kv_write_step_rope_device(flare_kv* kv, int layer, const float* d_key, const float* d_value, const long long* d_pos,
+                                    float* d_q_rows, int q_heads) {
     FLARE_TRY(check_layer_seq(kv, layer, 0));
     flare_attn_ctx* ctx = kv->ctx;
     BIND(ctx);
@@ -536,9 +538,10 @@ int flare_kv_write_step_rope_device(flare_kv* kv, int layer, const float* d_key,
         FLARE_TRY(flare_ensure(ctx, &ctx->d_conv, &ctx->conv_bytes, bytes));
         FLARE_CUDA_OK(ctx, cudaMemcpyAsync(ctx->d_conv, d_key, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
         FLARE_TRY(flare_launch_rope_rows(kv, (float*)ctx->d_conv, kv->batch, kv->num_kv_heads, d_pos));
+        if (d_q_rows) FLARE_TRY(flare_launch_rope_rows(kv, d_q_rows, kv->batch, q_heads, d_pos));
         return flare_launch_kv_write_step(kv, layer, d_ring, (const float*)ctx->d_conv, d_value);
     }
-    return flare_launch_kv_write_step(kv, layer, d_ring, d_key, d_value, d_pos);
+    return flare_launch_kv_write_step(kv, layer, d_ring, d_key, d_value, d_pos, d_q_rows, q_heads);
 }
 
 int flare_rope_rows_f32(flare_kv* kv, float* rows, int n_rows, int num_heads, const int64_t* positions, int on_device) {

@@ -198,9 +198,10 @@ int flare_launch_kv_write(flare_kv* kv, int layer, int seq, int64_t first_abs_po
 // d_positions (with the cache's rotary table): the key rows are rotated for these absolute positions on their way
 // into the cache; null = stored as given
 int flare_launch_kv_write_step(flare_kv* kv, int layer, const int2* d_ring, const float* d_key, const float* d_value,
-                               const long long* d_positions = nullptr);
+                               const long long* d_positions = nullptr, float* d_q_rows = nullptr, int q_heads = 0);
 int flare_launch_rope_rows(flare_kv* kv, float* d_rows, int n_rows, int num_heads, const long long* d_positions);
-extern "C" int flare_kv_write_step_rope_device(flare_kv* kv, int layer, const float* d_key, const float* d_value, const long long* d_pos);
+extern "C" int flare_kv_write_step_rope_device(flare_kv* kv, int layer, const float* d_key, const float* d_value, const long long* d_pos,
+                                               float* d_q_rows, int q_heads);
 // Programmatic dependent launch for chains of small kernels (the forward pass): a kernel launched with
 // flare_launch_pdl may be scheduled while its predecessor in the stream still runs; it begins with
 // flare_pdl_wait(), which returns once the predecessor has completed and its writes are visible, and then lets its

@@ -73,6 +73,7 @@ struct Q8Params {
     int whole_rows;             // 1: the maps deliver all heads of a tile in one copy; 0: one copy per head
     int prefetch_q;             // ask L2 for q's lines before waiting for the previous kernel
     int early_trigger;          // let the next kernel be scheduled as soon as this CTA has requested its first tiles
+    int wait_first;             // the previous kernel may write the cache (a step write): wait for it before the first tile request
     int* err;
 };
 
@@ -202,6 +203,10 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
             }
         }
     };
+    // Launched as a programmatic dependent in every case: after one of this path's own kernels the first tiles are
+    // requested while that kernel drains; after anything else (a step write into the cache, above all) only the launch
+    // latency is hidden and the kernel waits here before it touches the cache.
+    if (p.wait_first) pdl_wait();
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) { ptx::mbar_init(&full_bar[s], 1); done_cnt[s] = 0; }
         ptx::fence_barrier_init();
@@ -677,8 +682,9 @@ int flare_launch_decode_q8(flare_attn_ctx* ctx, const DecodeArgs& a) {
     cfg.dynamicSmemBytes = smem;
     cfg.stream = ctx->stream;
     // the attributes in use are a contiguous run of attr[]: [PDL][cluster]
-    cfg.attrs = ctx->last_launch_overlappable ? attr : attr + 1;
-    cfg.numAttrs = (ctx->last_launch_overlappable ? 1 : 0) + (cluster ? 1 : 0);
+    p.wait_first = ctx->last_launch_overlappable ? 0 : 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1 + (cluster ? 1 : 0);
     if (hd == 64) FLARE_CUDA_OK(ctx, cudaLaunchKernelEx(&cfg, decode_q8_kernel<64>, *a.kmap, *a.vmap, p));
     else FLARE_CUDA_OK(ctx, cudaLaunchKernelEx(&cfg, decode_q8_kernel<128>, *a.kmap, *a.vmap, p));
     FLARE_LAUNCH_CHECK(ctx);

@@ -294,8 +294,7 @@ int flare_forward_token(flare_attn_ctx* ctx, flare_model* m, flare_kv* kv, const
             FLARE_CUDA_OK(ctx, flare_launch_pdl(split_qkv_kernel, dim3(grid_for((size_t)q_dim + 2 * kv_dim), B), dim3(256), 0, st, m->qkv, q_dim, kv_dim, m->q, m->k, m->v));
             FLARE_LAUNCH_CHECK(ctx);
         }
-        FLARE_TRY(flare_launch_rope_rows(kv, q, B, c.num_heads, m->pos));
-        FLARE_TRY(flare_kv_write_step_rope_device(kv, layer, k, v, m->pos));
+        FLARE_TRY(flare_kv_write_step_rope_device(kv, layer, k, v, m->pos, q, c.num_heads));     // rotates q as well
         FLARE_TRY(flare_decode_attn(ctx, kv, layer, c.num_heads, q, 1, nullptr, 0.0f, m->attn, 1));
         FLARE_TRY(flare_launch_quantize_input(ctx, m->attn, (size_t)B * q_dim / 32, m->xq, m->xs));
         FLARE_TRY(flare_launch_matvec_q8_0_preq(ctx, L.wo, m->xq, m->xs, B, m->x, 1));

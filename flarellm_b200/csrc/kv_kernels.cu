@@ -65,6 +65,8 @@ struct RopeArgs {
     const float* sin;
     const long long* positions;  // per row: absolute token position = row of the table
     int head_dim;
+    float* q_rows;               // optional: [batch][q_heads][head_dim] query rows rotated in place by the same launch
+    int q_heads;
 };
 // Channel c of the rotated key row `row` (kv_dim values) of a token at table row `pos`.
 __device__ __forceinline__ float rope_channel(const float* __restrict__ row, int c, const RopeArgs& r, long long pos) {
@@ -76,9 +78,7 @@ __device__ __forceinline__ float rope_channel(const float* __restrict__ row, int
     return __fadd_rn(__fmul_rn(row[head0 + i], sr[i]), __fmul_rn(row[head0 + e], cr[i]));
 }
 // In-place rotation of [n_rows][num_heads][head_dim] (used for q, and for the key rows of the 2-bit caches).
-__global__ void rope_rows_kernel(float* __restrict__ rows, int n_rows, int num_heads, RopeArgs r) {
-    flare_pdl_wait();
-    flare_pdl_trigger();
+__device__ __forceinline__ void rope_rows_in_place(float* __restrict__ rows, int n_rows, int num_heads, const RopeArgs& r) {
     const int half = r.head_dim >> 1;
     const size_t total = (size_t)n_rows * num_heads * half;
     for (size_t t = blockIdx.x * (size_t)blockDim.x + threadIdx.x; t < total; t += (size_t)gridDim.x * blockDim.x) {
@@ -93,11 +93,18 @@ __global__ void rope_rows_kernel(float* __restrict__ rows, int n_rows, int num_h
         x[i + half] = __fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c));
     }
 }
+__global__ void rope_rows_kernel(float* __restrict__ rows, int n_rows, int num_heads, RopeArgs r) {
+    flare_pdl_wait();
+    flare_pdl_trigger();
+    rope_rows_in_place(rows, n_rows, num_heads, r);
+}
 
 // One new token per sequence (a decode step of the whole batch): row b -> ring slot position[b].
 __global__ void write_step_f32_kernel(float* __restrict__ K, float* __restrict__ V, size_t seq_stride_floats,
                                       const float* __restrict__ key, const float* __restrict__ value,
                                       const int2* __restrict__ ring, int batch, int kv_dim, RopeArgs rope) {
+    flare_pdl_wait();
+    flare_pdl_trigger();
     size_t total = (size_t)batch * kv_dim;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         int b = (int)(i / kv_dim), c = (int)(i % kv_dim);
@@ -105,11 +112,14 @@ __global__ void write_step_f32_kernel(float* __restrict__ K, float* __restrict__
         K[dst] = rope.cos ? rope_channel(key + (size_t)b * kv_dim, c, rope, rope.positions[b]) : key[i];
         V[dst] = value[i];
     }
+    if (rope.cos && rope.q_rows) rope_rows_in_place(rope.q_rows, batch, rope.q_heads, rope);
 }
 __global__ void write_step_q8_kernel(int8_t* __restrict__ Kq, __half* __restrict__ Ks, int8_t* __restrict__ Vq,
                                      __half* __restrict__ Vs, size_t q_stride, size_t s_stride,
                                      const float* __restrict__ key, const float* __restrict__ value,
                                      const int2* __restrict__ ring, int batch, int kv_dim, RopeArgs rope) {
+    flare_pdl_wait();
+    flare_pdl_trigger();
     const int lane = threadIdx.x & 31;
     const int bpr = kv_dim / 32;
     const size_t n_blocks = (size_t)batch * bpr * 2;
@@ -131,6 +141,7 @@ __global__ void write_step_q8_kernel(int8_t* __restrict__ Kq, __half* __restrict
         (is_v ? Vq : Kq)[(size_t)b * q_stride + (size_t)slot * kv_dim + blk * 32 + lane] = (int8_t)qi;
         if (lane == 0) (is_v ? Vs : Ks)[(size_t)b * s_stride + (size_t)slot * bpr + blk] = __float2half_rn(d);
     }
+    if (rope.cos && rope.q_rows) rope_rows_in_place(rope.q_rows, batch, rope.q_heads, rope);
 }
 
 // ------------------------------------------------------------------ 2-bit group quantiser
@@ -455,7 +466,7 @@ int flare_launch_kv_write(flare_kv* kv, int layer, int seq, int64_t first_pos, i
 int flare_launch_rope_rows(flare_kv* kv, float* d_rows, int n_rows, int num_heads, const long long* d_positions) {
     flare_attn_ctx* ctx = kv->ctx;
     if (n_rows <= 0) return FLARE_OK;
-    RopeArgs r = {kv->rope_cos, kv->rope_sin, d_positions, kv->head_dim};
+    RopeArgs r = {kv->rope_cos, kv->rope_sin, d_positions, kv->head_dim, nullptr, 0};
     FLARE_CUDA_OK(ctx, flare_launch_pdl(rope_rows_kernel, dim3(grid_for((size_t)n_rows * num_heads * (kv->head_dim / 2), 256)), dim3(256), 0,
                                         ctx->stream, d_rows, n_rows, num_heads, r));
     FLARE_LAUNCH_CHECK(ctx);
@@ -463,22 +474,25 @@ int flare_launch_rope_rows(flare_kv* kv, float* d_rows, int n_rows, int num_head
 }
 
 int flare_launch_kv_write_step(flare_kv* kv, int layer, const int2* d_ring, const float* d_key, const float* d_value,
-                               const long long* d_positions) {
+                               const long long* d_positions, float* d_q_rows, int q_heads) {
     flare_attn_ctx* ctx = kv->ctx;
     const int kvd = kv->kv_dim, B = kv->batch;
-    RopeArgs rope = {d_positions ? kv->rope_cos : nullptr, kv->rope_sin, d_positions, kv->head_dim};
+    // f32 and Q8_0 caches: the same launch rotates the step's query rows in place when they are given
+    RopeArgs rope = {d_positions ? kv->rope_cos : nullptr, kv->rope_sin, d_positions, kv->head_dim,
+                     (kv->dtype == FLARE_KV_F32 || kv->dtype == FLARE_KV_Q8_0) ? d_q_rows : nullptr, q_heads};
     switch (kv->dtype) {
         case FLARE_KV_F32:
-            write_step_f32_kernel<<<grid_for((size_t)B * kvd, 256), 256, 0, ctx->stream>>>(
-                (float*)kv->plane_ptr(FLARE_PLANE_K, layer, 0), (float*)kv->plane_ptr(FLARE_PLANE_V, layer, 0),
-                kv->plane_bytes[FLARE_PLANE_K] / 4, d_key, d_value, d_ring, B, kvd, rope);
+            FLARE_CUDA_OK(ctx, flare_launch_pdl(write_step_f32_kernel, dim3(grid_for((size_t)B * kvd, 256)), dim3(256), 0, ctx->stream,
+                                                (float*)kv->plane_ptr(FLARE_PLANE_K, layer, 0), (float*)kv->plane_ptr(FLARE_PLANE_V, layer, 0),
+                                                kv->plane_bytes[FLARE_PLANE_K] / 4, d_key, d_value, d_ring, B, kvd, rope));
             FLARE_LAUNCH_CHECK(ctx);
             return FLARE_OK;
         case FLARE_KV_Q8_0:
-            write_step_q8_kernel<<<grid_for((size_t)B * kvd * 2, 256), 256, 0, ctx->stream>>>(
-                (int8_t*)kv->plane_ptr(FLARE_PLANE_K_Q, layer, 0), (__half*)kv->plane_ptr(FLARE_PLANE_K_SCALE, layer, 0),
-                (int8_t*)kv->plane_ptr(FLARE_PLANE_V_Q, layer, 0), (__half*)kv->plane_ptr(FLARE_PLANE_V_SCALE, layer, 0),
-                kv->plane_bytes[FLARE_PLANE_K_Q], kv->plane_bytes[FLARE_PLANE_K_SCALE] / 2, d_key, d_value, d_ring, B, kvd, rope);
+            FLARE_CUDA_OK(ctx, flare_launch_pdl(write_step_q8_kernel, dim3(grid_for((size_t)B * kvd * 2, 256)), dim3(256), 0, ctx->stream,
+                                                (int8_t*)kv->plane_ptr(FLARE_PLANE_K_Q, layer, 0), (__half*)kv->plane_ptr(FLARE_PLANE_K_SCALE, layer, 0),
+                                                (int8_t*)kv->plane_ptr(FLARE_PLANE_V_Q, layer, 0), (__half*)kv->plane_ptr(FLARE_PLANE_V_SCALE, layer, 0),
+                                                kv->plane_bytes[FLARE_PLANE_K_Q], kv->plane_bytes[FLARE_PLANE_K_SCALE] / 2, d_key, d_value,
+                                                d_ring, B, kvd, rope));
             FLARE_LAUNCH_CHECK(ctx);
             return FLARE_OK;
         default:
