@@ -685,6 +685,9 @@ int flare_launch_decode_q8(flare_attn_ctx* ctx, const DecodeArgs& a) {
     p.wait_first = ctx->last_launch_overlappable ? 0 : 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1 + (cluster ? 1 : 0);
+#ifdef FLARE_TUNE
+    if (const char* e = getenv("FLARE_Q8_ALWAYS_PDL")) if (!atoi(e) && !ctx->last_launch_overlappable) { cfg.attrs = attr + 1; cfg.numAttrs = cluster ? 1 : 0; }
+#endif
     if (hd == 64) FLARE_CUDA_OK(ctx, cudaLaunchKernelEx(&cfg, decode_q8_kernel<64>, *a.kmap, *a.vmap, p));
     else FLARE_CUDA_OK(ctx, cudaLaunchKernelEx(&cfg, decode_q8_kernel<128>, *a.kmap, *a.vmap, p));
     FLARE_LAUNCH_CHECK(ctx);

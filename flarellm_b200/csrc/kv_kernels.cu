@@ -488,6 +488,16 @@ int flare_launch_kv_write_step(flare_kv* kv, int layer, const int2* d_ring, cons
             FLARE_LAUNCH_CHECK(ctx);
             return FLARE_OK;
         case FLARE_KV_Q8_0:
+#ifdef FLARE_TUNE
+            if (const char* e = getenv("FLARE_STEP_PDL")) if (!atoi(e)) {
+                write_step_q8_kernel<<<grid_for((size_t)B * kvd * 2, 256), 256, 0, ctx->stream>>>(
+                    (int8_t*)kv->plane_ptr(FLARE_PLANE_K_Q, layer, 0), (__half*)kv->plane_ptr(FLARE_PLANE_K_SCALE, layer, 0),
+                    (int8_t*)kv->plane_ptr(FLARE_PLANE_V_Q, layer, 0), (__half*)kv->plane_ptr(FLARE_PLANE_V_SCALE, layer, 0),
+                    kv->plane_bytes[FLARE_PLANE_K_Q], kv->plane_bytes[FLARE_PLANE_K_SCALE] / 2, d_key, d_value, d_ring, B, kvd, rope);
+                FLARE_LAUNCH_CHECK(ctx);
+                return FLARE_OK;
+            }
+#endif
             FLARE_CUDA_OK(ctx, flare_launch_pdl(write_step_q8_kernel, dim3(grid_for((size_t)B * kvd * 2, 256)), dim3(256), 0, ctx->stream,
                                                 (int8_t*)kv->plane_ptr(FLARE_PLANE_K_Q, layer, 0), (__half*)kv->plane_ptr(FLARE_PLANE_K_SCALE, layer, 0),
                                                 (int8_t*)kv->plane_ptr(FLARE_PLANE_V_Q, layer, 0), (__half*)kv->plane_ptr(FLARE_PLANE_V_SCALE, layer, 0),
