@@ -240,6 +240,95 @@ __global__ void __launch_bounds__(32 * WARPS) matvec_q8_0_ring_kernel(MatvecPara
     if (failed && lane == 0) flare_report(p.err, FLARE_ERR_TIMEOUT);
 }
 
+// One input vector, rows of at most 64 blocks (cols <= 2048: the projections that read the hidden state): the case a
+// single-token forward pass spends most of its bytes on.  Two things change against the kernel above.  The input's
+// blocks of a lane are the same for every row, so they stay in registers for the whole kernel; and the ordered sum of
+// a row, which one lane has to do alone, is done for GROUP rows at a time, a lane per row, so that its 64 dependent
+// adds cost 8 instruction slots per row instead of 128.
+constexpr int GROUP = 16;
+
+__global__ void __launch_bounds__(32 * WARPS) matvec_q8_0_ring1_kernel(MatvecParams p) {
+    extern __shared__ __align__(128) unsigned char ring_smem[];
+    __shared__ uint64_t full_bar[WARPS][RING];
+    flare_pdl_wait();
+    flare_pdl_trigger();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nb = p.cols / 32;                       // <= 64: one chunk per row
+    unsigned char* my_ring = ring_smem + (size_t)warp * RING * RING_CHUNK_BYTES;
+    float* terms = reinterpret_cast<float*>(ring_smem + (size_t)WARPS * RING * RING_CHUNK_BYTES) + (size_t)warp * GROUP * TS;
+    uint64_t* bars = full_bar[warp];
+    const int first_row = blockIdx.x * WARPS + warp, row_step = gridDim.x * WARPS;
+    const int my_rows = first_row < p.rows ? (p.rows - first_row + row_step - 1) / row_step : 0;
+    auto issue = [&](int k) {                          // lane 0 only: row number k of this warp -> stage k % RING
+        const int s = k % RING;
+        const int row = first_row + k * row_step;
+        unsigned char* dst = my_ring + (size_t)s * RING_CHUNK_BYTES;
+        ptx::mbar_expect_tx(&bars[s], (uint32_t)nb * 34);
+        ptx::bulk_load(dst, p.wq + (size_t)row * p.cols, (uint32_t)nb * 32, &bars[s]);
+        ptx::bulk_load(dst + CHUNK * 32, p.ws + (size_t)row * nb, (uint32_t)nb * 2, &bars[s]);
+    };
+    if (lane == 0) {
+        for (int s = 0; s < RING; s++) ptx::mbar_init(&bars[s], 1);
+        ptx::fence_barrier_init();
+        ptx::fence_proxy_async();
+        for (int k = 0; k < RING && k < my_rows; k++) issue(k);
+    }
+    // the input's blocks of this lane
+    int4 x0[2], x1[2];
+    float xsc[2];
+#pragma unroll
+    for (int k = 0; k < 2; k++) {
+        const int blk = lane + 32 * k;
+        if (blk < nb) {
+            const int4* xp = reinterpret_cast<const int4*>(p.xq + (size_t)blk * 32);
+            x0[k] = __ldg(xp); x1[k] = __ldg(xp + 1);
+            xsc[k] = __ldg(p.xs + blk);
+        } else {
+            x0[k] = make_int4(0, 0, 0, 0); x1[k] = make_int4(0, 0, 0, 0); xsc[k] = 0.0f;
+        }
+    }
+    __syncwarp();
+    bool failed = false;
+    for (int k = 0; k < my_rows; k++) {
+        const int s = k % RING, slot = k % GROUP;
+        if (!ptx::mbar_wait(&bars[s], (uint32_t)((k / RING) & 1))) { failed = true; break; }
+        const unsigned char* buf = my_ring + (size_t)s * RING_CHUNK_BYTES;
+        float t[2];
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            const int blk = lane + 32 * j;
+            if (blk < nb) {
+                const int4* wp = reinterpret_cast<const int4*>(buf + blk * 32);
+                const int4 w0 = wp[0], w1 = wp[1];
+                const float wsc = __half2float(*reinterpret_cast<const __half*>(buf + CHUNK * 32 + blk * 2));
+                int acc = 0;
+                acc = __dp4a(w0.x, x0[j].x, acc); acc = __dp4a(w0.y, x0[j].y, acc);
+                acc = __dp4a(w0.z, x0[j].z, acc); acc = __dp4a(w0.w, x0[j].w, acc);
+                acc = __dp4a(w1.x, x1[j].x, acc); acc = __dp4a(w1.y, x1[j].y, acc);
+                acc = __dp4a(w1.z, x1[j].z, acc); acc = __dp4a(w1.w, x1[j].w, acc);
+                t[j] = __fmul_rn(__fmul_rn(wsc, xsc[j]), (float)acc);
+            } else t[j] = 0.0f;
+        }
+        __syncwarp();                                  // every lane has read its blocks: the buffer may be refilled
+        if (lane == 0 && k + RING < my_rows) { ptx::fence_proxy_async(); issue(k + RING); }
+        if (lane < nb) terms[slot * TS + lane] = t[0];
+        if (lane + 32 < nb) terms[slot * TS + lane + 32] = t[1];
+        if (slot == GROUP - 1 || k == my_rows - 1) {
+            __syncwarp();
+            if (lane <= slot) {                        // lane r: the r-th row of this group, blocks in ascending order
+                const float* tp = terms + lane * TS;
+                float sum = 0.0f;
+#pragma unroll 8
+                for (int blk = 0; blk < nb; blk++) sum = __fadd_rn(sum, tp[blk]);
+                float* o = p.out + (first_row + (k - slot + lane) * row_step);
+                *o = p.accumulate ? __fadd_rn(*o, sum) : sum;
+            }
+            __syncwarp();
+        }
+    }
+    if (failed && lane == 0) flare_report(p.err, FLARE_ERR_TIMEOUT);
+}
+
 }  // namespace
 
 extern "C" {
@@ -354,6 +443,24 @@ int flare_launch_matvec_q8_0_preq(flare_attn_ctx* ctx, const flare_weight* w, co
     }
     p.err = ctx->d_err;
     ctx->last_launch_overlappable = false;
+    if (w->cols % 256 == 0 && batch == 1 && w->cols <= CHUNK * 32) {
+        const int ring1_smem = WARPS * RING * RING_CHUNK_BYTES + WARPS * GROUP * TS * (int)sizeof(float);
+        {
+            static std::mutex m3;
+            std::lock_guard<std::mutex> lock(m3);
+            static bool ring1_attr[64] = {};
+            if (!ring1_attr[ctx->device & 63]) {
+                FLARE_CUDA_OK(ctx, cudaFuncSetAttribute(matvec_q8_0_ring1_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ring1_smem));
+                ring1_attr[ctx->device & 63] = true;
+            }
+        }
+        int grid = (w->rows + WARPS - 1) / WARPS;
+        const int max_grid = 148 * 2;                 // two CTAs per SM fit
+        if (grid > max_grid) grid = max_grid;
+        FLARE_CUDA_OK(ctx, flare_launch_pdl(matvec_q8_0_ring1_kernel, dim3(grid), dim3(32 * WARPS), (size_t)ring1_smem, ctx->stream, p));
+        FLARE_LAUNCH_CHECK(ctx);
+        return FLARE_OK;
+    }
     if (w->cols % 256 == 0 && batch <= 2) {
         // One or two input vectors: the product is bound by memory, and rows and chunks start on 16-byte boundaries, so
         // the weights go through a ring of bulk copies.  (From 8 input vectors on the dots dominate and the direct-load
