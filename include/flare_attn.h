@@ -316,7 +316,8 @@ FLARE_API int flare_merge_partials(flare_attn_ctx* ctx, const float* partials, i
  *
  * flare_weight_upload_q8_0   a weight matrix [rows][cols] as the GGUF Q8_0 block stream the loader hands out
  *                            (rows * cols / 32 blocks of 34 bytes, flare-loader/src/quantize.rs:188-197), copied
- *                            to the device once.  cols % 32 == 0.
+ *                            to the device once and kept there as an int8 plane and an f16 scale plane (the same
+ *                            numbers; a block's weights then start on a 32-byte boundary).  cols % 32 == 0.
  * flare_matvec_q8_0          out[b][r] = row r of the matrix . x[b], computed the reference's way so that the
  *                            result is bit-identical to the CPU (x86_64 branch): x is quantised per block of 32
  *                            (scale kept in f32), the int8 dot of a block is exact, and a row's blocks are added
