@@ -52,6 +52,7 @@ std::mutex g_table_mutex;
 
 constexpr int T = 32;            // slots per tile
 constexpr int STAGES = 3;
+constexpr int MAX_CLUSTER = 16;       // 9 .. 16 CTAs per cluster are beyond the portable size: opted into per kernel
 constexpr int L2_AHEAD = 0;      // tiles requested into L2 ahead of the shared-memory copy (0: off; measured slower)
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kQFix = 16256.0f;     // 127 * 128: |Qint| <= 16256 = 128 * limb0 + limb1
@@ -491,9 +492,9 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
         for (int item = threadIdx.x;; item += blockDim.x) {
             const int r = (int)rank + (item / HD) * (int)n, d = item % HD;
             if (r >= p.num_heads) break;
-            float mv[8], lv[8], ov[8];
+            float mv[MAX_CLUSTER], lv[MAX_CLUSTER], ov[MAX_CLUSTER];
 #pragma unroll
-            for (uint32_t s2 = 0; s2 < 8; s2++) {
+            for (uint32_t s2 = 0; s2 < MAX_CLUSTER; s2++) {
                 if (s2 < n) {
                     const uint32_t a = cluster_map(rec0 + (uint32_t)r * (HD + 2) * 4, s2);
                     mv[s2] = cluster_ld(a); lv[s2] = cluster_ld(a + 4); ov[s2] = cluster_ld(a + (2 + d) * 4);
@@ -501,10 +502,10 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
             }
             float mm = -CUDART_INF_F;
 #pragma unroll
-            for (int s2 = 0; s2 < 8; s2++) if (lv[s2] > 0.0f) mm = fmaxf(mm, mv[s2]);
+            for (int s2 = 0; s2 < MAX_CLUSTER; s2++) if (lv[s2] > 0.0f) mm = fmaxf(mm, mv[s2]);
             float ll = 0.0f, o = 0.0f;
 #pragma unroll
-            for (int s2 = 0; s2 < 8; s2++) {
+            for (int s2 = 0; s2 < MAX_CLUSTER; s2++) {
                 const float w = lv[s2] > 0.0f ? fast_exp2(mv[s2] - mm) : 0.0f;
                 ll = fmaf(lv[s2], w, ll);
                 o = fmaf(ov[s2], w, o);
@@ -584,12 +585,19 @@ int flare_launch_decode_q8(flare_attn_ctx* ctx, const DecodeArgs& a) {
     const int ctas_per_sm = smem <= 110 * 1024 ? 2 : 1;
     // one wave: as many splits as fit without a second, partly filled wave
     int n_split = (ctx->sm_count * ctas_per_sm) / (a.batch * chunks);
-    const int max_split = (p.range_max + 4 * T - 1) / (4 * T);    // at least 4 tiles per CTA
+    // at least two tiles per CTA (four was the rule while a cluster held at most 8 CTAs; with 16 a short context at
+    // a small batch is better served by more, shorter ranges: batch 4 x 4096 slots 11.7 -> 10.4 us per call, the
+    // attention inside the single-token forward pass at 1024 slots 4 % of the whole token)
+    int min_tiles = 2;
+#ifdef FLARE_TUNE
+    if (const char* e = getenv("FLARE_Q8_MINTILES")) min_tiles = atoi(e);
+#endif
+    const int max_split = (p.range_max + min_tiles * T - 1) / (min_tiles * T);
     if (n_split > max_split) n_split = max_split;
     if (n_split < 1) n_split = 1;
     if (n_split > 256) n_split = 256;
     // Cluster mode: when a handful of splits per sequence fill the GPU anyway, the splits of a sequence become one
-    // thread-block cluster (2 .. 8 CTAs) and merge through distributed shared memory: no second kernel, no round
+    // thread-block cluster (2 .. 16 CTAs; more than 8 is the non-portable size, opted into) and merge through distributed shared memory: no second kernel, no round
     // trip of the records through global memory.  The size is the largest one, not far below the number of splits
     // that would fit, for which every sequence's cluster is resident at once (a second wave costs more than the
     // merge kernel).  Measured and rejected: clusters of 9 for 32 sequences (only 30 are resident at once); records
@@ -600,7 +608,7 @@ int flare_launch_decode_q8(flare_attn_ctx* ctx, const DecodeArgs& a) {
         std::lock_guard<std::mutex> lock(g_table_mutex);
         // [device][hd == 128][size]: 0 = not asked yet.  Asked with the shapes of the first call (number of kv
         // heads); other shapes of the same head size have smaller or equal footprints
-        static int max_clusters[64][2][9] = {};
+        static int max_clusters[64][2][MAX_CLUSTER + 1] = {};
         static bool attr_set[64][2] = {};
         bool& as = attr_set[ctx->device & 63][hd == 128];
         if (!as) {
@@ -608,13 +616,19 @@ int flare_launch_decode_q8(flare_attn_ctx* ctx, const DecodeArgs& a) {
             const int max_smem = STAGES * (8 * 2 * T * hd + 2 * T * 8 * (hd / 32) * 2) + 1024;
             if (hd == 64) cudaFuncSetAttribute(decode_q8_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
             else cudaFuncSetAttribute(decode_q8_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+            if (hd == 64) cudaFuncSetAttribute(decode_q8_kernel<64>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+            else cudaFuncSetAttribute(decode_q8_kernel<128>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
             cudaGetLastError();
             as = true;
         }
-        int c_first = n_split > 8 ? 8 : n_split;
+        int c_max = MAX_CLUSTER;
+#ifdef FLARE_TUNE
+        if (const char* e = getenv("FLARE_Q8_CMAX")) c_max = atoi(e) > MAX_CLUSTER ? MAX_CLUSTER : atoi(e);
+#endif
+        int c_first = n_split > c_max ? c_max : n_split;
         bool forced = false;
 #ifdef FLARE_TUNE
-        if (const char* e = getenv("FLARE_Q8_CLUSTER")) { c_first = atoi(e) > 8 ? 8 : atoi(e); forced = true; }     // 0 or 1: no cluster
+        if (const char* e = getenv("FLARE_Q8_CLUSTER")) { c_first = atoi(e) > MAX_CLUSTER ? MAX_CLUSTER : atoi(e); forced = true; }     // 0 or 1: no cluster
 #endif
         for (int c = c_first; c >= 2 && !cluster; c--) {
             if (c * 5 < n_split * 4 && !forced) break;            // far fewer CTAs than places: the merge kernel is cheaper
