@@ -385,6 +385,55 @@ def case_kivi(R: Run, steps=None):
             "gpu_launches_per_call": t["launches_per_region"] / (steps or 20), "clocks": t["clocks"], "parity_check": check}
 
 
+def case_verify(R: Run, steps=None, n_q=6):
+    """Speculative verify (flare-core/src/generate.rs:258-303 done in one call per layer): n_q causally ordered
+    queries per sequence over the Q8_0 cache of the headline case (batch 32, context 4096); query i sees
+    n_q - 1 - i slots fewer than the last one.  Two identical layers are read alternately."""
+    torch, fb, eng, args = R.torch, R.fb, R.eng, R.args
+    nh, nkv, hd, ctx, B, L = NH, NKV, HD, CTX, 32, 2
+    kv = eng.kv_alloc(L, B, ctx, nkv, hd, fb.KV_Q8_0)
+    gen = torch.Generator(device="cuda").manual_seed(6 + R.rank)
+    for b in range(B):
+        k = torch.randn(ctx, nkv * hd, device="cuda", generator=gen)
+        v = torch.randn(ctx, nkv * hd, device="cuda", generator=gen)
+        for layer in range(L):
+            kv.append(layer, b, k.data_ptr(), v.data_ptr(), n_rows=ctx)
+        kv.advance(b, ctx)
+    q = torch.randn(B, n_q, nh, hd, device="cuda", generator=gen) * 0.125
+    o = torch.empty(L, B, n_q, nh, hd, device="cuda")
+    att = [ctx] * B
+    state = {"i": 0}
+
+    def fn():
+        layer = state["i"] & 1
+        state["i"] += 1
+        eng.decode(kv, layer, nh, q.data_ptr(), n_q=n_q, attend_len=att, out=o[layer].data_ptr())
+    t = R.timed(fn, steps or 10, 3, min_repeats=10, min_seconds=0.3)
+    check = None
+    if R.rank == 0 and not args.no_cpu:
+        import oracle
+        got = o.cpu().numpy()
+        worst, ok = 0.0, True
+        for layer, b in ((0, 0), (1, B - 1)):
+            kd, vd = kv.export_dequant(layer, b)
+            want = oracle.gqa_decode_batched(q[b].cpu().numpy().reshape(1, n_q, -1), kd[None], vd[None], np.full(1, ctx, np.int32),
+                                             nh, nkv, hd, n_q=n_q).reshape(n_q, -1)
+            err = np.abs(got[layer, b].reshape(n_q, -1) - want)
+            worst = max(worst, float(err.max()))
+            ok = ok and bool(np.all(err <= 2e-3 + 1e-3 * np.abs(want)))
+        check = {"sequences_checked": 2, "queries": n_q, "max_abs_err": worst, "within_tolerance": ok}
+    nbytes = B * ctx * 2 * ROW_BYTES
+    kv.free()
+    return {"metric": "verify_attn_us_per_layer_call", "value": t["ms"] * 1e3, "unit": "us per layer call", "higher_is_better": False,
+            "ms": t["ms"], "repeats": _repeat_info(t), "dtype": DTYPE, "scaling": "weak",
+            "workload": f"speculative verify: {n_q} causally ordered queries per sequence, Q8_0, 32q/8kv heads, head_dim 64, "
+                        f"ctx {ctx}, batch {B}/GPU, 1 layer per call (2 cache copies alternate)",
+            "roofline": R.roofline("hbm", nbytes / (t["ms"] * 1e-3) / 1e9,
+                                   per_launch=f"{nbytes} algorithmic KV bytes (the cache read once for all {n_q} queries) / call time; the "
+                                              "kernel reads the cache once per query, mostly out of L2"),
+            "clocks": t["clocks"], "parity_check": check}
+
+
 def case_f32(R: Run, steps=None):
     """configs[0]: SmolLM2-135M-shaped f32 decode, 512 cached + 1, batch 1: a latency case (788 KB of K+V)."""
     torch, fb, eng, args = R.torch, R.fb, R.eng, R.args
@@ -604,7 +653,7 @@ def _prefill_batch(R):
 
 CASES = {"prefill": lambda R, **kw: case_prefill(R, 0, _prefill_batch(R), **kw),
          "prefill_window": lambda R, **kw: case_prefill(R, 4096, _prefill_batch(R), **kw),
-         "kivi": case_kivi, "longctx": case_longctx, "f32": case_f32, "forward": case_forward}
+         "kivi": case_kivi, "longctx": case_longctx, "f32": case_f32, "forward": case_forward, "verify": case_verify}
 
 
 def case_decode(R: Run):
@@ -725,7 +774,7 @@ def main():
     out = case_decode(R)
     if args.case == "all":
         cases = {}
-        for name in ("prefill", "prefill_window", "kivi", "longctx", "f32", "forward"):
+        for name in ("prefill", "prefill_window", "kivi", "longctx", "f32", "forward", "verify"):
             try:
                 cases[name] = CASES[name](R)
             except Exception as e:                     # a failing side case must not take the headline line with it

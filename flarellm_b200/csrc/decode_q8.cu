@@ -595,6 +595,16 @@ int flare_launch_decode_q8(flare_attn_ctx* ctx, const DecodeArgs& a) {
     const int max_split = (p.range_max + min_tiles * T - 1) / (min_tiles * T);
     if (n_split > max_split) n_split = max_split;
     if (n_split < 1) n_split = 1;
+    // Several queries (or head groups) per sequence and a wave filled to less than three quarters: two full waves of
+    // shorter ranges keep every SM loaded twice (speculative verify, 6 queries x 32 sequences: 192 CTAs on 296 places
+    // took 200 us per call, 576 CTAs take 158 us; 4, 8 and 16 ranges per query were slower)
+    {
+        const int units = a.batch * chunks, places = ctx->sm_count * ctas_per_sm;
+        if (chunks > 1 && n_split * units * 4 < places * 3) {
+            const int two_waves = (2 * places) / units;
+            if (two_waves > n_split && two_waves <= max_split) n_split = two_waves;
+        }
+    }
     if (n_split > 256) n_split = 256;
     // Cluster mode: when a handful of splits per sequence fill the GPU anyway, the splits of a sequence become one
     // thread-block cluster (2 .. 16 CTAs; more than 8 is the non-portable size, opted into) and merge through distributed shared memory: no second kernel, no round
