@@ -132,7 +132,12 @@ __device__ __forceinline__ float cluster_ld(uint32_t addr) {
     float v; asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory"); return v;
 }
 
-template <int HD>
+// TWOQ: a warp's 16 MMA rows carry two work items (a query, or a group of 4 heads of a query) instead of one item
+// twice: rows 0-3 / 8-11 the two limbs of the first, rows 4-7 / 12-15 of the second; in the output product row g
+// carries the weights scaled for the first 32-channel block of a 64-channel tile and row g + 8 those for the second.
+// Calls with several items per sequence (speculative verify, more than 4 query heads per KV head) then read the
+// cache once per pair of items at nearly the cost of one.
+template <int HD, bool TWOQ>
 __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ CUtensorMap kmap,
                                                         const __grid_constant__ CUtensorMap vmap, Q8Params p) {
     constexpr int NB = HD / 32;        // Q8_0 blocks per head row
@@ -158,10 +163,21 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
 
     // blockIdx.z: which query of the sequence (speculative verify: query i sees n_q-1-i slots fewer) and which
     // group of up to 4 query heads per KV head; each such chunk streams the cache on its own
-    const int qi = blockIdx.z / p.hgroups, hg = blockIdx.z % p.hgroups;
-    // slot range of this (sequence, query, split), in whole tiles
-    int lo = 0, hi = max(0, (p.n_small ? p.attend_small[b] : p.attend_len[b]) - (p.causal_q ? (p.n_q - 1 - qi) : 0));
-    if (p.slot_end >= 0) { lo = max(lo, p.slot_begin); hi = min(hi, p.slot_end); }
+    const int n_items = p.n_q * p.hgroups;
+    const int item = TWOQ ? min(2 * (int)blockIdx.z + (g >> 2), n_items - 1) : (int)blockIdx.z;     // this lane's item
+    const bool item_ok = !TWOQ || 2 * (int)blockIdx.z + (g >> 2) < n_items;
+    const int qi = item / p.hgroups, hg = item % p.hgroups;
+    // slot range of this (sequence, query, split), in whole tiles.  With two items the tiles cover the longer of the two
+    // ranges (the later query's); a lane masks what lies beyond its own.
+    const int attend_b = p.n_small ? p.attend_small[b] : p.attend_len[b];
+    int lo = 0, hi = max(0, attend_b - (p.causal_q ? (p.n_q - 1 - qi) : 0));
+    int hi_lane = hi, hi_short = hi;
+    if (TWOQ) {
+        const int q_hi = min(2 * (int)blockIdx.z + 1, n_items - 1) / p.hgroups, q_lo = (2 * (int)blockIdx.z) / p.hgroups;
+        hi = max(0, attend_b - (p.causal_q ? (p.n_q - 1 - q_hi) : 0));
+        hi_short = max(0, attend_b - (p.causal_q ? (p.n_q - 1 - q_lo) : 0));
+    }
+    if (p.slot_end >= 0) { lo = max(lo, p.slot_begin); hi = min(hi, p.slot_end); hi_lane = min(hi_lane, p.slot_end); hi_short = min(hi_short, p.slot_end); }
     int t_first = lo / T, t_last = hi > lo ? (hi + T - 1) / T : t_first;
     const int n_tiles_seq = t_last - t_first;
     const int t_begin = t_first + (int)(((long long)split * n_tiles_seq) / p.n_split);
@@ -218,7 +234,7 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
     // q was written by an earlier kernel of the stream: asking L2 for its lines ahead of the wait below is harmless
     // (L2 stays coherent with later writes) and takes a DRAM round trip out of the path between the wait and the
     // first product when q has been pushed out of L2 by the cache stream of the previous call
-    if (p.prefetch_q && (lane & 3) < NB) {
+    if (!TWOQ && p.prefetch_q && (lane & 3) < NB) {
         const int hq0 = (lane >> 2) & 3;
         const int heads_here = min(4, p.G - 4 * (int)(blockIdx.z % p.hgroups));
         const size_t row0 = ((size_t)b * p.n_q + blockIdx.z / p.hgroups) * p.num_heads + warp * p.G + 4 * (blockIdx.z % p.hgroups) +
@@ -239,7 +255,7 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
 
     // ---- q as two int8 limbs per head, laid out as the A operand of m16n8k32 --------------
     const int hq = g & 3;                          // query head of this lane within the group
-    const bool head_ok = hq < min(4, p.G - 4 * hg);
+    const bool head_ok = item_ok && hq < min(4, p.G - 4 * hg);
     const size_t row = ((size_t)b * p.n_q + qi) * p.num_heads + kvh * p.G + 4 * hg + (head_ok ? hq : 0);
     uint32_t qa[NB][4];
     float qs;                                       // score = qs * sum_blk ks * (int dot)
@@ -291,9 +307,9 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
             for (int e = 0; e < 2; e++)
 #pragma unroll
                 for (int i = 0; i < 4; i++) acc[mt][c][e][i] = 0.0f;
-    float m_run = -CUDART_INF_F, l_run = 0.0f, lb[MT];
+    float m_run = -CUDART_INF_F, l_run = 0.0f, lb[MT], lb2[MT];      // lb2: TWOQ, the second channel block's bias sum
 #pragma unroll
-    for (int mt = 0; mt < MT; mt++) lb[mt] = 0.0f;
+    for (int mt = 0; mt < MT; mt++) { lb[mt] = 0.0f; lb2[mt] = 0.0f; }
 
     const int lane_blk = g >> 2;    // which block of an M-tile this lane's rows belong to
 
@@ -311,7 +327,7 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
             voff[mt][cp] = payload + kvh * TILE + swz<HD>(((lane >> 3) & 1) * 8 + (lane & 7), 4 * mt + 2 * cp + (lane >> 4));
     // scales of slot 2*tig (+1) of each 8-slot step, this head: [slot][nkv*NB] f16
     const uint32_t ksoff = 2 * payload + (2 * tig * bpr + kvh * NB) * 2;
-    const uint32_t vsoff = ksoff + scale_tile + lane_blk * 2;
+    const uint32_t vsoff = ksoff + scale_tile + (TWOQ ? 0 : lane_blk * 2);
 
     bool failed = false;
     TL_STAMP(3);            // q ready
@@ -325,8 +341,9 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
 
         // ---- scores: int8 MMA per 8-slot column tile and 32-channel block ------------------
         float sc[4][2], vs[MT][4][2];    // sc: integer-domain scores (score = qs * sc, qs >= 0)
+        float vs2[TWOQ ? MT : 1][4][2];  // TWOQ: the scales of the second 32-channel block (vs holds the first)
         float tmax = -CUDART_INF_F;
-        const bool edge_tile = (slot0 < lo) || (slot0 + T > hi);      // warp-uniform
+        const bool edge_tile = (slot0 < lo) || (slot0 + T > (TWOQ ? hi_short : hi));      // warp-uniform
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             float s0 = 0.0f, s1 = 0.0f;
@@ -335,8 +352,15 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
                 // (blk 2h, blk 2h+1) scales of slots 8j + 2tig and 8j + 2tig + 1
                 const float2 kf0 = unpack_half2(*reinterpret_cast<const uint32_t*>(kt + FLARE_CK(ksoff + (8 * j * bpr + 2 * h) * 2, 4, stage_bytes, p.err)));
                 const float2 kf1 = unpack_half2(*reinterpret_cast<const uint32_t*>(kt + FLARE_CK(ksoff + ((8 * j + 1) * bpr + 2 * h) * 2, 4, stage_bytes, p.err)));
-                vs[h][j][0] = __half2float(*reinterpret_cast<const __half*>(kt + FLARE_CK(vsoff + (8 * j * bpr + 2 * h) * 2, 2, stage_bytes, p.err)));
-                vs[h][j][1] = __half2float(*reinterpret_cast<const __half*>(kt + FLARE_CK(vsoff + ((8 * j + 1) * bpr + 2 * h) * 2, 2, stage_bytes, p.err)));
+                if (TWOQ) {
+                    const float2 v0 = unpack_half2(*reinterpret_cast<const uint32_t*>(kt + FLARE_CK(vsoff + (8 * j * bpr + 2 * h) * 2, 4, stage_bytes, p.err)));
+                    const float2 v1 = unpack_half2(*reinterpret_cast<const uint32_t*>(kt + FLARE_CK(vsoff + ((8 * j + 1) * bpr + 2 * h) * 2, 4, stage_bytes, p.err)));
+                    vs[h][j][0] = v0.x; vs2[h][j][0] = v0.y;
+                    vs[h][j][1] = v1.x; vs2[h][j][1] = v1.y;
+                } else {
+                    vs[h][j][0] = __half2float(*reinterpret_cast<const __half*>(kt + FLARE_CK(vsoff + (8 * j * bpr + 2 * h) * 2, 2, stage_bytes, p.err)));
+                    vs[h][j][1] = __half2float(*reinterpret_cast<const __half*>(kt + FLARE_CK(vsoff + ((8 * j + 1) * bpr + 2 * h) * 2, 2, stage_bytes, p.err)));
+                }
 #pragma unroll
                 for (int bb = 0; bb < 2; bb++) {
                     const int blk = 2 * h + bb;
@@ -354,15 +378,16 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
                 // the end of the plane are never copied, so that part of the stage keeps what an earlier kernel
                 // left in shared memory (possibly Inf or NaN bit patterns, and 0 * NaN = NaN).  Zero it as well.
                 const int slot = slot0 + 8 * j + 2 * tig;
-                if (slot < lo || slot >= hi) {
+                const int hi_mine = TWOQ ? hi_lane : hi;
+                if (slot < lo || slot >= hi_mine) {
                     s0 = -CUDART_INF_F;
 #pragma unroll
-                    for (int h = 0; h < NB / 2; h++) vs[h][j][0] = 0.0f;
+                    for (int h = 0; h < NB / 2; h++) { vs[h][j][0] = 0.0f; if (TWOQ) vs2[h][j][0] = 0.0f; }
                 }
-                if (slot + 1 < lo || slot + 1 >= hi) {
+                if (slot + 1 < lo || slot + 1 >= hi_mine) {
                     s1 = -CUDART_INF_F;
 #pragma unroll
-                    for (int h = 0; h < NB / 2; h++) vs[h][j][1] = 0.0f;
+                    for (int h = 0; h < NB / 2; h++) { vs[h][j][1] = 0.0f; if (TWOQ) vs2[h][j][1] = 0.0f; }
                 }
             }
             sc[j][0] = s0; sc[j][1] = s1;
@@ -381,6 +406,7 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
 #pragma unroll
             for (int mt = 0; mt < MT; mt++) {
                 lb[mt] *= alpha;
+                lb2[mt] *= alpha;
 #pragma unroll
                 for (int c = 0; c < 4; c++)
 #pragma unroll
@@ -392,7 +418,8 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
         // every tile of a non-empty range holds at least one slot of it, so m_run is finite from the
         // first tile on and a masked slot gives exp2(-inf) = 0
         float pw[4][2];
-        const float neg_m = -m_run;
+        // two items: a lane whose own range ends before this CTA's first tile has seen nothing yet (m_run = -inf)
+        const float neg_m = (TWOQ && m_run == -CUDART_INF_F) ? 0.0f : -m_run;
 #pragma unroll
         for (int j = 0; j < 4; j++)
 #pragma unroll
@@ -413,7 +440,14 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
                 const float2 wf = unpack_half2(wb);
                 lb[mt] += wf.x + wf.y;
                 pa[j >> 1][(j & 1) * 2] = wb;             // a0 / a2: row g
-                pa[j >> 1][(j & 1) * 2 + 1] = 0u;         // a1 / a3: row g+8 unused
+                if (TWOQ) {                               // a1 / a3: row g+8, the weights for the second channel block
+                    const uint32_t wb2 = pack_half2(pw[j][0] * vs2[mt][j][0], pw[j][1] * vs2[mt][j][1]);
+                    const float2 wf2 = unpack_half2(wb2);
+                    lb2[mt] += wf2.x + wf2.y;
+                    pa[j >> 1][(j & 1) * 2 + 1] = wb2;
+                } else {
+                    pa[j >> 1][(j & 1) * 2 + 1] = 0u;     // a1 / a3: row g+8 unused
+                }
             }
 #pragma unroll
             for (int kstep = 0; kstep < 2; kstep++) {
@@ -464,8 +498,12 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
     for (int mt = 0; mt < MT; mt++) {
         lb[mt] += __shfl_xor_sync(0xffffffffu, lb[mt], 1);
         lb[mt] += __shfl_xor_sync(0xffffffffu, lb[mt], 2);
+        if (TWOQ) {
+            lb2[mt] += __shfl_xor_sync(0xffffffffu, lb2[mt], 1);
+            lb2[mt] += __shfl_xor_sync(0xffffffffu, lb2[mt], 2);
+        }
     }
-    if (p.cluster) {
+    if (!TWOQ && p.cluster) {
         // The splits of this sequence are the CTAs of one cluster: every CTA leaves its (m, l, o) records
         // in its own shared memory, then each merges a share of the rows by reading its peers' records.
         __syncthreads();                                    // all warps are done with the stage buffers
@@ -522,6 +560,29 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
 #ifdef FLARE_DEBUG_BOUNDS
     if (row >= (size_t)gridDim.y * p.n_q * p.num_heads || split >= p.n_split) { flare_report(p.err, FLARE_ERR_BOUNDS); return; }
 #endif
+    if (TWOQ) {
+        // this lane's row: channels of the first block from row g (accumulator elements 0, 1), of the second from row g + 8
+#pragma unroll
+        for (int mt = 0; mt < MT; mt++) {
+#pragma unroll
+            for (int vb = 0; vb < 2; vb++) {
+                const float bias = 1152.0f * (vb ? lb2[mt] : lb[mt]);
+#pragma unroll
+                for (int lc = 0; lc < 2; lc++) {
+                    const int c = 2 * vb + lc, d0 = 64 * mt + 16 * c + 4 * tig;
+                    const float o0 = acc[mt][c][0][2 * vb] - bias, o1 = acc[mt][c][1][2 * vb] - bias;
+                    const float o2 = acc[mt][c][0][2 * vb + 1] - bias, o3 = acc[mt][c][1][2 * vb + 1] - bias;
+                    if (final_out) {
+                        *reinterpret_cast<float4*>(p.out + row * HD + d0) = make_float4(o0 * inv_l, o1 * inv_l, o2 * inv_l, o3 * inv_l);
+                    } else {
+                        *reinterpret_cast<float2*>(wrec + 2 + d0) = make_float2(o0, o1);
+                        *reinterpret_cast<float2*>(wrec + 2 + d0 + 2) = make_float2(o2, o3);
+                    }
+                }
+            }
+        }
+        if (!final_out && tig == 0) { wrec[0] = m_run; wrec[1] = l_run; }
+    } else {
 #pragma unroll
     for (int mt = 0; mt < MT; mt++) {
         const float bias = 1152.0f * lb[mt];
@@ -543,6 +604,7 @@ __global__ void __launch_bounds__(256) decode_q8_kernel(const __grid_constant__ 
         }
     }
     if (!final_out && g < 4 && tig == 0) { wrec[0] = m_run; wrec[1] = l_run; }
+    }
 }
 
 }  // namespace
@@ -584,7 +646,10 @@ int flare_launch_decode_q8(flare_attn_ctx* ctx, const DecodeArgs& a) {
     const size_t smem = STAGES * stage + 1024;
     const int ctas_per_sm = smem <= 110 * 1024 ? 2 : 1;
     // one wave: as many splits as fit without a second, partly filled wave
-    int n_split = (ctx->sm_count * ctas_per_sm) / (a.batch * chunks);
+    // several items (queries, groups of 4 heads) per sequence go two to a CTA
+    const bool two_items = chunks >= 2;
+    const int zdim = two_items ? (chunks + 1) / 2 : chunks;
+    int n_split = (ctx->sm_count * ctas_per_sm) / (a.batch * zdim);
     // at least two tiles per CTA (four was the rule while a cluster held at most 8 CTAs; with 16 a short context at
     // a small batch is better served by more, shorter ranges: batch 4 x 4096 slots 11.7 -> 10.4 us per call, the
     // attention inside the single-token forward pass at 1024 slots 4 % of the whole token)
@@ -599,7 +664,7 @@ int flare_launch_decode_q8(flare_attn_ctx* ctx, const DecodeArgs& a) {
     // shorter ranges keep every SM loaded twice (speculative verify, 6 queries x 32 sequences: 192 CTAs on 296 places
     // took 200 us per call, 576 CTAs take 158 us; 4, 8 and 16 ranges per query were slower)
     {
-        const int units = a.batch * chunks, places = ctx->sm_count * ctas_per_sm;
+        const int units = a.batch * zdim, places = ctx->sm_count * ctas_per_sm;
         if (chunks > 1 && n_split * units * 4 < places * 3) {
             const int two_waves = (2 * places) / units;
             if (two_waves > n_split && two_waves <= max_split) n_split = two_waves;
@@ -624,10 +689,10 @@ int flare_launch_decode_q8(flare_attn_ctx* ctx, const DecodeArgs& a) {
         if (!as) {
             // the opt-in to large dynamic shared memory has to precede the occupancy queries
             const int max_smem = STAGES * (8 * 2 * T * hd + 2 * T * 8 * (hd / 32) * 2) + 1024;
-            if (hd == 64) cudaFuncSetAttribute(decode_q8_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
-            else cudaFuncSetAttribute(decode_q8_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
-            if (hd == 64) cudaFuncSetAttribute(decode_q8_kernel<64>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
-            else cudaFuncSetAttribute(decode_q8_kernel<128>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+            if (hd == 64) cudaFuncSetAttribute(decode_q8_kernel<64, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+            else cudaFuncSetAttribute(decode_q8_kernel<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+            if (hd == 64) cudaFuncSetAttribute(decode_q8_kernel<64, false>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+            else cudaFuncSetAttribute(decode_q8_kernel<128, false>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
             cudaGetLastError();
             as = true;
         }
@@ -651,8 +716,8 @@ int flare_launch_decode_q8(flare_attn_ctx* ctx, const DecodeArgs& a) {
                 qc.gridDim = dim3(c, 1); qc.blockDim = dim3(32 * nkv); qc.dynamicSmemBytes = smem;
                 qc.attrs = ca; qc.numAttrs = 1;
                 int n = 0;
-                cudaError_t e = hd == 64 ? cudaOccupancyMaxActiveClusters(&n, decode_q8_kernel<64>, &qc)
-                                         : cudaOccupancyMaxActiveClusters(&n, decode_q8_kernel<128>, &qc);
+                cudaError_t e = hd == 64 ? cudaOccupancyMaxActiveClusters(&n, decode_q8_kernel<64, false>, &qc)
+                                         : cudaOccupancyMaxActiveClusters(&n, decode_q8_kernel<128, false>, &qc);
                 if (e != cudaSuccess) { cudaGetLastError(); n = 0; }
                 mc = n > 0 ? n : -1;
             }
@@ -687,8 +752,8 @@ int flare_launch_decode_q8(flare_attn_ctx* ctx, const DecodeArgs& a) {
         bool& done = attr_done[ctx->device & 63][hd == 128];
         if (!done) {
             const int max_smem = STAGES * (8 * 2 * T * hd + 2 * T * 8 * (hd / 32) * 2) + 1024;
-            if (hd == 64) FLARE_CUDA_OK(ctx, cudaFuncSetAttribute(decode_q8_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
-            else FLARE_CUDA_OK(ctx, cudaFuncSetAttribute(decode_q8_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
+            if (hd == 64) FLARE_CUDA_OK(ctx, cudaFuncSetAttribute(decode_q8_kernel<64, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
+            else FLARE_CUDA_OK(ctx, cudaFuncSetAttribute(decode_q8_kernel<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
             done = true;
         }
     }
@@ -701,7 +766,7 @@ int flare_launch_decode_q8(flare_attn_ctx* ctx, const DecodeArgs& a) {
     attr[1].id = cudaLaunchAttributeClusterDimension;
     attr[1].val.clusterDim.x = cluster ? cluster : 1; attr[1].val.clusterDim.y = 1; attr[1].val.clusterDim.z = 1;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(n_split, a.batch, chunks);
+    cfg.gridDim = dim3(n_split, a.batch, zdim);
     cfg.blockDim = dim3(32 * nkv);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = ctx->stream;
@@ -712,8 +777,24 @@ int flare_launch_decode_q8(flare_attn_ctx* ctx, const DecodeArgs& a) {
 #ifdef FLARE_TUNE
     if (const char* e = getenv("FLARE_Q8_ALWAYS_PDL")) if (!atoi(e) && !ctx->last_launch_overlappable) { cfg.attrs = attr + 1; cfg.numAttrs = cluster ? 1 : 0; }
 #endif
-    if (hd == 64) FLARE_CUDA_OK(ctx, cudaLaunchKernelEx(&cfg, decode_q8_kernel<64>, *a.kmap, *a.vmap, p));
-    else FLARE_CUDA_OK(ctx, cudaLaunchKernelEx(&cfg, decode_q8_kernel<128>, *a.kmap, *a.vmap, p));
+    if (two_items) {
+        std::lock_guard<std::mutex> lock(g_table_mutex);
+        static bool attr2_done[64][2] = {};
+        bool& done2 = attr2_done[ctx->device & 63][hd == 128];
+        if (!done2) {
+            const int max_smem = STAGES * (8 * 2 * T * hd + 2 * T * 8 * (hd / 32) * 2) + 1024;
+            if (hd == 64) FLARE_CUDA_OK(ctx, cudaFuncSetAttribute(decode_q8_kernel<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
+            else FLARE_CUDA_OK(ctx, cudaFuncSetAttribute(decode_q8_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
+            done2 = true;
+        }
+    }
+    if (two_items) {
+        if (hd == 64) FLARE_CUDA_OK(ctx, cudaLaunchKernelEx(&cfg, decode_q8_kernel<64, true>, *a.kmap, *a.vmap, p));
+        else FLARE_CUDA_OK(ctx, cudaLaunchKernelEx(&cfg, decode_q8_kernel<128, true>, *a.kmap, *a.vmap, p));
+    } else {
+        if (hd == 64) FLARE_CUDA_OK(ctx, cudaLaunchKernelEx(&cfg, decode_q8_kernel<64, false>, *a.kmap, *a.vmap, p));
+        else FLARE_CUDA_OK(ctx, cudaLaunchKernelEx(&cfg, decode_q8_kernel<128, false>, *a.kmap, *a.vmap, p));
+    }
     FLARE_LAUNCH_CHECK(ctx);
     ctx->last_launch_overlappable = true;
     if (a.defer_merge && a.want_partial) {          // the caller merges: tell it where the records are
