@@ -246,7 +246,8 @@ FLARE_API int flare_kv_export_dequant(flare_kv* kv, int layer, int seq, float* k
  *                  query i reads attend_len[b] - (n_q-1-i) slots.  NULL = ring state:
  *                  min(length + 1, max_seq_len)  (model.rs:2209; clamped once the ring is full).
  *   softcap        must be 0 (the wgpu backend asserts the same, backend.rs:4907-4910).
- * K/V are streamed once per kv head for all query heads that share it.  With host buffers
+ * K/V are streamed once per kv head for up to 4 query heads that share it and one query; with several queries
+ * (or more than 4 heads per kv head) a Q8_0 cache with head_dim 64 / 128 is streamed once per pair of them.  With host buffers
  * (on_device = 0) the call returns when `out` is filled; an `out` in page-locked memory
  * (cudaHostAlloc / cudaHostRegister) is written by the kernels directly, with no copy after them. */
 FLARE_API int flare_decode_attn(flare_attn_ctx* ctx, flare_kv* kv, int layer, int num_heads,
