@@ -653,7 +653,9 @@ int flare_launch_decode_q8(flare_attn_ctx* ctx, const DecodeArgs& a) {
     // at least two tiles per CTA (four was the rule while a cluster held at most 8 CTAs; with 16 a short context at
     // a small batch is better served by more, shorter ranges: batch 4 x 4096 slots 11.7 -> 10.4 us per call, the
     // attention inside the single-token forward pass at 1024 slots 4 % of the whole token)
-    int min_tiles = 2;
+    // (slot-range calls and calls whose records another kernel merges keep four: twice the ranges are twice the
+    // records for that kernel)
+    int min_tiles = (a.defer_merge || a.want_partial || a.slot_end >= 0) ? 4 : 2;
 #ifdef FLARE_TUNE
     if (const char* e = getenv("FLARE_Q8_MINTILES")) min_tiles = atoi(e);
 #endif
