@@ -20,7 +20,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 DBG = os.path.join(ROOT, "flarellm_b200", "libflare_attn_dbg.so")
 
 SELECTION = [
-    ("tests/test_gpu_decode.py", "q8_split_counts or ring_size_not_a_tile or q8_ring_wrap or speculative or bounded_wait"),
+    ("tests/test_gpu_decode.py", "q8_split_counts or ring_size_not_a_tile or q8_ring_wrap or speculative or two_items or bounded_wait"),
     ("tests/test_gpu_kivi.py", "tensor_core_path or wrapped_ring or ragged_batch"),
     ("tests/test_gpu_prefill.py", "tensor_core"),
 ]

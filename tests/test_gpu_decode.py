@@ -294,6 +294,32 @@ def test_q8_speculative_verify_six_queries(eng, fb, orc):
     kv.free()
 
 
+@pytest.mark.parametrize("nh,nkv,hd,n_q,prior", [
+    (32, 8, 128, 5, 1000),        # head_dim 128, an odd number of queries: the last CTA carries one item only
+    (16, 2, 64, 3, 777),          # 8 query heads per kv head: two head groups per query, 6 items in 3 CTAs
+    (16, 2, 64, 1, 2000),         # the same heads, plain decode: the two head groups of one query share a CTA
+])
+def test_q8_two_items_per_warp(eng, fb, orc, nh, nkv, hd, n_q, prior):
+    """Calls with several (query, group of 4 heads) items per sequence put two of them into one CTA: each query must
+    see exactly its own causal range and each head its own rows, also when the items differ in range or are odd in
+    number."""
+    B = 3
+    ms = 2048 if prior + n_q <= 2048 else 4096
+    kv, k, v = _q8_setup(eng, fb, orc, B, ms, prior, nkv, hd, 71)
+    dk_, dv_ = normal(73, (B, n_q, nkv * hd)), normal(74, (B, n_q, nkv * hd))
+    for b in range(B):
+        for i in range(n_q):
+            kv.write(0, b, prior + i, dk_[b, i], dv_[b, i])
+    q = normal(75, (B, n_q, nh, hd), 0.5)
+    got = eng.decode(kv, 0, nh, q, n_q=n_q, attend_len=np.full(B, prior + n_q, np.int32))
+    kd = orc.dequant_q8_0(orc.quantize_q8_0(np.concatenate([k, dk_], axis=1)))
+    vd = orc.dequant_q8_0(orc.quantize_q8_0(np.concatenate([v, dv_], axis=1)))
+    want = orc.gqa_decode_batched(q.reshape(B, n_q, -1), kd, vd, np.full(B, prior + n_q, np.int32), nh, nkv, hd,
+                                  n_q=n_q, threads=8)
+    assert_close(got, want, f"two items per warp, {nh}/{nkv} heads x {hd}, {n_q} queries")
+    kv.free()
+
+
 def test_q8_head_dim_128_long_context_and_partials(eng, fb, orc):
     """Llama-3-8B shape (32/8, head_dim 128), Q8_0; slot ranges merged by log-sum-exp."""
     nh, nkv, hd, n = 32, 8, 128, 8192
