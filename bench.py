@@ -697,9 +697,12 @@ def case_decode(R: Run):
     q_l = [pack_np[i, 2 * row_fl:] for i in range(layers)]
     o_l = [out_host[i] for i in range(layers)]
 
+    # host addresses resolved once, as a Rust caller's slices are (the ndarrays above stay alive)
+    k_a, v_a, q_a, o_a = ([int(x.ctypes.data) for x in xs] for xs in (k_l, v_l, q_l, o_l))
+
     def step_e2e():
         for layer in range(layers):
-            eng.decode_step(kv, layer, NH, k_l[layer], v_l[layer], q_l[layer], out=o_l[layer])
+            eng.decode_step(kv, layer, NH, k_a[layer], v_a[layer], q_a[layer], out=o_a[layer], on_device=False)
 
     t = R.timed(step_device, args.steps, max(3, args.warmup))
     te = R.timed(step_e2e, max(3, min(args.steps, 20)), 3, min_repeats=10, min_seconds=0.3)

@@ -230,9 +230,16 @@ class Engine:
                                             int(on_device)))
         return out
 
-    def decode_step(self, kv: "KvCache", layer, num_heads, key, value, q, out=None):
+    def decode_step(self, kv: "KvCache", layer, num_heads, key, value, q, out=None, on_device=None):
         """flare_decode_step: store the new K/V row of every sequence, then attend.  Host ndarrays
-        (``out`` optional) or device pointers (``out`` required)."""
+        (``out`` optional), device pointers (``out`` required), or — with ``on_device=False`` — plain host addresses
+        (ints) of buffers the caller keeps alive, resolved once outside a loop the way a Rust caller's slices are:
+        converting four ndarrays to pointers costs about 5 us per call in Python."""
+        if on_device is not None and not isinstance(q, np.ndarray):
+            rc = self.L.flare_decode_step(self.h, kv.h, layer, num_heads, key, value, q, out, 1 if on_device else 0)
+            if rc:
+                self.check(rc)
+            return out
         on_device = not isinstance(q, np.ndarray)
         if not on_device:
             key, value, q = (a if (a.dtype == np.float32 and a.flags["C_CONTIGUOUS"]) else

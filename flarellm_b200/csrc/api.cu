@@ -140,6 +140,17 @@ static const float* device_view_of_host(const void* p) {
     return nullptr;
 }
 
+// The same question for an INPUT buffer, remembered per address: a wrong answer (memory freed and reused as pageable at
+// the same address) only costs the copy its speed, never its correctness, which is why outputs are always asked anew.
+static bool input_is_locked(flare_attn_ctx* ctx, const void* p) {
+    for (auto& e : ctx->lock_cache)
+        if (e.p == p) return e.locked;
+    const bool locked = device_view_of_host(p) != nullptr;
+    auto& slot = ctx->lock_cache[ctx->lock_cache_next++ % 64];
+    slot.p = p; slot.locked = locked;
+    return locked;
+}
+
 #define CHECK_CTX(ctx) do { if (!(ctx)) return FLARE_ERR_INVALID_ARG; } while (0)
 #define BIND(ctx) FLARE_CUDA_OK(ctx, cudaSetDevice((ctx)->device))
 
@@ -861,7 +872,7 @@ int flare_decode_step(flare_attn_ctx* ctx, flare_kv* kv, int layer, int num_head
     FLARE_TRY(flare_ensure(ctx, &ctx->d_stage_in, &ctx->stage_in_bytes, bytes));
     float* d = (float*)ctx->d_stage_in;
     const float *dk = d, *dv = d + row_fl, *dq = d + 2 * row_fl;
-    const bool locked = device_view_of_host(key) && device_view_of_host(value) && device_view_of_host(q);
+    const bool locked = input_is_locked(ctx, key) && input_is_locked(ctx, value) && input_is_locked(ctx, q);
     const size_t slot_bytes = 1u << 20;
     if (locked && value == key + row_fl && q == value + row_fl) {
         // page-locked and laid out [K rows][V rows][q] in one piece (a host that keeps its per-layer forward

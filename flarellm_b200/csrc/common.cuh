@@ -45,6 +45,10 @@ struct flare_attn_ctx {
     void* h_rows = nullptr;      size_t rows_slot_bytes = 0;
     cudaEvent_t rows_events[FLARE_ROW_SLOTS] = {};
     uint64_t rows_counter = 0;
+    // inputs of flare_decode_step already classified as page-locked or pageable (a decode loop passes the same
+    // buffers every token; the driver query costs about a microsecond per pointer)
+    struct { const void* p; bool locked; } lock_cache[64] = {};
+    unsigned lock_cache_next = 0;
     uint64_t small_counter = 0;
     std::vector<int> small_last;       // host copy of the last uploaded (ring, attend) arrays
     const void* small_last_dev = nullptr;
